@@ -1,0 +1,71 @@
+// Shared device helpers for every kernel file: element load/store through fp32,
+// warp and block reductions, and the status word that kernels write instead of
+// trapping. Each .cu file is compiled on its own into one shared library and
+// exports plain C entry points that take raw device pointers and a stream.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SI_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Status codes written (atomicMax) into the engine's device status word.
+enum SiStatus : int {
+  SI_OK = 0,
+  SI_BAD_TOKEN = 1,      // token id outside [0, vocab)
+  SI_BAD_PAGE = 2,       // block table entry outside [0, num_pages)
+  SI_BAD_SEQ = 3,        // row names a sequence outside the batch
+  SI_WAIT_LIMIT = 4,     // a bounded wait inside a kernel ran out
+};
+
+// dtype codes shared with the Python binding
+enum SiDtype : int { SI_F32 = 0, SI_BF16 = 1 };
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();                 // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float s = lane < nwarps ? scratch[lane] : 0.f;
+    s = warp_sum(s);
+    if (lane == 0) scratch[32] = s;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__device__ __forceinline__ void set_status(int* status, int code) {
+  if (status) atomicMax(status, code);
+}
+
+static inline int si_last_error() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}

@@ -1,0 +1,207 @@
+"""Python side of the CUDA kernels: thin wrappers that check shapes and dtypes, pass raw
+device pointers and the current stream to the C entry points, and raise on any error.
+Nothing here computes on the CPU or through a library: a missing build fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, found {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_p:
+    return _c_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> _c_p:
+    return _c_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*ts) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels take CUDA tensors only; there is no CPU path")
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc == -2:
+        raise KernelError(f"{what}: this size is outside what the kernel supports")
+    raise KernelError(f"{what}: CUDA error {rc}")
+
+
+_fn_cache = {}
+
+
+def _fn(libname: str, symbol: str, argtypes):
+    key = (libname, symbol)
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = build.load(libname)
+        f = getattr(lib, symbol)
+        f.argtypes = argtypes
+        f.restype = _c_int
+        _fn_cache[key] = f
+    return f
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> None:
+    if t is not None:
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be contiguous int32")
+
+
+# ---------------------------------------------------------------------------------------
+
+def embedding_gather(tokens, table, out, status=None) -> None:
+    """out[t,:] (fp32) = table[tokens[t],:]."""
+    _cuda(tokens, table, out, status)
+    _i32(tokens, "tokens")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous(),
+          "embedding: out must be contiguous fp32, table contiguous")
+    T, d = out.shape
+    _need(table.shape[1] == d and tokens.numel() == T, "embedding: shape mismatch")
+    f = _fn("embedding", "si_embedding_gather",
+            [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(tokens), _ptr(table), _dt(table), _ptr(out), T, d, table.shape[0],
+             _ptr(status), _stream()), "embedding_gather")
+
+
+def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None) -> None:
+    """resid (fp32, in place) += delta; out = weight * resid * rsqrt(mean(resid^2) + eps).
+
+    With ``rows`` (int32 [R]) output row r comes from stream row rows[r] and resid stays
+    as it is.
+    """
+    _cuda(resid, delta, weight, out, rows)
+    _i32(rows, "rows")
+    d = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
+          and weight.is_contiguous(), "add_rmsnorm: tensors must be contiguous, resid fp32")
+    _need(weight.numel() == d and out.shape[-1] == d, "add_rmsnorm: width mismatch")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == resid.shape,
+              "add_rmsnorm: delta must match resid's shape and out's dtype")
+    R = out.shape[0]
+    _need(R == (rows.numel() if rows is not None else resid.shape[0]), "add_rmsnorm: row count mismatch")
+    f = _fn("norm", "si_add_rmsnorm",
+            [_c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), _dt(weight), _ptr(out), _dt(out),
+             R, d, float(eps), _stream()), f"add_rmsnorm(hidden={d})")
+
+
+def rope_kv_write(qkv, positions, row_seq, inv_freq, rot_dim: int, block_table, k_cache, v_cache,
+                  page_size: int, num_seqs: int, H: int, KV: int, hs: int, status=None) -> None:
+    """Rotate q (in place) and k, store k and v of every row into its page.
+
+    qkv: [T, (H+2KV)*hs]; k_cache/v_cache: [num_pages, KV, page_size, hs] of one layer, or None
+    to rotate q only; inv_freq: fp32 [rot_dim/2] or None for no rotation.
+    """
+    _cuda(qkv, positions, row_seq, inv_freq, block_table, k_cache, v_cache, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    T = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (H + 2 * KV) * hs, "rope_kv_write: qkv shape")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dim,
+              "rope_kv_write: inv_freq must be fp32 [rot_dim/2]")
+    num_pages = 0
+    if k_cache is not None:
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype and k_cache.is_contiguous()
+              and v_cache.is_contiguous(), "rope_kv_write: cache dtype/layout")
+        _need(tuple(k_cache.shape[1:]) == (KV, page_size, hs) and k_cache.shape == v_cache.shape,
+              "rope_kv_write: cache must be [pages, KV, page_size, hs]")
+        num_pages = k_cache.shape[0]
+    f = _fn("rope_kv", "si_rope_kv_write",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(positions), _ptr(row_seq), _ptr(inv_freq),
+             rot_dim, _ptr(block_table), block_table.shape[1], _ptr(k_cache), _ptr(v_cache),
+             num_pages, page_size, T, num_seqs, H, KV, hs, _ptr(status), _stream()),
+           f"rope_kv_write(head_dim={hs}, rot_dim={rot_dim})")
+
+
+def paged_attention_ref(q, k_cache, v_cache, block_table, row_seq, positions, out, page_size: int,
+                        num_seqs: int, H: int, KV: int, hs: int, scale: float, window: int = 0,
+                        status=None) -> None:
+    """Plain fp32-arithmetic attention over the paged cache; q may be a strided row view."""
+    _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    T = q.shape[0]
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * hs and out.shape[1] == H * hs,
+          "paged_attention_ref: q/out shape")
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "paged_attention_ref: dtypes differ")
+    _need(tuple(k_cache.shape[1:]) == (KV, page_size, hs) and k_cache.is_contiguous()
+          and v_cache.is_contiguous(), "paged_attention_ref: cache must be [pages, KV, page_size, hs]")
+    f = _fn("attention_ref", "si_paged_attention_ref",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p])
+    _check(f(_ptr(q), _dt(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(row_seq), _ptr(positions), _ptr(out), out.stride(0),
+             k_cache.shape[0], page_size, T, num_seqs, H, KV, hs, float(scale), int(window or 0),
+             _ptr(status), _stream()), f"paged_attention_ref(head_dim={hs})")
+
+
+def swiglu(gu, out) -> None:
+    """out[t,f] = silu(gu[t,f]) * gu[t,F+f]."""
+    _cuda(gu, out)
+    T, F = out.shape
+    _need(gu.shape == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous()
+          and gu.dtype == out.dtype, "swiglu: gu must be [T, 2F] like out [T, F]")
+    f = _fn("swiglu", "si_swiglu", [_c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(gu), _ptr(out), _dt(out), T, F, _stream()), "swiglu")
+
+
+def gemm_f32(a, w, out) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T in true fp32 (FFMA)."""
+    _cuda(a, w, out)
+    _need(a.dtype == w.dtype == out.dtype == torch.float32, "gemm_f32: fp32 tensors only")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1
+          and out.stride(1) == 1, "gemm_f32: shapes/strides")
+    f = _fn("gemm_f32", "si_gemm_f32",
+            [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
+             _stream()), f"gemm_f32(M={M}, N={N}, K={K})")
+
+
+def sample(logits, out, temperature=None, top_k=None, top_p=None, seed=None, counter=None) -> None:
+    """Pick one token per row of fp32 logits; all per-row parameter tensors are optional
+    (absent temperature means greedy)."""
+    _cuda(logits, out, temperature, top_k, top_p, seed, counter)
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: logits must be fp32 rows")
+    _i32(out, "out"); _i32(top_k, "top_k")
+    R, V = logits.shape
+    for t, dt, nm in ((temperature, torch.float32, "temperature"), (top_p, torch.float32, "top_p"),
+                      (seed, torch.int64, "seed"), (counter, torch.int64, "counter")):
+        if t is not None:
+            _need(t.dtype == dt and t.numel() == R and t.is_contiguous(), f"sample: {nm} must be {dt} [rows]")
+    f = _fn("sampling", "si_sample",
+            [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p])
+    _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+             _ptr(seed), _ptr(counter), _ptr(out), _stream()), "sample")

@@ -1,0 +1,2 @@
+from . import llama  # noqa: F401  (registers "LlamaForCausalLM")
+from .model import Model
