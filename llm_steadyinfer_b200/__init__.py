@@ -6,3 +6,6 @@ sampling, and hand-written sm_100a kernels with a bfloat16 and a true float32 pa
 from . import models as _models  # noqa: F401  (registers the architectures)
 
 __version__ = "0.1.0"
+
+from .engine import LLM, GenerationResult  # noqa: E402
+from .sampling import SamplingParams  # noqa: E402

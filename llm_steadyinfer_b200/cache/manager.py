@@ -205,7 +205,7 @@ class CacheManager:
         """Cut the request back to ``keep_length`` tokens (rounded down as
         ``can_truncate_to`` says) and give the pages behind it back. Returns the new length."""
         rc = self.requests[req]
-        keep = min(self.can_truncate_to(keep_length), rc.length)
+        keep = min(self.can_truncate_to(keep_length), rc.length // self.page_size * self.page_size)
         nb = keep // self.page_size
         for g in self.groups:
             t = g.tables[req]

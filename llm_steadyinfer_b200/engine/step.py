@@ -176,9 +176,9 @@ class ModelRunner:
         S = len(entries)
         R = sum(len(e.want) for e in entries)
         S_cap = seq_cap or S
-        W = max(1, max(mgr.blocks_for(n) for n in self._new_lengths))
-        W_cap = width_cap or W
         G = len(mgr.groups)
+        W = max([1] + [len(mgr.table(g, e.req)) for g in range(G) for e in entries])   # pages may be reserved ahead
+        W_cap = width_cap or W
         # layout (ints): tokens T | positions T | row_seq T | logit_rows R | q_start S+1 | ctx_len S | slots S | tables G*S*W
         offs = {}
         o = 0
@@ -236,6 +236,9 @@ class ModelRunner:
         dtabs = dev[table_off:table_off + G * S_cap * W_cap].view(G, S_cap, W_cap)
         self._tables = [dtabs[g] for g in range(G)]
         return ctx
+
+    def graphs_available(self) -> bool:
+        return False
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel reported a fault (it never traps)."""

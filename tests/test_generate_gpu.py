@@ -1,0 +1,113 @@
+"""Generation through the Python entry point against the plain implementation: greedy and
+seeded temperature/top-p sampling, alone and batched, with page pressure and prefix reuse."""
+import pytest
+import torch
+
+import plain_llama
+import replay_util as ru
+from tiny_configs import CONFIGS, make_model_folder
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {n: make_model_folder(root, n) for n in CONFIGS}
+
+
+def prompts_of(name, lengths):
+    cfg, seed, _ = CONFIGS[name]
+    return [ru.random_tokens(cfg["vocab_size"], n, 500 + 10 * seed + i) for i, n in enumerate(lengths)]
+
+
+def plain_generate(folder, prompts, n_new, **kw):
+    cfg, w = plain_llama.read_model_folder(folder)
+    seeds = kw.pop("seeds", [0] * len(prompts))
+    return [plain_llama.generate(cfg, w, p, n_new, seed=s, **kw) for p, s in zip(prompts, seeds)]
+
+
+def test_greedy_matches_plain_config_a(folders):
+    """Config A's workload: 4 requests, prompts 1/7/33/64, greedy, 16 tokens each, page size 16."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("A", [1, 7, 33, 64])
+    want = plain_generate(folders["A"], prompts, 16)
+    llm = LLM(folders["A"], dtype="float32", max_batch=4, max_seq_len=128, max_gen_len=16, block_size=16)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [g.token_ids for g in got] == want
+    assert all(g.finish_reason == "length" for g in got)
+    llm.runner.manager.check_invariant()
+    assert not llm.runner.manager.requests
+
+
+def test_sampled_matches_plain_config_b(folders):
+    """Config B's workload: 6 requests, budget 48 tokens mixed with decodes, temperature 0.7,
+    top-p 0.9, 24 tokens, per-request seeds, page size 8."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("B", [3, 17, 50, 100, 129, 200])
+    seeds = [11, 22, 33, 44, 55, 66]
+    want = plain_generate(folders["B"], prompts, 24, temperature=0.7, top_p=0.9, seeds=seeds)
+    llm = LLM(folders["B"], dtype="float32", max_batch=6, max_seq_len=256, max_gen_len=24, block_size=8,
+              max_num_batched_tokens=48)
+    params = [SamplingParams(temperature=0.7, top_p=0.9, seed=s, ignore_eos=True) for s in seeds]
+    got = llm.generate(prompts, params)
+    assert [g.token_ids for g in got] == want
+    assert llm.stats["steps"] > 24, "prompts were cut into portions"
+
+
+def test_greedy_bf16_follows_plain(folders):
+    """bf16 greedy tokens equal the plain ones as long as the plain top-2 logits are further
+    apart than the bf16 error bound; compared up to the first near-tie."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    cfg, w = plain_llama.read_model_folder(folders["A"])
+    prompts = prompts_of("A", [9, 40])
+    llm = LLM(folders["A"], dtype="bfloat16", max_batch=2, max_seq_len=128, max_gen_len=12, block_size=16)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    for p, g in zip(prompts, got):
+        toks = list(p)
+        for t in g.token_ids:
+            lg = plain_llama.forward(cfg, w, toks)[-1]
+            top2 = torch.topk(lg, 2).values
+            if (top2[0] - top2[1]).item() < 2e-2:
+                break
+            assert t == int(torch.argmax(lg))
+            toks.append(t)
+
+
+def test_preemption_keeps_tokens_equal(folders):
+    """So few pages that running requests are preempted and recomputed: the tokens are those
+    of an unconstrained run."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("B", [30, 41, 52, 25])
+    want = plain_generate(folders["B"], prompts, 40)
+    # 4 requests grow to 70..92 tokens = 9..12 pages each; 30 pages cannot hold them all
+    llm = LLM(folders["B"], dtype="float32", max_batch=4, max_seq_len=128, max_gen_len=40, block_size=8,
+              num_blocks=30, enable_prefix_cache=False)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [g.token_ids for g in got] == want
+    assert llm.scheduler.num_preemptions > 0
+    llm.runner.manager.check_invariant()
+
+
+def test_prefix_reuse_keeps_tokens_equal(folders):
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    cfg = CONFIGS["A"][0]
+    shared = ru.random_tokens(cfg["vocab_size"], 48, 900)
+    prompts = [shared + ru.random_tokens(cfg["vocab_size"], n, 901 + n) for n in (5, 9, 20)]
+    want = plain_generate(folders["A"], prompts, 8)
+    llm = LLM(folders["A"], dtype="float32", max_batch=1, max_seq_len=128, max_gen_len=8, block_size=16)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [g.token_ids for g in got] == want
+    assert [g.prefix_hit_tokens for g in got] == [0, 48, 48]
+    llm.runner.manager.check_invariant()
+
+
+def test_eos_stops(folders):
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("A", [12])
+    free_run = plain_generate(folders["A"], prompts, 10)[0]
+    stop_at = free_run[4]
+    llm = LLM(folders["A"], dtype="float32", max_batch=1, max_seq_len=64, max_gen_len=10)
+    got = llm.generate(prompts, SamplingParams(stop_token_ids=(stop_at,), ignore_eos=True))[0]
+    assert got.token_ids == free_run[:free_run.index(stop_at) + 1]
+    assert got.finish_reason == "eos"

@@ -1,0 +1,223 @@
+"""Each kernel alone against a plain fp32 reference of the same op, at sizes other than the
+engine tests': widths and vocabularies that are no power of two, odd head counts, head sizes in
+steps of 16, pages of several sizes."""
+import math
+
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from llm_steadyinfer_b200.csrc import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,d,T", [(1000, 96, 7), (4099, 1336, 33)])
+def test_embedding(dtype, V, d, T):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, d, generator=g).to(dtype).to(DEV)
+    tok = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(T, d, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embedding_gather(tok, table, out, status)
+    assert torch.equal(out, table[tok.long()].float())
+    assert status.item() == 0
+    tok[T // 2] = V                                  # outside the vocabulary: flagged, row zeroed
+    ops().embedding_gather(tok, table, out, status)
+    assert status.item() == 1 and out[T // 2].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("xdtype,wdtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                           (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("d,T,eps", [(96, 5, 1e-6), (1336, 19, 1e-5), (5120, 3, 1e-5)])
+def test_add_rmsnorm(xdtype, wdtype, d, T, eps):
+    g = torch.Generator().manual_seed(1)
+    resid = torch.randn(T, d, generator=g).to(DEV)
+    delta = torch.randn(T, d, generator=g).to(xdtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(d, generator=g)).to(wdtype).to(DEV)
+    h = resid.double() + delta.double()
+    want = plain_llama.rmsnorm(h.cpu(), w.double().cpu(), eps)
+    r2 = resid.clone()
+    out = torch.empty(T, d, dtype=xdtype, device=DEV)
+    ops().add_rmsnorm(r2, delta, w, eps, out)
+    assert torch.allclose(r2.double(), h, atol=1e-6)
+    tol = 1e-5 if xdtype == torch.float32 else 2 ** -8 * want.abs().max().item()
+    assert (out.double().cpu() - want).abs().max().item() <= tol
+    # rows: only the listed rows, stream untouched
+    rows = torch.tensor([T - 1, 0, T - 1], dtype=torch.int32, device=DEV)
+    r3 = resid.clone()
+    out2 = torch.empty(3, d, dtype=xdtype, device=DEV)
+    ops().add_rmsnorm(r3, delta, w, eps, out2, rows=rows)
+    assert torch.equal(r3, resid)
+    assert torch.equal(out2, out[rows.long()])
+    # without delta
+    out3 = torch.empty(T, d, dtype=xdtype, device=DEV)
+    ops().add_rmsnorm(r3, None, w, eps, out3)
+    want3 = plain_llama.rmsnorm(resid.double().cpu(), w.double().cpu(), eps)
+    assert (out3.double().cpu() - want3).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,F", [(3, 320), (17, 1336)])
+def test_swiglu(dtype, T, F):
+    g = torch.Generator().manual_seed(2)
+    gu = (3 * torch.randn(T, 2 * F, generator=g)).to(dtype).to(DEV)
+    out = torch.empty(T, F, dtype=dtype, device=DEV)
+    ops().swiglu(gu, out)
+    want = plain_llama.swiglu(gu[:, :F].double().cpu(), gu[:, F:].double().cpu())
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -8 * want.abs().max().item()
+    assert (out.double().cpu() - want).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (7, 513, 320), (130, 200, 1336), (64, 64, 16), (3, 5, 7)])
+def test_gemm_f32(M, N, K):
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(M, K, generator=g).to(DEV)
+    w = torch.randn(N, K, generator=g).to(DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_f32(a, w, out)
+    want = a.double() @ w.double().T
+    assert (out.double() - want).abs().max().item() <= 1e-6 * K * 4
+    # a row's result does not depend on the other rows of the call
+    one = torch.empty(1, N, device=DEV)
+    ops().gemm_f32(a[M - 1:M], w, one)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def build_cache(dtype, lengths, H, KV, hs, page_size, seed, shuffle=True):
+    """Random q/k/v of several whole sequences laid into a paged cache with shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lengths)
+    blocks = [-(-n // page_size) for n in lengths]
+    num_pages = sum(blocks) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist() if shuffle else list(range(num_pages))
+    W = max(blocks)
+    table = torch.full((S, W), -1, dtype=torch.int32)
+    kc = torch.zeros(num_pages, KV, page_size, hs)
+    vc = torch.zeros(num_pages, KV, page_size, hs)
+    seqs = []
+    p = 0
+    for s, n in enumerate(lengths):
+        q = torch.randn(n, H, hs, generator=g).to(dtype).float()
+        k = torch.randn(n, KV, hs, generator=g).to(dtype).float()
+        v = torch.randn(n, KV, hs, generator=g).to(dtype).float()
+        for b in range(blocks[s]):
+            page = perm[p]; p += 1
+            table[s, b] = page
+            m = min(page_size, n - b * page_size)
+            kc[page, :, :m] = k[b * page_size:b * page_size + m].transpose(0, 1)
+            vc[page, :, :m] = v[b * page_size:b * page_size + m].transpose(0, 1)
+        seqs.append((q, k, v))
+    return seqs, table, kc.to(dtype), vc.to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,hs,page_size,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, None),
+                                                     (8, 2, 128, 16, None), (5, 5, 80, 32, 7), (2, 1, 256, 16, 40)])
+def test_paged_attention_ref(dtype, H, KV, hs, page_size, window):
+    lengths = [1, 37, 130]
+    seqs, table, kc, vc = build_cache(dtype, lengths, H, KV, hs, page_size, seed=4)
+    scale = 1.0 / math.sqrt(hs)
+    # rows: the last 5 positions of each sequence (a portion that continues from the cache)
+    qrows, pos, rseq, want = [], [], [], []
+    for s, (q, k, v) in enumerate(seqs):
+        full = plain_llama.attention(q.double(), k.double(), v.double(), scale, window)
+        for t in range(max(0, lengths[s] - 5), lengths[s]):
+            qrows.append(q[t].reshape(-1)); pos.append(t); rseq.append(s); want.append(full[t].reshape(-1))
+    q = torch.stack(qrows).to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().paged_attention_ref(q, kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor(rseq, dtype=torch.int32, device=DEV),
+                              torch.tensor(pos, dtype=torch.int32, device=DEV), out, page_size, len(lengths),
+                              H, KV, hs, scale, window or 0, status)
+    assert status.item() == 0
+    tol = 2e-6 if dtype == torch.float32 else 2 ** -8
+    assert (out.double().cpu() - torch.stack(want)).abs().max().item() <= tol * 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,hs,rot,page_size", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 80, 40, 4), (8, 2, 128, 128, 16)])
+def test_rope_kv_write(dtype, H, KV, hs, rot, page_size):
+    g = torch.Generator().manual_seed(5)
+    lengths = [9, 40]
+    T = sum(lengths)
+    qkv = torch.randn(T, (H + 2 * KV) * hs, generator=g).to(dtype)
+    pos = torch.cat([torch.arange(100, 100 + n) for n in lengths]).to(torch.int32)     # far positions
+    rseq = torch.cat([torch.full((n,), s) for s, n in enumerate(lengths)]).to(torch.int32)
+    W = (100 + max(lengths)) // page_size + 1
+    num_pages = 2 * W
+    table = torch.randperm(num_pages, generator=g).to(torch.int32).view(2, W)
+    freqs = plain_llama.rope_frequencies(rot, 500000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                         "high_freq_factor": 4.0, "original_max_position_embeddings": 64})
+    kc = torch.zeros(num_pages, KV, page_size, hs, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    dq = qkv.clone().to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().rope_kv_write(dq, pos.to(DEV), rseq.to(DEV), freqs.to(DEV), rot, table.to(DEV), kc, vc, page_size, 2,
+                        H, KV, hs, status)
+    assert status.item() == 0
+    x = qkv.double()
+    q3 = x[:, :H * hs].view(T, H, hs); k3 = x[:, H * hs:(H + KV) * hs].view(T, KV, hs); v3 = x[:, (H + KV) * hs:].view(T, KV, hs)
+    def rot_part(t3):
+        r = plain_llama.rope(t3[..., :rot], pos, freqs)
+        return torch.cat([r, t3[..., rot:]], -1)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -8 * 5
+    wq, wk = rot_part(q3), rot_part(k3)
+    assert (dq[:, :H * hs].double().cpu().view(T, H, hs) - wq).abs().max().item() <= tol
+    kc, vc = kc.double().cpu(), vc.double().cpu()
+    for t in range(T):
+        page = table[rseq[t], pos[t] // page_size].item()
+        off = pos[t].item() % page_size
+        assert (kc[page, :, off] - wk[t]).abs().max().item() <= tol
+        assert torch.equal(vc[page, :, off], v3[t])
+
+
+def test_sampling_kernel_matches_plain():
+    g = torch.Generator().manual_seed(6)
+    V, R = 1000, 24
+    logits = (2.5 * torch.randn(R, V, generator=g)).float()
+    logits[3, 17] = logits[3, 400] = logits[3].max() + 1          # a tie: the lowest index wins
+    dl = logits.to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops().sample(dl, out)
+    assert out.tolist() == [plain_llama.sample(logits[r]) for r in range(R)]
+    assert out[3].item() == 17
+    cases = [(0.7, 0, 0.9), (1.0, 5, 1.0), (1.3, 50, 0.5), (0.5, 0, 1.0), (1.0, 1, 1.0), (2.0, 0, 0.1)]
+    for temp, k, p in cases:
+        t = torch.full((R,), temp, device=DEV)
+        tk = torch.full((R,), k, dtype=torch.int32, device=DEV)
+        tp = torch.full((R,), p, device=DEV)
+        seed = torch.arange(R, dtype=torch.int64, device=DEV) * 7919 + 1
+        ctr = torch.arange(R, dtype=torch.int64, device=DEV) % 5
+        ops().sample(dl, out, temperature=t, top_k=tk, top_p=tp, seed=seed, counter=ctr)
+        want = [plain_llama.sample(logits[r], temp, k, p, seed=int(seed[r]), counter=int(ctr[r])) for r in range(R)]
+        assert out.tolist() == want, (temp, k, p)
+
+
+def test_sampling_distribution():
+    """Draws over many counters follow softmax(x / T) restricted by top-p."""
+    V = 37
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(V, generator=g).float()
+    R = 4096
+    dl = x.to(DEV).repeat(R, 1)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    t = torch.full((R,), 0.8, device=DEV)
+    tp = torch.full((R,), 0.9, device=DEV)
+    seed = torch.full((R,), 1234, dtype=torch.int64, device=DEV)
+    ctr = torch.arange(R, dtype=torch.int64, device=DEV)
+    ops().sample(dl, out, temperature=t, top_p=tp, seed=seed, counter=ctr)
+    p = torch.softmax(x.double() / 0.8, 0)
+    order = torch.argsort(p, descending=True)
+    csum = torch.cumsum(p[order], 0)
+    kept = order[: int((csum < 0.9).sum()) + 1]
+    pk = torch.zeros(V, dtype=torch.double); pk[kept] = p[kept] / p[kept].sum()
+    freq = torch.bincount(out.cpu().long(), minlength=V).double() / R
+    assert freq[pk == 0].sum().item() == 0
+    assert (freq - pk).abs().max().item() < 4 * math.sqrt(0.25 / R)
