@@ -1,0 +1,185 @@
+"""The scheduler's decisions, on the host with a stand-in for the model: admission order, the
+token budget, portions, decode rows, preemption when pages run out, finishing and freeing."""
+import pytest
+
+from llm_steadyinfer_b200.cache import CacheLayout, CacheManager
+from llm_steadyinfer_b200.engine.scheduler import RequestRejected, Scheduler, SeqState
+from llm_steadyinfer_b200.parts.base import CacheNeed
+from llm_steadyinfer_b200.sampling import SamplingParams
+
+
+def make(num_pages=64, page_size=4, max_seqs=4, budget=16, max_len=256, max_gen=8, prefix=False, eos=()):
+    cache = CacheManager(CacheLayout([CacheNeed(1, 8, None)], [None]), page_size, num_pages, max_seqs, prefix)
+    return Scheduler(cache, max_seqs, max_len, max_gen, token_budget=budget, eos_token_ids=eos), cache
+
+
+def run_step(s, cache, next_token=lambda seq: 100 + len(seq.outputs)):
+    """What the engine does around the model: commit the lengths, hand back one token per wanted row."""
+    items = s.schedule()
+    for it in items:
+        assert cache.length(it.seq.id) == it.start, "a portion starts where the cache ends"
+        assert cache.blocks_for(it.start + it.count) <= len(cache.table(0, it.seq.id)), "pages are there"
+        cache.commit(it.seq.id, it.start + it.count)
+    sampled = {it.seq.id: next_token(it.seq) for it in items if it.want_logits}
+    s.update(items, sampled)
+    cache.check_invariant()
+    return items
+
+
+def test_portions_under_the_budget_and_decode_rows_first():
+    s, cache = make(budget=16)
+    a = s.add_request(list(range(40)))
+    b = s.add_request(list(range(5)))
+    it = run_step(s, cache)
+    assert [(i.seq.id, i.start, i.count, i.want_logits) for i in it] == [(a, 0, 16, False)]
+    it = run_step(s, cache)
+    assert [(i.seq.id, i.start, i.count) for i in it] == [(a, 16, 16)]
+    it = run_step(s, cache)                                   # a's last 8, then 5 of b fill the budget
+    assert [(i.seq.id, i.start, i.count, i.want_logits) for i in it] == [(a, 32, 8, True), (b, 0, 5, True)]
+    it = run_step(s, cache)                                   # both decode now
+    assert [(i.seq.id, i.start, i.count, i.want_logits) for i in it] == [(a, 40, 1, True), (b, 5, 1, True)]
+    c = s.add_request(list(range(30)))
+    it = run_step(s, cache)                                   # decode rows first, then the new prompt
+    assert [(i.seq.id, i.count) for i in it] == [(a, 1), (b, 1), (c, 16)]
+
+
+def test_finishing_frees_and_reasons():
+    s, cache = make(max_gen=3, eos=[7])
+    a = s.add_request([1, 2, 3])
+    b = s.add_request([4, 5], SamplingParams(max_tokens=10))
+    c = s.add_request([6], SamplingParams(max_tokens=10, ignore_eos=True, stop_token_ids=(9,)))
+    toks = {a: [11, 12, 13, 14], b: [21, 7, 22], c: [7, 8, 9, 10]}
+    while s.has_unfinished():
+        run_step(s, cache, lambda seq: toks[seq.id][len(seq.outputs)])
+    fin = {q.id: q for q in s.finished}
+    assert fin[a].outputs == [11, 12, 13] and fin[a].finish_reason == "length"
+    assert fin[b].outputs == [21, 7] and fin[b].finish_reason == "eos"
+    assert fin[c].outputs == [7, 8, 9] and fin[c].finish_reason == "eos"
+    assert cache.free_pages() == 64 and not cache.requests
+
+
+def test_rejections_and_max_gen_clamp():
+    s, cache = make(max_len=16, num_pages=3, max_gen=100)
+    with pytest.raises(RequestRejected):
+        s.add_request([])
+    with pytest.raises(RequestRejected):
+        s.add_request(list(range(16)))                        # no room to generate
+    with pytest.raises(RequestRejected):
+        s.add_request(list(range(12)))                        # 13 tokens do not fit 3 pages of 4
+    s.add_request(list(range(10)))
+    assert s.waiting[0].max_gen == 6                          # clamped to max_len - prompt
+
+
+def test_admission_is_fcfs_and_waits_for_pages_and_slots():
+    s, cache = make(num_pages=10, max_seqs=2, budget=64, max_gen=2)
+    a = s.add_request(list(range(20)))                        # 5 pages
+    b = s.add_request(list(range(24)))                        # 6 pages: does not fit beside a
+    c = s.add_request(list(range(4)))                         # would fit, but b is first in line
+    it = run_step(s, cache)
+    assert [i.seq.id for i in it] == [a] and [q.id for q in s.waiting] == [b, c]
+    while any(q.id == a for q in s.running):
+        run_step(s, cache)
+    it = run_step(s, cache)
+    assert {i.seq.id for i in it} == {b, c}
+    d = s.add_request([1])
+    run_step(s, cache)
+    assert [q.id for q in s.waiting] == [d], "two are running: the third waits for a slot"
+
+
+def test_decode_growth_preempts_the_newest_and_it_recomputes():
+    s, cache = make(num_pages=6, page_size=4, max_seqs=3, budget=64, max_gen=12)
+    a = s.add_request(list(range(7)))                         # 2 pages
+    b = s.add_request(list(range(6)))                         # 2 pages
+    c = s.add_request(list(range(5)))                         # 2 pages: the pool is full
+    run_step(s, cache)                                        # prompts, first tokens: 8, 7, 6 tokens known
+    assert cache.free_pages() == 0
+    it = run_step(s, cache)                                   # a writes position 7: still page 2
+    assert [i.seq.id for i in it] == [a, b, c]
+    it = run_step(s, cache)                                   # a needs a third page: c, the newest, gives one
+    seqs = {q.id: q for q in list(s.running) + list(s.waiting)}
+    assert seqs[c].state is SeqState.PREEMPTED and s.waiting[0].id == c
+    assert [i.seq.id for i in it] == [a, b]
+    assert seqs[c].num_computed == 4 and cache.length(c) == 4 and len(cache.table(0, c)) == 1
+    assert seqs[c].outputs == [100, 101], "generated tokens are kept"
+    n_before = s.num_preemptions
+    while s.has_unfinished():
+        run_step(s, cache)
+    fin = {q.id: q for q in s.finished}
+    assert all(fin[r].finish_reason == "length" and len(fin[r].outputs) == 12 for r in (a, b, c))
+    assert fin[c].num_preemptions >= 1 and s.num_preemptions >= n_before
+    assert cache.free_pages() == 6
+
+
+def test_recompute_after_preemption_runs_known_tokens_as_a_portion():
+    s, cache = make(num_pages=4, page_size=4, max_seqs=2, budget=64, max_gen=6)
+    a = s.add_request(list(range(6)))
+    b = s.add_request(list(range(6)))
+    for _ in range(3):
+        run_step(s, cache)                                    # both hold 2 pages, 8 tokens known each
+    it = run_step(s, cache)                                   # a needs page 3 -> b preempted (keeps 1 page)
+    assert [i.seq.id for i in it] == [a]
+    bq = s.waiting[0]
+    assert bq.id == b and bq.num_computed == 4
+    while any(q.id == a for q in s.running):
+        run_step(s, cache)
+    it = run_step(s, cache)                                   # b comes back: recomputes 4..end in one portion
+    assert [(i.seq.id, i.start, i.want_logits) for i in it] == [(b, 4, True)]
+    assert it[0].count == len(bq.prompt) + len(bq.outputs) - 1 - 4, "all known tokens but the newest were stored before"
+    while s.has_unfinished():
+        run_step(s, cache)
+    assert cache.free_pages() == 4
+
+
+def test_alone_and_too_large_is_aborted_not_hung():
+    s, cache = make(num_pages=2, page_size=4, max_seqs=2, budget=64, max_gen=50)
+    a = s.add_request(list(range(5)))
+    steps = 0
+    while s.has_unfinished():
+        run_step(s, cache)
+        steps += 1
+        assert steps < 20
+    assert s.finished[0].finish_reason == "aborted" and len(s.finished[0].outputs) == 4   # 5 + 4 = 9 > 8 slots
+    assert cache.free_pages() == 2
+
+
+def test_newest_waits_for_older_ones_instead_of_cutting_them():
+    s, cache = make(num_pages=5, page_size=4, max_seqs=2, budget=64, max_gen=6)
+    a = s.add_request(list(range(11)))                        # 3 pages, room for 12 tokens
+    b = s.add_request(list(range(6)))                         # 2 pages, room for 8
+    run_step(s, cache); run_step(s, cache)                    # a: 13 known? no: a has 12 known -> needs page at 13
+    while s.has_unfinished():
+        run_step(s, cache)
+    fin = {q.id: q for q in s.finished}
+    assert len(fin[a].outputs) == 6 and len(fin[b].outputs) == 6
+    assert fin[a].num_preemptions == 0, "the older request is never cut for the newer one"
+
+
+def test_adaptive_budget_moves_one_doubling_per_step():
+    s, cache = make(num_pages=4096, page_size=16, max_seqs=8, budget="adaptive", max_len=20000, max_gen=4)
+    assert s.token_budget == 1024
+    s.add_request(list(range(9000)))
+    counts = []
+    for _ in range(4):
+        counts.append(run_step(s, cache)[0].count)
+    assert counts == [2048, 4096, 2856][:len(counts)] or counts[:2] == [2048, 4096]
+    for i in range(6):
+        s.add_request(list(range(3)))
+    s.add_request(list(range(9000)))
+    for _ in range(3):
+        run_step(s, cache)
+    assert s.token_budget <= 2048, "decode pressure above a half shrinks the budget"
+
+
+def test_prefix_hits_skip_computed_pages():
+    s, cache = make(num_pages=32, page_size=4, max_seqs=1, budget=64, max_gen=2, prefix=True)
+    shared = list(range(50, 62))
+    a = s.add_request(shared + [1, 2, 3])
+    while s.has_unfinished():
+        run_step(s, cache)
+    b = s.add_request(shared + [9])
+    it = run_step(s, cache)
+    assert [(i.start, i.count, i.want_logits) for i in it] == [(12, 1, True)]
+    assert it[0].seq.prefix_hit_tokens == 12
+    while s.has_unfinished():
+        run_step(s, cache)
+    cache.check_invariant()
