@@ -205,3 +205,76 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, seed=None, cou
             [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p])
     _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
              _ptr(seed), _ptr(counter), _ptr(out), _stream()), "sample")
+
+
+# ---- tensor-core attention (bf16) ---------------------------------------------------------
+
+_c_llr = ctypes.c_longlong
+
+
+def attn_portion_tokens(H: int, KV: int, hs: int) -> int:
+    """Most tokens of one item of the portion kernel (0: this head layout is not supported)."""
+    lib = build.load("attention_mma")
+    lib.si_attn_portion_tokens.restype = _c_int
+    return lib.si_attn_portion_tokens(_c_int(H), _c_int(KV), _c_int(hs))
+
+
+def attn_decode_rows(H: int, KV: int, hs: int) -> int:
+    """Rows (tokens * heads per kv head) one item of the decode kernel may have; 0: none."""
+    lib = build.load("attention_mma")
+    lib.si_attn_decode_rows.restype = _c_int
+    return lib.si_attn_decode_rows(_c_int(H), _c_int(KV), _c_int(hs))
+
+
+def attn_decode_scratch_floats(num_items: int, H: int, KV: int, hs: int, nsplit: int) -> int:
+    lib = build.load("attention_mma")
+    lib.si_attn_decode_scratch_floats.restype = _c_llr
+    return lib.si_attn_decode_scratch_floats(_c_int(num_items), _c_int(H), _c_int(KV), _c_int(hs), _c_int(nsplit))
+
+
+def _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, what):
+    _cuda(q, k_cache, v_cache, block_table, items, out)
+    _i32(block_table, "block_table"); _i32(items, "items")
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+          and v_cache.dtype == torch.bfloat16, f"{what}: bfloat16 tensors only")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * hs and out.shape[1] == H * hs,
+          f"{what}: q/out must be [T, H*hs] rows")
+    _need(tuple(k_cache.shape[1:]) == (KV, page_size, hs) and k_cache.is_contiguous() and v_cache.is_contiguous(),
+          f"{what}: cache must be [pages, KV, page_size, hs]")
+    _need(items.dim() == 2 and items.shape[1] == 4, f"{what}: items must be int32 [n, 4]")
+    _need(q.data_ptr() % 16 == 0 and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0,
+          f"{what}: q and cache must be 16-byte aligned")
+
+
+def attn_portion(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int,
+                 KV: int, hs: int, scale: float, window: int = 0, status=None) -> None:
+    """Tensor-core attention for prompt portions. ``items``: int32 [n, 4] rows
+    (sequence, first row, tokens, first position), at most ``attn_portion_tokens`` tokens each."""
+    _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_portion")
+    f = _fn("attention_mma", "si_attn_portion",
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_f, _c_int, _c_p, _c_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(items), items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs,
+             H, KV, hs, float(scale), int(window or 0), _ptr(status), _stream()),
+           f"attn_portion(heads={H}, kv_heads={KV}, head_dim={hs})")
+
+
+def attn_decode(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int,
+                hs: int, scale: float, window: int = 0, nsplit: int = 1, scratch=None, status=None) -> None:
+    """Tensor-core attention for decode rows and short portions (at most
+    ``attn_decode_rows // (H // KV)`` tokens an item). With ``nsplit`` > 1 the key range is split
+    over blocks and ``scratch`` (fp32, ``attn_decode_scratch_floats`` elements) holds the partials."""
+    _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_decode")
+    if nsplit > 1:
+        _cuda(scratch)
+        need = attn_decode_scratch_floats(items.shape[0], H, KV, hs, nsplit)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need,
+              f"attn_decode: scratch must hold {need} floats")
+    f = _fn("attention_mma", "si_attn_decode",
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(items), items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs,
+             H, KV, hs, float(scale), int(window or 0), int(nsplit), _ptr(scratch), _ptr(status), _stream()),
+           f"attn_decode(heads={H}, kv_heads={KV}, head_dim={hs})")

@@ -54,11 +54,16 @@ class StepContext:
         self.q_start = self.ctx_len = self.slots = self.logit_rows = None
         # host copies
         self.h_positions = self.h_q_start = self.h_ctx_len = self.h_slots = None
-        self.graph_safe = False        # True while a fixed-shape decode step is being captured/replayed
+        self.seq_cap: Optional[int] = None   # set for fixed-shape decode steps (graphs): sequences the shapes are for
 
     def buf(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """A scratch tensor that lives until the same key is asked for again."""
         return self._runner.workspace(key, shape, dtype)
+
+    def upload_ints(self, key: str, values: np.ndarray, capacity: Optional[int] = None) -> torch.Tensor:
+        """Copy a small int32 array to a device buffer that keeps its address from step to step
+        (parts send their per-step work lists through this from ``prepare``)."""
+        return self._runner.upload_ints(key, values, capacity)
 
 
 class ModelRunner:
@@ -86,6 +91,7 @@ class ModelRunner:
         self._copied: List[Optional[torch.cuda.Event]] = []
         self._ring = 0
         self._dev = None
+        self._uploads: Dict[str, dict] = {}
         self.ctx = StepContext(self)
 
     # ---- scratch -----------------------------------------------------------------------
@@ -101,6 +107,32 @@ class ModelRunner:
             t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._scratch[k] = t
         return t[:n].view(*shape)
+
+    def upload_ints(self, key: str, values: np.ndarray, capacity: Optional[int] = None) -> torch.Tensor:
+        values = np.ascontiguousarray(values, dtype=np.int32).reshape(-1)
+        n = values.size
+        cap = max(capacity or 0, n, 4)
+        ent = self._uploads.get(key)
+        if ent is None or ent["cap"] < cap:
+            if torch.cuda.is_current_stream_capturing():
+                raise StepError(f"upload buffer {key!r} would have to grow during graph capture")
+            cap = max(cap, 2 * (ent["cap"] if ent else 0))
+            ent = {"cap": cap, "ring": 0, "events": [None] * 4,
+                   "hosts": [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)],
+                   "dev": torch.empty(cap, dtype=torch.int32, device=self.device)}
+            self._uploads[key] = ent
+        ent["ring"] = (ent["ring"] + 1) % 4
+        ev = ent["events"][ent["ring"]]
+        if ev is not None:
+            ev.synchronize()
+        host = ent["hosts"][ent["ring"]]
+        host.numpy()[:n] = values
+        if n:
+            ent["dev"][:n].copy_(host[:n], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            ent["events"][ent["ring"]] = ev
+        return ent["dev"][:n]
 
     def _staging(self, n_ints: int):
         """A pinned host buffer whose last copy has finished, and the device buffer."""
@@ -132,6 +164,7 @@ class ModelRunner:
         ctx = self._prepare(entries)
         self.storage.zero_new_slots()
         caches = self.storage.layer_views(self._tables)
+        self.model.prepare(ctx, caches)
         logits = self.model.forward(ctx, caches)
         for e, new_len in zip(entries, self._new_lengths):
             self.manager.commit(e.req, new_len)

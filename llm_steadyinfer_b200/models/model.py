@@ -83,6 +83,12 @@ class Model:
             part.load_weights({n: tensors[prefix + n] for n in part.weight_shapes()})
 
     # ---- forward -------------------------------------------------------------------
+    def prepare(self, ctx, caches) -> None:
+        """Host-side planning of the parts for this step (work lists, uploads); runs before
+        ``forward`` and also before a captured step is replayed."""
+        for i in sorted(set(self.spec.order)):
+            self.blocks[i].mixer.prepare(ctx, caches[i])
+
     def forward(self, ctx, caches) -> Optional[torch.Tensor]:
         """Run the step's rows through all layers; returns fp32 logits [R, vocab] for
         ``ctx.logit_rows`` or None when no row is wanted. ``caches[i]`` is layer i's view."""

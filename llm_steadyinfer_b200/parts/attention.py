@@ -8,11 +8,18 @@ positions up to the row's own (llama3.cpp:1048-1067); output projection (llama3.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..csrc import ops
 from .base import CacheNeed, Mixer, register_mixer
 from .linear import linear
+
+
+USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
+TARGET_BLOCKS = 2 * 148      # blocks wanted in flight for decode attention
+MAX_SPLITS = 32
+MIN_TILES_PER_SPLIT = 2      # a split covers at least this many 64-key tiles
 
 
 class Attention(Mixer):
@@ -65,10 +72,69 @@ class Attention(Mixer):
         linear(attn, self.o, out)
         return out
 
+    # ---- kernels ---------------------------------------------------------------------
+    def uses_tensor_cores(self) -> bool:
+        return self.dtype == torch.bfloat16 and USE_TENSOR_CORES and self.hs % 16 == 0
+
+    def prepare(self, ctx, cache):
+        """Cut the step's sequences into work items for the tensor-core kernels: runs of few
+        tokens (decode rows) for the decode kernel, longer portions in runs of
+        ``attn_portion_tokens``. One plan serves every layer with the same head layout."""
+        if not self.uses_tensor_cores():
+            return
+        key = ("attention", self.H, self.KV, self.hs)
+        if key in ctx.plans:
+            return
+        G = self.H // self.KV
+        dec_tokens = ops.attn_decode_rows(self.H, self.KV, self.hs) // G
+        por_tokens = ops.attn_portion_tokens(self.H, self.KV, self.hs)
+        if por_tokens <= 0:
+            raise ops.KernelError(f"attention: {G} query heads per kv head do not fit the tensor-core kernels")
+        dec, por = [], []
+        S = ctx.num_seqs
+        qs, cl = ctx.h_q_start, ctx.h_ctx_len
+        for s in range(S):
+            row0, n = int(qs[s]), int(qs[s + 1] - qs[s])
+            pos0 = int(cl[s]) - n
+            if n <= dec_tokens:
+                dec.append((s, row0, n, pos0))
+            else:
+                for b in range(0, n, por_tokens):
+                    por.append((s, row0 + b, min(por_tokens, n - b), pos0 + b))
+        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None}
+        n_dec = len(dec)
+        if ctx.seq_cap is not None:                   # fixed shapes: pad with empty items
+            dec += [(0, 0, 0, 0)] * (ctx.seq_cap - n_dec)
+        if dec:
+            # enough blocks to fill the GPU when few sequences decode
+            nsplit = max(1, min(MAX_SPLITS, -(-TARGET_BLOCKS // (len(dec) * self.KV))))
+            if ctx.seq_cap is None:
+                longest = max(d[3] + d[2] for d in dec)
+                nsplit = min(nsplit, max(1, -(-longest // (64 * MIN_TILES_PER_SPLIT))))
+            plan["nsplit"] = nsplit
+            plan["dec"] = ctx.upload_ints(f"attn_dec_{self.H}_{self.KV}_{self.hs}",
+                                          np.asarray(dec, dtype=np.int32)).view(-1, 4)
+            if nsplit > 1:
+                n = ops.attn_decode_scratch_floats(len(dec), self.H, self.KV, self.hs, nsplit)
+                plan["scratch"] = ctx.buf("attn_split", (n,), torch.float32)
+        if por:
+            plan["por"] = ctx.upload_ints(f"attn_por_{self.H}_{self.KV}_{self.hs}",
+                                          np.asarray(por, dtype=np.int32)).view(-1, 4)
+        ctx.plans[key] = plan
+
     def attend(self, q, cache, ctx, out):
-        ops.paged_attention_ref(q, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions,
-                                out, cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs,
-                                self.scale, self.window or 0, status=ctx.status)
+        if not self.uses_tensor_cores():
+            ops.paged_attention_ref(q, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions,
+                                    out, cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs,
+                                    self.scale, self.window or 0, status=ctx.status)
+            return
+        plan = ctx.plans[("attention", self.H, self.KV, self.hs)]
+        args = (cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs, self.scale, self.window or 0)
+        if plan["dec"] is not None:
+            ops.attn_decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,
+                            nsplit=plan["nsplit"], scratch=plan["scratch"], status=ctx.status)
+        if plan["por"] is not None:
+            ops.attn_portion(q, cache.k, cache.v, cache.block_table, plan["por"], out, *args, status=ctx.status)
 
 
 register_mixer("attention", Attention)

@@ -8,7 +8,8 @@ know which model or layer it sits in. Four kinds exist:
 ``PositionEncoding``  gives a mixer what it needs to encode positions: ``rotary()`` returns
                       ``(inv_freq, rot_dim)`` for mixers that fuse the rotation, or None, in
                       which case the mixer calls ``apply(q, k, ctx)`` on unfused views.
-``Mixer``             ``forward(x, ctx, cache) -> delta`` mixes token rows of a sequence; it
+``Mixer``             ``forward(x, ctx, cache) -> delta`` mixes token rows of a sequence
+                      (``prepare(ctx, cache)`` may plan the step on the host first); it
                       declares the cache it needs (``cache_need()``: paged keys/values, with or
                       without a window) and per-request state of fixed size (``state_need()``).
 ``FeedForward``       ``forward(x, ctx) -> delta`` acts on each row alone.
@@ -93,6 +94,10 @@ class Mixer(Part):
 
     def state_need(self) -> Optional[StateNeed]:
         return None
+
+    def prepare(self, ctx, cache) -> None:
+        """Host-side planning for the step (optional): runs once per step before any layer's
+        ``forward``, and again before each replay of a captured step."""
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         raise NotImplementedError

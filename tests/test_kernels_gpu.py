@@ -221,3 +221,131 @@ def test_sampling_distribution():
     freq = torch.bincount(out.cpu().long(), minlength=V).double() / R
     assert freq[pk == 0].sum().item() == 0
     assert (freq - pk).abs().max().item() < 4 * math.sqrt(0.25 / R)
+
+
+# ---- tensor-core attention -----------------------------------------------------------------
+
+def _items_for(lengths, tails, dec_tokens, por_tokens):
+    """Rows = the last ``tails[s]`` tokens of each sequence, cut into kernel items."""
+    dec, por, rows = [], [], []
+    row = 0
+    for s, (n, tl) in enumerate(zip(lengths, tails)):
+        tl = min(tl, n)
+        pos0 = n - tl
+        if tl <= dec_tokens:
+            dec.append((s, row, tl, pos0))
+        else:
+            for b in range(0, tl, por_tokens):
+                por.append((s, row + b, min(por_tokens, tl - b), pos0 + b))
+        rows += [(s, pos0 + i) for i in range(tl)]
+        row += tl
+    return dec, por, rows
+
+
+def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit):
+    o = ops()
+    G = H // KV
+    dec_tokens = o.attn_decode_rows(H, KV, hs) // G
+    por_tokens = o.attn_portion_tokens(H, KV, hs)
+    dec, por, rows = _items_for(lengths, tails, dec_tokens, por_tokens)
+    q = torch.stack([seqs[s][0][p].reshape(-1) for s, p in rows]).to(torch.bfloat16).to(DEV)
+    out = torch.full_like(q, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    kcd, vcd, tb = kc.to(DEV), vc.to(DEV), table.to(DEV)
+    if dec:
+        items = torch.tensor(dec, dtype=torch.int32, device=DEV)
+        scratch = None
+        if nsplit > 1:
+            scratch = torch.empty(o.attn_decode_scratch_floats(len(dec), H, KV, hs, nsplit), device=DEV)
+        o.attn_decode(q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0,
+                      nsplit=nsplit, scratch=scratch, status=status)
+    if por:
+        items = torch.tensor(por, dtype=torch.int32, device=DEV)
+        o.attn_portion(q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0, status=status)
+    assert status.item() == 0
+    return out.double().cpu(), rows, bool(dec), bool(por)
+
+
+@pytest.mark.parametrize("H,KV,hs,page_size,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, None), (8, 2, 128, 16, None), (32, 8, 128, 16, None),
+    (5, 5, 80, 32, 7), (2, 1, 256, 16, 40), (32, 1, 64, 16, None), (40, 1, 128, 16, None), (24, 8, 128, 16, 100),
+    (14, 2, 64, 64, None), (9, 3, 96, 16, 65)])
+@pytest.mark.parametrize("nsplit", [1, 3])
+def test_attention_tensor_cores(H, KV, hs, page_size, window, nsplit):
+    lengths = [1, 37, 130, 700, 64, 129]
+    tails = [1, 1, 3, 700, 64, 2]           # decode rows, short runs, a whole long prompt, an exact tile
+    seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page_size, seed=8)
+    out, rows, used_dec, used_por = _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit)
+    assert used_por
+    scale = 1.0 / math.sqrt(hs)
+    full = [plain_llama.attention(q.double(), k.double(), v.double(), scale, window) for q, k, v in seqs]
+    want = torch.stack([full[s][p].reshape(-1) for s, p in rows])
+    assert not torch.isnan(out).any(), "every row was written"
+    # probabilities and outputs are rounded to bf16 (2^-9 relative each): 2^-8 of the largest value
+    vmax = max(v.abs().max().item() for _, _, v in seqs)
+    assert (out - want).abs().max().item() <= 2 ** -8 * vmax
+
+
+@pytest.mark.parametrize("hs,page_size", [(128, 16), (64, 8), (32, 4)])
+def test_attention_finds_one_far_key(hs, page_size):
+    """One key among hundreds matches the query strongly: the output is that key's value row,
+    wherever the key lies (first and last slot of a page, edges of the 64-key tiles, the row's
+    own position), for a decode row, with and without splits, and for a row inside a portion."""
+    H, KV = 4, 2
+    n = 333
+    g = torch.Generator().manual_seed(9)
+    for target in [0, page_size - 1, page_size, 63, 64, 65, 127, 128, 200, n - 2, n - 1]:
+        q = 0.1 * torch.randn(n, H, hs, generator=g)
+        k = 0.1 * torch.randn(n, KV, hs, generator=g)
+        v = torch.randn(n, KV, hs, generator=g)
+        direction = torch.randn(hs, generator=g)
+        direction /= direction.norm()
+        k[target, :, :] = 6.0 * direction
+        q[n - 1, :, :] = 6.0 * math.sqrt(hs) * direction        # score 36 against ~0 elsewhere
+        q[n - 5, :, :] = 6.0 * math.sqrt(hs) * direction
+        seqs = [(q.to(torch.bfloat16).float(), k.to(torch.bfloat16).float(), v.to(torch.bfloat16).float())]
+        blocks = -(-n // page_size)
+        perm = torch.randperm(blocks + 2, generator=g)
+        table = perm[:blocks].to(torch.int32).view(1, -1)
+        kc = torch.zeros(blocks + 2, KV, page_size, hs); vc = torch.zeros_like(kc)
+        for b in range(blocks):
+            m = min(page_size, n - b * page_size)
+            kc[table[0, b], :, :m] = seqs[0][1][b * page_size:b * page_size + m].transpose(0, 1)
+            vc[table[0, b], :, :m] = seqs[0][2][b * page_size:b * page_size + m].transpose(0, 1)
+        kc, vc = kc.to(torch.bfloat16), vc.to(torch.bfloat16)
+        for tails, nsplit in (([1], 1), ([1], 4), ([n], 1)):
+            out, rows, _, _ = _run_tc_attention(seqs, table, kc, vc, [n], tails, H, KV, hs, page_size, None, nsplit)
+            for r, (s, p) in enumerate(rows):
+                if p not in (n - 1, n - 5) or target > p:
+                    continue
+                got = out[r].view(H, hs)
+                want = seqs[0][2][target].double().repeat_interleave(H // KV, 0)
+                assert (got - want).abs().max().item() < 0.02, (target, tails, nsplit, p)
+
+
+def test_attention_window_edge():
+    """The key just inside the window counts, the one just outside does not."""
+    H, KV, hs, page_size, window, n = 2, 1, 64, 16, 50, 180
+    g = torch.Generator().manual_seed(10)
+    direction = torch.randn(hs, generator=g); direction /= direction.norm()
+    for target, visible in ((n - 1 - window, False), (n - window, True)):
+        q = 0.1 * torch.randn(n, H, hs, generator=g)
+        k = 0.1 * torch.randn(n, KV, hs, generator=g)
+        v = torch.randn(n, KV, hs, generator=g)
+        k[target] = 6.0 * direction
+        q[n - 1] = 6.0 * math.sqrt(hs) * direction
+        seqs = [(q.to(torch.bfloat16).float(), k.to(torch.bfloat16).float(), v.to(torch.bfloat16).float())]
+        blocks = -(-n // page_size)
+        table = torch.arange(blocks, dtype=torch.int32).view(1, -1)
+        kc = torch.zeros(blocks, KV, page_size, hs); vc = torch.zeros_like(kc)
+        for b in range(blocks):
+            m = min(page_size, n - b * page_size)
+            kc[b, :, :m] = seqs[0][1][b * page_size:b * page_size + m].transpose(0, 1)
+            vc[b, :, :m] = seqs[0][2][b * page_size:b * page_size + m].transpose(0, 1)
+        for tails in ([1], [n]):
+            out, rows, _, _ = _run_tc_attention(seqs, table, kc.to(torch.bfloat16), vc.to(torch.bfloat16), [n], tails,
+                                                H, KV, hs, page_size, window, 1)
+            got = out[-1].view(H, hs)
+            hit = (got - seqs[0][2][target].double()).abs().max().item() < 0.02
+            assert hit == visible, (target, tails)
