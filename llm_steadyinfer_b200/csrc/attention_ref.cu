@@ -31,8 +31,8 @@ paged_attention_ref_kernel(const T* __restrict__ q, long long q_row_stride,
   const int pos = positions[t];
   const int seq = row_seq[t];
   T* o = out + (size_t)t * out_row_stride + (size_t)h * hs;
-  if (seq < 0 || seq >= num_seqs) {
-    if (threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+  if (seq < 0 || seq >= num_seqs) {      // seq < 0 marks a padding row of a fixed-shape step
+    if (threadIdx.x == 0 && seq >= 0) set_status(status, SI_BAD_SEQ);
     for (int d = threadIdx.x; d < hs; d += blockDim.x) o[d] = from_f32<T>(0.f);
     return;
   }

@@ -48,8 +48,24 @@ def _cuda(*ts) -> None:
             raise KernelError("kernels take CUDA tensors only; there is no CPU path")
 
 
-def _check(rc: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far in this process (graph replays are added by
+    the code that replays them)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(rc: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if rc == 0:
+        _launches += kernels
         return
     if rc == -2:
         raise KernelError(f"{what}: this size is outside what the kernel supports")
@@ -277,4 +293,4 @@ def attn_decode(q, k_cache, v_cache, block_table, items, out, page_size: int, nu
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(items), items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs,
              H, KV, hs, float(scale), int(window or 0), int(nsplit), _ptr(scratch), _ptr(status), _stream()),
-           f"attn_decode(heads={H}, kv_heads={KV}, head_dim={hs})")
+           f"attn_decode(heads={H}, kv_heads={KV}, head_dim={hs})", kernels=2 if nsplit > 1 else 1)

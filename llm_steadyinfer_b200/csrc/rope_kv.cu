@@ -28,7 +28,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long row_stride,
 
   long long page = -1;
   if (k_cache) {
-    if (seq < 0 || seq >= num_seqs) {
+    if (seq < 0) {
+      // a padding row of a fixed-shape step: nothing is stored
+    } else if (seq >= num_seqs) {
       if (threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
     } else {
       const int slot = pos / page_size;

@@ -62,7 +62,7 @@ class LLM:
         budget_cap = 4096 if max_num_batched_tokens == "adaptive" else int(max_num_batched_tokens)
         self.runner = ModelRunner(self.model, page_size=block_size, num_pages=self.num_blocks,
                                   max_requests=self.max_batch, max_step_tokens=budget_cap + self.max_batch,
-                                  prefix_reuse=enable_prefix_cache)
+                                  prefix_reuse=enable_prefix_cache, max_seq_len=self.max_seq_len)
         eos = self.model.config.eos_token_ids() if hasattr(self.model.config, "eos_token_ids") else []
         self.scheduler = Scheduler(self.runner.manager, self.max_batch, self.max_seq_len, max_gen_len,
                                    token_budget=max_num_batched_tokens, eos_token_ids=eos)

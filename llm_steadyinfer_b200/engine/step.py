@@ -8,6 +8,11 @@ one block-table row per *token* (src/source/scheduler/scheduler.cpp:526-551) and
 logits for all rows, where this one uploads one row per *sequence* and a list of wanted rows.
 
 All integer inputs of a step travel in one pinned buffer and one host-to-device copy.
+
+Pure decode steps can be replayed from CUDA graphs, one per (sequence count rounded up, table
+width) as the reference keeps one per batch size (src/source/model/model.cpp:74-254): the step is
+laid out with fixed shapes (rows of absent sequences are padding that stores nothing), captured
+once, and later steps only refresh the integer inputs and the parts' work lists before the replay.
 """
 from __future__ import annotations
 
@@ -18,6 +23,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheLayout, CacheManager, CacheStorage, OutOfPages
+from ..csrc import ops
 from ..csrc.ops import KernelError
 
 STATUS_TEXT = {
@@ -26,6 +32,7 @@ STATUS_TEXT = {
     3: "a row names a sequence outside the batch",
     4: "a bounded wait inside a kernel ran out",
 }
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
 @dataclass
@@ -44,17 +51,17 @@ class StepContext:
 
     def __init__(self, runner: "ModelRunner"):
         self._runner = runner
-        self.num_tokens = 0
+        self.num_tokens = 0               # rows of the step (with padding rows in a fixed-shape step)
         self.num_seqs = 0
         self.num_logit_rows = 0
         self.status = runner.status
-        self.plans: Dict = {}          # per-step scratch of parts (host-side plans), cleared each step
-        # device int32 views, set by ModelRunner._stage
+        self.plans: Dict = {}             # per-step host-side plans of parts, cleared each step
+        self.seq_cap: Optional[int] = None    # fixed-shape (graph) steps: sequences the shapes are for
+        # device int32 views
         self.tokens = self.positions = self.row_seq = None
         self.q_start = self.ctx_len = self.slots = self.logit_rows = None
-        # host copies
+        # host copies (real sequences only)
         self.h_positions = self.h_q_start = self.h_ctx_len = self.h_slots = None
-        self.seq_cap: Optional[int] = None   # set for fixed-shape decode steps (graphs): sequences the shapes are for
 
     def buf(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """A scratch tensor that lives until the same key is asked for again."""
@@ -66,11 +73,37 @@ class StepContext:
         return self._runner.upload_ints(key, values, capacity)
 
 
+class _PinnedRing:
+    """A device int32 buffer fed from four pinned host buffers in turn, so that the host never
+    rewrites a buffer whose copy may still be in flight."""
+
+    def __init__(self, cap: int, device):
+        self.cap = cap
+        self.hosts = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * 4
+        self.dev = torch.zeros(cap, dtype=torch.int32, device=device)
+        self.turn = 0
+
+    def next_host(self) -> np.ndarray:
+        self.turn = (self.turn + 1) % 4
+        ev = self.events[self.turn]
+        if ev is not None:
+            ev.synchronize()
+        return self.hosts[self.turn].numpy()
+
+    def send(self, n: int) -> None:
+        if n:
+            self.dev[:n].copy_(self.hosts[self.turn][:n], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[self.turn] = ev
+
+
 class ModelRunner:
     """Owns the model's cache (manager + storage), the step's staging buffers and scratch."""
 
     def __init__(self, model, page_size: int, num_pages: int, max_requests: int,
-                 max_step_tokens: int, prefix_reuse: bool = False):
+                 max_step_tokens: int, prefix_reuse: bool = False, max_seq_len: Optional[int] = None):
         if model.device.type != "cuda":
             raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
         self.model = model
@@ -83,16 +116,19 @@ class ModelRunner:
         self.storage = CacheStorage(self.layout, self.manager, model.dtype, self.device)
         self.page_size = page_size
         self.max_requests = max_requests
-        self.max_step_tokens = max_step_tokens
+        self.max_step_tokens = max(max_step_tokens, max_requests)
+        self.max_seq_len = int(max_seq_len or num_pages * page_size)
+        self.max_width = max(1, min(num_pages, -(-self.max_seq_len // page_size)))
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._scratch: Dict[str, torch.Tensor] = {}
-        self._stage_cap = 0
-        self._hosts: List[torch.Tensor] = []      # ring of pinned buffers, one copy in flight each
-        self._copied: List[Optional[torch.cuda.Event]] = []
-        self._ring = 0
-        self._dev = None
-        self._uploads: Dict[str, dict] = {}
+        self._scratch: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._uploads: Dict[str, _PinnedRing] = {}
+        G = max(1, len(self.manager.groups))
+        T, S, W = self.max_step_tokens, max_requests, self.max_width
+        self._stage = _PinnedRing(4 * (T + 4) + 3 * (S + 4) + 8 + G * S * W, self.device)
+        self._graphs: Dict[Tuple[int, int], dict] = {}
+        self._generation = 0              # bumped when a captured address may have changed
         self.ctx = StepContext(self)
+        self.launches_last_step = 0
 
     # ---- scratch -----------------------------------------------------------------------
     def workspace(self, key: str, shape, dtype) -> torch.Tensor:
@@ -104,58 +140,30 @@ class ModelRunner:
         if t is None or t.numel() < n:
             if torch.cuda.is_current_stream_capturing():
                 raise StepError(f"scratch {key!r} would have to grow during graph capture")
-            t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            t = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._scratch[k] = t
+            self._drop_graphs()
         return t[:n].view(*shape)
 
     def upload_ints(self, key: str, values: np.ndarray, capacity: Optional[int] = None) -> torch.Tensor:
         values = np.ascontiguousarray(values, dtype=np.int32).reshape(-1)
         n = values.size
         cap = max(capacity or 0, n, 4)
-        ent = self._uploads.get(key)
-        if ent is None or ent["cap"] < cap:
+        ring = self._uploads.get(key)
+        if ring is None or ring.cap < cap:
             if torch.cuda.is_current_stream_capturing():
                 raise StepError(f"upload buffer {key!r} would have to grow during graph capture")
-            cap = max(cap, 2 * (ent["cap"] if ent else 0))
-            ent = {"cap": cap, "ring": 0, "events": [None] * 4,
-                   "hosts": [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)],
-                   "dev": torch.empty(cap, dtype=torch.int32, device=self.device)}
-            self._uploads[key] = ent
-        ent["ring"] = (ent["ring"] + 1) % 4
-        ev = ent["events"][ent["ring"]]
-        if ev is not None:
-            ev.synchronize()
-        host = ent["hosts"][ent["ring"]]
-        host.numpy()[:n] = values
-        if n:
-            ent["dev"][:n].copy_(host[:n], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            ent["events"][ent["ring"]] = ev
-        return ent["dev"][:n]
+            ring = _PinnedRing(max(cap, 2 * (ring.cap if ring else 0)), self.device)
+            self._uploads[key] = ring
+            self._drop_graphs()
+        ring.next_host()[:n] = values
+        ring.send(n)
+        return ring.dev[:n]
 
-    def _staging(self, n_ints: int):
-        """A pinned host buffer whose last copy has finished, and the device buffer."""
-        if n_ints > self._stage_cap:
-            if torch.cuda.is_current_stream_capturing():
-                raise StepError("staging buffers would have to grow during graph capture")
-            torch.cuda.current_stream().synchronize()
-            cap = max(1024, 2 * n_ints)
-            self._hosts = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)]
-            self._copied = [None] * 4
-            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._stage_cap = cap
-        self._ring = (self._ring + 1) % len(self._hosts)
-        ev = self._copied[self._ring]
-        if ev is not None:
-            ev.synchronize()
-        return self._hosts[self._ring], self._dev
-
-    def _upload(self, host: torch.Tensor, n_ints: int) -> None:
-        self._dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._copied[self._ring] = ev
+    def _drop_graphs(self) -> None:
+        if self._graphs:
+            self._graphs.clear()
+        self._generation += 1
 
     # ---- the step ----------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -164,11 +172,58 @@ class ModelRunner:
         ctx = self._prepare(entries)
         self.storage.zero_new_slots()
         caches = self.storage.layer_views(self._tables)
+        before = ops.launch_count()
         self.model.prepare(ctx, caches)
         logits = self.model.forward(ctx, caches)
+        self.launches_last_step = ops.launch_count() - before
+        self._commit(entries)
+        return logits
+
+    def _commit(self, entries) -> None:
         for e, new_len in zip(entries, self._new_lengths):
             self.manager.commit(e.req, new_len)
-        return logits
+
+    def graphs_available(self) -> bool:
+        return True
+
+    def step_decode_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A pure decode step (one token and one wanted row per entry) through a CUDA graph.
+        The first step of a shape runs directly and is then captured; later ones are replays.
+        Returns logits [len(entries), vocab]."""
+        S = len(entries)
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            raise StepError("a graph step takes one token and one wanted row per entry")
+        cap = next((b for b in GRAPH_BUCKETS if b >= S), None)
+        if cap is None or cap > self.max_requests:
+            cap = self.max_requests
+        if S > cap:
+            raise StepError(f"{S} sequences exceed the limit of {self.max_requests}")
+        ctx = self._prepare(entries, seq_cap=cap, width_cap=self.max_width)
+        self.storage.zero_new_slots()
+        caches = self.storage.layer_views(self._tables)
+        self.model.prepare(ctx, caches)
+        key = (cap, self.max_width)
+        g = self._graphs.get(key)
+        if g is None:
+            before = ops.launch_count()
+            logits = self.model.forward(ctx, caches)            # runs this step, allocates all scratch
+            launches = ops.launch_count() - before
+            gen = self._generation
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.current_stream().synchronize()
+            with torch.cuda.graph(graph):
+                captured = self.model.forward(ctx, caches)      # recorded, not run
+            ops.add_launches(-launches)                          # recording launched nothing
+            if gen == self._generation:                           # no buffer moved while capturing
+                self._graphs[key] = {"graph": graph, "logits": captured, "launches": launches}
+            self.launches_last_step = launches
+        else:
+            g["graph"].replay()
+            ops.add_launches(g["launches"])
+            self.launches_last_step = g["launches"]
+            logits = g["logits"]
+        self._commit(entries)
+        return logits[:S]
 
     def _prepare(self, entries: Sequence[StepEntry], seq_cap: Optional[int] = None,
                  width_cap: Optional[int] = None) -> StepContext:
@@ -187,8 +242,11 @@ class ModelRunner:
                 if not 0 <= w < len(e.tokens):
                     raise StepError(f"request {e.req!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
             T += len(e.tokens)
+        S = len(entries)
         if T > self.max_step_tokens:
             raise StepError(f"step of {T} tokens exceeds the limit of {self.max_step_tokens}")
+        if S > self.max_requests:
+            raise StepError(f"step of {S} sequences exceeds the limit of {self.max_requests}")
         for e in entries:
             if not mgr.has(e.req):
                 mgr.admit(e.req)
@@ -203,33 +261,45 @@ class ModelRunner:
         self._new_lengths = []
         for e in entries:
             new_len = mgr.length(e.req) + len(e.tokens)
+            if new_len > self.max_width * self.page_size:
+                raise StepError(f"request {e.req!r} would hold {new_len} tokens, above the limit "
+                                f"of {self.max_width * self.page_size}")
             mgr.grow(e.req, new_len)
             self._new_lengths.append(new_len)
 
-        S = len(entries)
         R = sum(len(e.want) for e in entries)
-        S_cap = seq_cap or S
         G = len(mgr.groups)
         W = max([1] + [len(mgr.table(g, e.req)) for g in range(G) for e in entries])   # pages may be reserved ahead
+        fixed = seq_cap is not None
+        S_cap = seq_cap or S
         W_cap = width_cap or W
-        # layout (ints): tokens T | positions T | row_seq T | logit_rows R | q_start S+1 | ctx_len S | slots S | tables G*S*W
+        T_cap = S_cap if fixed else T          # fixed-shape steps: one row per sequence slot
+        R_cap = S_cap if fixed else R
+        # layout (ints): tokens | positions | row_seq | logit_rows | q_start | ctx_len | slots | tables
         offs = {}
         o = 0
-        for name, n in (("tokens", T), ("positions", T), ("row_seq", T), ("logit_rows", max(R, 1)),
+        for name, n in (("tokens", T_cap), ("positions", T_cap), ("row_seq", T_cap), ("logit_rows", max(R_cap, 1)),
                         ("q_start", S_cap + 1), ("ctx_len", S_cap), ("slots", S_cap)):
-            offs[name] = (o, n)
+            offs[name] = o
             o += (n + 3) // 4 * 4                     # 16-byte aligned regions
         table_off = o
         o += G * S_cap * W_cap
-        host, dev = self._staging(o)
-        h = host.numpy()
-        row = 0
-        r = 0
-        b_tok, _ = offs["tokens"]; b_pos, _ = offs["positions"]; b_seq, _ = offs["row_seq"]
-        b_lr, _ = offs["logit_rows"]; b_qs, _ = offs["q_start"]; b_cl, _ = offs["ctx_len"]; b_sl, _ = offs["slots"]
+        if o > self._stage.cap:
+            raise StepError(f"step inputs of {o} integers exceed the staging buffer of {self._stage.cap}")
+        h = self._stage.next_host()
+        dev = self._stage.dev
+        b_tok, b_pos, b_seq = offs["tokens"], offs["positions"], offs["row_seq"]
+        b_lr, b_qs, b_cl, b_sl = offs["logit_rows"], offs["q_start"], offs["ctx_len"], offs["slots"]
+        if fixed:
+            h[b_tok:b_tok + T_cap] = 0
+            h[b_pos:b_pos + T_cap] = 0
+            h[b_seq:b_seq + T_cap] = -1               # padding rows store nothing
+            h[b_lr:b_lr + R_cap] = np.arange(R_cap, dtype=np.int32)
         h[b_qs:b_qs + S_cap + 1] = T
         h[b_cl:b_cl + S_cap] = 0
         h[b_sl:b_sl + S_cap] = 0
+        row = 0
+        r = 0
         for s, e in enumerate(entries):
             n = len(e.tokens)
             start = mgr.length(e.req)
@@ -249,19 +319,19 @@ class ModelRunner:
             for s, e in enumerate(entries):
                 t = mgr.table(g, e.req)
                 tabs[g, s, :len(t)] = t
-        self._upload(host, o)
+        self._stage.send(o)
 
         ctx = self.ctx
         ctx.plans.clear()
-        ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, R
-        view = lambda name, n: dev[offs[name][0]:offs[name][0] + n]
-        ctx.tokens = view("tokens", T)
-        ctx.positions = view("positions", T)
-        ctx.row_seq = view("row_seq", T)
-        ctx.logit_rows = view("logit_rows", R)
-        ctx.q_start = view("q_start", S_cap + 1)
-        ctx.ctx_len = view("ctx_len", S_cap)
-        ctx.slots = view("slots", S_cap)
+        ctx.seq_cap = seq_cap
+        ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T_cap, S, R_cap
+        ctx.tokens = dev[b_tok:b_tok + T_cap]
+        ctx.positions = dev[b_pos:b_pos + T_cap]
+        ctx.row_seq = dev[b_seq:b_seq + T_cap]
+        ctx.logit_rows = dev[b_lr:b_lr + R_cap]
+        ctx.q_start = dev[b_qs:b_qs + S_cap + 1]
+        ctx.ctx_len = dev[b_cl:b_cl + S_cap]
+        ctx.slots = dev[b_sl:b_sl + S_cap]
         ctx.h_positions = h[b_pos:b_pos + T].copy()
         ctx.h_q_start = h[b_qs:b_qs + S + 1].copy()
         ctx.h_ctx_len = h[b_cl:b_cl + S].copy()
@@ -269,9 +339,6 @@ class ModelRunner:
         dtabs = dev[table_off:table_off + G * S_cap * W_cap].view(G, S_cap, W_cap)
         self._tables = [dtabs[g] for g in range(G)]
         return ctx
-
-    def graphs_available(self) -> bool:
-        return False
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel reported a fault (it never traps)."""

@@ -111,3 +111,24 @@ def test_eos_stops(folders):
     got = llm.generate(prompts, SamplingParams(stop_token_ids=(stop_at,), ignore_eos=True))[0]
     assert got.token_ids == free_run[:free_run.index(stop_at) + 1]
     assert got.finish_reason == "eos"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_decode_equals_direct_decode(folders, dtype):
+    """Decode steps replayed from CUDA graphs give the tokens of direct steps, while the batch
+    shrinks and grows across graph shapes."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("B", [5, 30, 12, 70, 3])
+    params = [SamplingParams(ignore_eos=True, max_tokens=n) for n in (40, 9, 25, 17, 33)]
+    outs = {}
+    for graphs in (False, True):
+        llm = LLM(folders["B"], dtype=dtype, max_batch=5, max_seq_len=160, max_gen_len=40, block_size=8,
+                  use_cuda_graph=graphs)
+        outs[graphs] = [g.token_ids for g in llm.generate(prompts, params)]
+        if graphs:
+            assert llm.stats["graph_steps"] > 20 and len(llm.runner._graphs) >= 2
+        llm.runner.manager.check_invariant()
+    assert outs[True] == outs[False]
+    if dtype == "float32":
+        assert outs[True] == plain_generate(folders["B"], prompts, 40)[:0] + [
+            o[:p.max_tokens] for o, p in zip(plain_generate(folders["B"], prompts, 40), params)]
