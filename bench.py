@@ -1,0 +1,269 @@
+"""Decode and prefill throughput of the engine at the Llama-3.1-8B shape, random weights, bf16.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests whose contexts end at 8192 tokens.
+``value`` is decoded tokens per second timed on the device around K steps (inputs staged from
+pinned memory, CUDA-graph replay, sampling kernel; no host read inside the region); ``e2e`` is
+the same through the Python entry point (``LLM.step``: scheduler, host-to-device copy of the
+step's inputs, device-to-host read of the sampled tokens, every step). One JSON line is printed.
+The engine runs on one GPU: for --gpus above 1 a line says so and the exit code is 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_3_1_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "bos_token_id": 128000, "eos_token_id": 128001,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}      # earlier measurement on this pool
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}, "measured"
+        except (ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        mhz = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill"],
+                    help="run only the device-timed decode steps or only the prefill (for profiling)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a CMake/C++ project with no Python package and no offline "
+                          "dependencies (glog, armadillo, sentencepiece, re2 tarballs are not shipped); "
+                          "pip cannot install it and its default CUDA path computes wrong attention"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    K, W = args.steps, max(3, args.warmup)
+
+    import torch
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    from llm_steadyinfer_b200.config import config_from_dict
+    from llm_steadyinfer_b200.csrc import ops
+    from llm_steadyinfer_b200.engine.step import StepEntry
+    from llm_steadyinfer_b200.models import Model
+    from llm_steadyinfer_b200.weights import init_random
+
+    torch.cuda.set_device(0)
+    cfg_d = dict(LLAMA_3_1_8B)
+    layers_full = cfg_d["num_hidden_layers"]
+    if args.layers:
+        cfg_d["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(cfg_d)
+    model = Model(cfg, torch.bfloat16, "cuda:0")
+    init_random(model, seed=0)
+    B, CTX, PAGE = args.batch, args.context, 16
+    big = 1 if (args.no_points or args.section != "all") else max(B, 64)
+    llm = LLM(model, dtype="bfloat16", max_batch=max(B, big), max_seq_len=CTX, max_gen_len=K + W + 8,
+              block_size=PAGE, max_num_batched_tokens=2048, enable_prefix_cache=False)
+    runner, mgr = llm.runner, llm.runner.manager
+    gen = torch.Generator().manual_seed(1)
+    V = cfg.vocab_size
+    rand_tokens = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+    pk, pk_src = peaks()
+    L, d, F = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
+    H, KV, hs = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    block_params = L * (d * (H + 2 * KV) * hs + H * hs * d + 3 * d * F)
+    weight_bytes = 2 * (block_params + V * d) + 2 * (2 * L + 1) * d
+    kv_bytes_per_token = 2 * L * KV * hs * 2
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    clocks = ClockSampler()
+
+    # ---- prefill of 2,048 tokens (one request, logits of the last row) -----------------------
+    PT = 2048
+    ptoks = rand_tokens(PT)
+
+    def prefill_once(i):
+        runner.step([StepEntry("prefill", ptoks, [PT - 1])])
+        runner.finish("prefill")
+
+    if args.section == "decode":
+        pre_ms = float("nan")
+    else:
+        for i in range(3):
+            prefill_once(i)
+        runner.check_status()
+        pre_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
+    if args.section == "prefill":
+        print(json.dumps({"section": "prefill", "tokens": PT, "ms": round(pre_ms, 3)}))
+        return 0
+    pre_flops = 2 * PT * block_params + L * 4 * H * hs * PT * (PT + 1) / 2 + 2 * V * d
+    prefill = {"value": round(PT / pre_ms * 1e3, 1), "tokens": PT, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode on the device: contexts filled synthetically, fixed next tokens ----------------
+    for t in runner.storage.keys + runner.storage.values:
+        t.normal_(0.0, 0.5)
+
+    def decode_run(batch, steps, warm, sample=True):
+        start = CTX - (steps + warm) - 1
+        ids = [f"d{i}" for i in range(batch)]
+        for r in ids:
+            mgr.admit(r)
+            mgr.grow(r, start)
+            mgr.commit(r, start)
+        toks = [rand_tokens(batch) for _ in range(steps + warm)]
+        rows = [(SamplingParams(), 0, 0)] * batch
+        state = {"i": 0}
+
+        def one(_):
+            entries = [StepEntry(r, [toks[state["i"]][j]], [0]) for j, r in enumerate(ids)]
+            logits = runner.step_decode_graph(entries)
+            if sample:
+                llm.sampler.sample(logits, rows)
+            state["i"] += 1
+
+        for i in range(warm):
+            one(i)
+        runner.check_status()
+        before = ops.launch_count()
+        ms = timed(one, steps)
+        launches = ops.launch_count() - before
+        runner.check_status()
+        for r in ids:
+            runner.finish(r)
+        mean_ctx = start + warm + (steps - 1) / 2 + 1
+        return ms, launches, mean_ctx
+
+    clocks.start()
+    ms, launches, mean_ctx = decode_run(B, K, W)
+    clocks.stop()
+    ms_per_step = ms / K
+    value = B * K / ms * 1e3
+    step_bytes = weight_bytes + B * mean_ctx * kv_bytes_per_token + B * d * 2
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
+
+    if args.section == "decode":
+        print(json.dumps({"section": "decode", "ms_per_step": round(ms_per_step, 4), "roofline": roofline,
+                          "gpu_launches": launches}))
+        return 0
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pm, _, _ = decode_run(b, min(K, 32), 4)
+            points[f"decode_b{b}"] = round(b * min(K, 32) / pm * 1e3, 1)
+
+    # ---- end to end through the Python entry point -------------------------------------------
+    plen = CTX - (K + W) - 2
+    for _ in range(B):
+        llm.add_request(rand_tokens(plen), SamplingParams(max_tokens=K + W + 1, ignore_eos=True))
+    while any(not s.prefill_done for s in llm.get_running()) or llm.scheduler.waiting:
+        llm.step()
+    for _ in range(W):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        llm.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = {"value": round(B * K / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": runner.h2d_bytes_last_step,      # step inputs + attention work list
+           "d2h_bytes_per_step": 4 * B + 4}                        # sampled ids + status word
+    while not llm.all_finished():
+        llm.step()
+
+    out = {
+        "metric": "decode tokens/s, Llama-3.1-8B shape, batch 8, context 8192", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights (seed 0), uniform random token ids", "impl": "ours",
+        "config": {"model": "Llama-3.1-8B shape", "layers": L, "layers_full": layers_full, "hidden": d,
+                   "heads": H, "kv_heads": KV, "head_dim": hs, "intermediate": F, "vocab": V,
+                   "global_batch": B, "seq_len": CTX, "prefill_tokens": PT, "page_size": PAGE,
+                   "parallelism": "single_gpu", "cuda_graph": True, "l2": "inputs larger than L2 (weights 16 GB)"},
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clocks.summary(),
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -56,7 +56,17 @@ def _digest(name: str) -> str:
     return h.hexdigest()[:16]
 
 
+_build_dir_cached: Optional[str] = None
+
+
 def _build_dir() -> str:
+    global _build_dir_cached
+    if _build_dir_cached is None:
+        _build_dir_cached = _find_build_dir()
+    return _build_dir_cached
+
+
+def _find_build_dir() -> str:
     d = os.path.join(CSRC_DIR, "_build")
     try:
         os.makedirs(d, exist_ok=True)
@@ -109,6 +119,12 @@ def _compile(name: str, out: str, verbose: bool) -> None:
         raise BuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n"
                          f"{' '.join(cmd)}\n{log.decode(errors='replace')}")
     os.replace(tmp, out)
+    for old in os.listdir(os.path.dirname(out)):             # libraries of earlier source versions
+        if old.startswith(name + "-") and old.endswith(".so") and old != os.path.basename(out):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), old))
+            except OSError:
+                pass
     if verbose:
         print(f"[build] {name}.cu done in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
@@ -139,11 +155,13 @@ def build_all(verbose: bool = True, jobs: Optional[int] = None) -> List[str]:
     todo = [n for n in names if not os.path.isfile(library_path(n))]
     errors: List[str] = []
 
+    _build_dir()
+
     def work(n):
         try:
             _compile(n, library_path(n), verbose)
-        except BuildError as e:
-            errors.append(str(e))
+        except Exception as e:      # a thread must not fail silently
+            errors.append(f"{n}.cu: {e}")
 
     jobs = jobs or min(len(todo), os.cpu_count() or 1, 8) or 1
     pending = list(todo)

@@ -129,6 +129,7 @@ class ModelRunner:
         self._generation = 0              # bumped when a captured address may have changed
         self.ctx = StepContext(self)
         self.launches_last_step = 0
+        self.h2d_bytes_last_step = 0
 
     # ---- scratch -----------------------------------------------------------------------
     def workspace(self, key: str, shape, dtype) -> torch.Tensor:
@@ -158,6 +159,7 @@ class ModelRunner:
             self._drop_graphs()
         ring.next_host()[:n] = values
         ring.send(n)
+        self.h2d_bytes_last_step += 4 * n
         return ring.dev[:n]
 
     def _drop_graphs(self) -> None:
@@ -320,6 +322,7 @@ class ModelRunner:
                 t = mgr.table(g, e.req)
                 tabs[g, s, :len(t)] = t
         self._stage.send(o)
+        self.h2d_bytes_last_step = 4 * o       # parts add their uploads in prepare()
 
         ctx = self.ctx
         ctx.plans.clear()
