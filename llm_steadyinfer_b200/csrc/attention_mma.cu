@@ -10,63 +10,13 @@
 //   portion kernel  rows are split over the warps (16 rows each); every warp walks all keys.
 //   decode kernel   16*MT rows shared by all warps; the 64 keys of a tile are split over the 4
 //                   warps, whose partial (max, sum, acc) are merged at the end. The key range can
-//                   also be split over gridDim.z blocks, which write fp32 partials that
-//                   `attn_reduce_kernel` merges (the reference's split kernel and combine,
+//                   also be split over gridDim.z blocks, which write fp32 partials; the block that
+//                   finishes last merges them (the reference's split kernel and combine,
 //                   src/source/op/kernels/cuda/paged_kernels.cu:96-253, work on one (token, head,
 //                   split) per block with scalar fp32 code and no sharing between the heads of a group).
 //
 // Masking: key j is visible to a row at position p when j <= p and (window == 0 or j > p - window).
-#include "common.cuh"
-#include <math.h>
-
-typedef __nv_bfloat16 bf16;
-
-struct AttnItem { int seq, row0, ntok, pos0; };
-
-struct AttnParams {
-  const bf16* q; long long q_stride;
-  const bf16* k_cache; const bf16* v_cache;
-  const int* block_table; int table_width;
-  const AttnItem* items;
-  bf16* out; long long out_stride;
-  float* part_o;            // [item][kv head][split][row][hs]  (decode kernel with nsplit > 1)
-  float* part_ml;           // [item][kv head][split][row][2]
-  int num_pages, page_size, num_seqs, H, KV, G, hs;
-  float scale_log2;         // scale * log2(e)
-  int window, nsplit;
-  int* status;
-};
-
-// ---- small PTX wrappers ---------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-  return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-  const int n = valid ? 16 : 0;       // src-size 0 zero-fills the 16 bytes
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-__device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldsm_x4_t(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
-                                         unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
+#include "attention_common.cuh"
 
 // Shared-memory tile of rows x HS_PAD bf16, 16-byte chunks XOR-swizzled by the row.
 template <int HS_PAD>
@@ -279,16 +229,21 @@ attn_portion_kernel(const AttnParams p) {
 }
 
 // ================================ decode kernel ===============================================
-// All warps share the 16*MT rows; warp w takes keys [16w, 16w+16) of every 64-key tile.
-template <int HS_PAD, int MT>
+// All warps share the 16*MT rows; warp w takes keys [16w, 16w+16) of every 64-key tile. Tiles
+// flow through a ring of STAGES shared-memory buffers filled by cp.async.
+// With nsplit > 1 each block writes its partial result to scratch and takes a ticket; the block
+// that draws the last ticket of its (item, kv head) merges all partials and resets the counter,
+// so the merge needs no launch of its own and nobody waits for anybody.
+template <int HS_PAD, int MT, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const AttnParams p) {
   constexpr int NWARPS = 4, THREADS = 128, BLOCK_N = 64, ROWS = 16 * MT;
   constexpr int KT = HS_PAD / 16, DT = HS_PAD / 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int s_last;
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
-  bf16* Ks = Qs + ROWS * HS_PAD;
-  bf16* Vs = Ks + 2 * BLOCK_N * HS_PAD;
+  bf16* Ks = Qs + ROWS * HS_PAD;                    // [STAGES][BLOCK_N][HS_PAD]
+  bf16* Vs = Ks + STAGES * BLOCK_N * HS_PAD;
 
   const AttnItem item = p.items[blockIdx.x];
   if (item.ntok <= 0) return;
@@ -329,24 +284,28 @@ attn_decode_kernel(const AttnParams p) {
       pos_of[mt][h2] = tok < item.ntok ? item.pos0 + tok : -1;
     }
 
-  if (ntiles > 0) {
-    load_q_tile<HS_PAD, ROWS, THREADS>(p, item, g, Qs);
-    load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin, kv_end, Ks, Vs);
+  if (ntiles > 0) load_q_tile<HS_PAD, ROWS, THREADS>(p, item, g, Qs);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < ntiles)
+      load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin + st * BLOCK_N, kv_end,
+                                             Ks + st * BLOCK_N * HS_PAD, Vs + st * BLOCK_N * HS_PAD);
     cp_async_commit();
   }
   for (int t = 0; t < ntiles; ++t) {
     const int j0 = kv_begin + t * BLOCK_N;
-    bf16* Kt = Ks + (t & 1) * BLOCK_N * HS_PAD;
-    bf16* Vt = Vs + (t & 1) * BLOCK_N * HS_PAD;
-    if (t + 1 < ntiles) {
-      load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, j0 + BLOCK_N, kv_end,
-                                             Ks + ((t + 1) & 1) * BLOCK_N * HS_PAD,
-                                             Vs + ((t + 1) & 1) * BLOCK_N * HS_PAD);
+    const int stage = t % STAGES;
+    bf16* Kt = Ks + stage * BLOCK_N * HS_PAD;
+    bf16* Vt = Vs + stage * BLOCK_N * HS_PAD;
+    {
+      const int tn = t + STAGES - 1;            // refill the buffer that was read in iteration t - 1
+      if (tn < ntiles)
+        load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin + tn * BLOCK_N, kv_end,
+                                               Ks + (tn % STAGES) * BLOCK_N * HS_PAD,
+                                               Vs + (tn % STAGES) * BLOCK_N * HS_PAD);
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
     const int jw = j0 + warp * 16;          // this warp's 16 keys
     if (jw < kv_end) {
@@ -409,8 +368,9 @@ attn_decode_kernel(const AttnParams p) {
     }
     __syncthreads();
   }
+  cp_async_wait<0>();
 
-  // merge the warps: shared memory is free now. fm/fl [NWARPS][ROWS], fo [NWARPS][ROWS][HS_PAD + 1]
+  // merge the warps: shared memory is free now. fm/fl [NWARPS][ROWS], fo [NWARPS][ROWS][HS_PAD + 4]
   float* fm = reinterpret_cast<float*>(smem_raw);
   float* fl = fm + NWARPS * ROWS;
   float* fo = fl + NWARPS * ROWS;
@@ -433,6 +393,7 @@ attn_decode_kernel(const AttnParams p) {
     }
   __syncthreads();
   const int rows_used = min(ROWS, item.ntok * p.G);
+  const size_t slab0 = ((size_t)blockIdx.x * p.KV + g) * p.nsplit * ROWS;
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
     const int r = idx / p.hs, d = idx - r * p.hs;
     float M = -INFINITY;
@@ -446,42 +407,45 @@ attn_decode_kernel(const AttnParams p) {
       L += fl[w * ROWS + r] * wgt;
       acc += fo[((size_t)w * ROWS + r) * OS + d] * wgt;
     }
-    const int tok = r / p.G, hh = r - tok * p.G;
     if (p.nsplit == 1) {
+      const int tok = r / p.G, hh = r - tok * p.G;
       p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
           __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
-      const size_t slab = (((size_t)blockIdx.x * p.KV + g) * p.nsplit + split) * ROWS + r;
-      p.part_o[slab * p.hs + d] = acc;
-      if (d == 0) { p.part_ml[slab * 2] = M; p.part_ml[slab * 2 + 1] = L; }
+      const size_t slab = slab0 + (size_t)split * ROWS + r;
+      __stcg(p.part_o + slab * p.hs + d, acc);
+      if (d == 0) { __stcg(p.part_ml + slab * 2, M); __stcg(p.part_ml + slab * 2 + 1, L); }
     }
   }
-}
+  if (p.nsplit == 1) return;
 
-// Merge the splits of the decode kernel: one block per (item, kv head), as the reference's
-// combine kernel does per (token, head) (paged_kernels.cu:210-253).
-__global__ void attn_reduce_kernel(const AttnParams p, int rows_cap) {
-  const AttnItem item = p.items[blockIdx.x];
-  if (item.ntok <= 0) return;
-  const int g = blockIdx.y;
-  const int rows_used = min(rows_cap, item.ntok * p.G);
-  const size_t slab0 = ((size_t)blockIdx.x * p.KV + g) * p.nsplit * rows_cap;
-  for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += blockDim.x) {
+  // ticket: the last block of this (item, kv head) merges the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(p.counters + blockIdx.x * p.KV + g, 1);
+    s_last = ticket == p.nsplit - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
     const int r = idx / p.hs, d = idx - r * p.hs;
     float M = -INFINITY;
-    for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, p.part_ml[(slab0 + (size_t)s * rows_cap + r) * 2]);
+    for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slab0 + (size_t)s * ROWS + r) * 2));
     float L = 0.f, acc = 0.f;
     for (int s = 0; s < p.nsplit; ++s) {
-      const size_t slab = slab0 + (size_t)s * rows_cap + r;
-      const float ms = p.part_ml[slab * 2];
+      const size_t slab = slab0 + (size_t)s * ROWS + r;
+      const float ms = __ldcg(p.part_ml + slab * 2);
       const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += p.part_ml[slab * 2 + 1] * wgt;
-      acc += p.part_o[slab * p.hs + d] * wgt;
+      L += __ldcg(p.part_ml + slab * 2 + 1) * wgt;
+      acc += __ldcg(p.part_o + slab * p.hs + d) * wgt;
     }
     const int tok = r / p.G, hh = r - tok * p.G;
     p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
         __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
+  if (threadIdx.x == 0) p.counters[blockIdx.x * p.KV + g] = 0;      // ready for the next launch
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -505,7 +469,7 @@ static bool fill_params(AttnParams& p, const void* q, long long q_stride, const 
   p.block_table = block_table; p.table_width = table_width;
   p.items = (const AttnItem*)items;
   p.out = (bf16*)out; p.out_stride = out_stride;
-  p.part_o = nullptr; p.part_ml = nullptr;
+  p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
   p.num_pages = num_pages; p.page_size = page_size; p.num_seqs = num_seqs;
   p.H = H; p.KV = KV; p.G = H / KV; p.hs = hs;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -556,25 +520,26 @@ SI_EXPORT int si_attn_decode_rows(int H, int KV, int hs) {
   return (G <= 64 && need <= cap) ? need : 0;
 }
 
+// Scratch of the split decode kernel in 4-byte words: partial outputs, (max, sum) pairs and
+// one ticket counter per (item, kv head). It must be zero before its first use; the kernel
+// leaves the counters at zero.
 SI_EXPORT long long si_attn_decode_scratch_floats(int num_items, int H, int KV, int hs, int nsplit) {
   if (nsplit <= 1) return 0;
   const long long rows = si_attn_decode_rows(H, KV, hs);
-  return (long long)num_items * KV * nsplit * rows * (hs + 2);
+  return (long long)num_items * KV * nsplit * rows * (hs + 2) + (long long)num_items * KV;
 }
 
 template <int HS_PAD, int MT>
 static int launch_decode(AttnParams& p, int num_items, cudaStream_t stream) {
   constexpr int ROWS = 16 * MT;
-  size_t smem = (size_t)(ROWS + 4 * 64) * HS_PAD * sizeof(bf16);
+  constexpr int STAGES = HS_PAD <= 128 ? 3 : 2;
+  size_t smem = (size_t)(ROWS + 2 * STAGES * 64) * HS_PAD * sizeof(bf16);
   const size_t merge = (size_t)4 * ROWS * (2 + HS_PAD + 4) * sizeof(float);
   if (merge > smem) smem = merge;
-  auto k = attn_decode_kernel<HS_PAD, MT>;
+  auto k = attn_decode_kernel<HS_PAD, MT, STAGES>;
   int rc = set_smem(k, smem);
   if (rc) return rc;
   k<<<dim3(num_items, p.KV, p.nsplit), 128, smem, stream>>>(p);
-  rc = si_last_error();
-  if (rc || p.nsplit == 1) return rc;
-  attn_reduce_kernel<<<dim3(num_items, p.KV), 128, 0, stream>>>(p, ROWS);
   return si_last_error();
 }
 
@@ -596,6 +561,7 @@ SI_EXPORT int si_attn_decode(const void* q, long long q_stride, const void* k_ca
     if (!scratch) return -2;
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)num_items * KV * nsplit * rows * hs;
+    p.counters = reinterpret_cast<int*>(p.part_ml + (size_t)num_items * KV * nsplit * rows * 2);
   }
   if (hs <= 64) {
     if (rows == 16) return launch_decode<64, 1>(p, num_items, stream);

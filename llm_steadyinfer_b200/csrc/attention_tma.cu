@@ -1,0 +1,420 @@
+// Decode attention over the paged cache with the K/V tiles brought in by TMA.
+//
+// Same arithmetic as `attn_decode_kernel` (attention_mma.cu): 16*MT rows (tokens x query heads
+// of one KV head) shared by four warps, each warp taking 16 of the 64 keys of a tile, bf16
+// mma.sync with fp32 accumulation and fp32 online softmax, optional split of the key range over
+// blocks with the last block merging. What differs is how tiles reach shared memory: one page of
+// one KV head is a contiguous [page_size, head_dim] slab of the cache, so a 64-key tile is
+// 64 / page_size boxes per 64-column half of K and of V. One elected thread issues them as
+// `cp.async.bulk.tensor.2d` copies with the 128-byte swizzle (which is the XOR layout ldmatrix
+// wants) and an mbarrier per stage counts the bytes in. The other threads spend no instructions
+// on addresses, which the cp.async version pays about 400 of per thread and tile.
+//
+// Conditions: head_dim 64 or 128, page_size a power of two from 8 to 64, at most 32 rows per
+// item. Everything else stays with the cp.async kernel. Every wait on an mbarrier is bounded:
+// when it runs out the block reports SI_WAIT_LIMIT in the status word and leaves.
+#include "attention_common.cuh"
+#include <cuda.h>
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  for (int it = 0; it < (1 << 20); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Tile of NROWS rows stored as 64-column halves; inside a half, row r holds its eight 16-byte
+// chunks at positions chunk ^ (r % 8): the layout the 128-byte TMA swizzle writes.
+template <int NROWS>
+__device__ __forceinline__ bf16* half_tile_ptr(bf16* base, int row, int chunk) {
+  return base + (size_t)(chunk >> 3) * (NROWS * 64) + (size_t)row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+}
+
+template <int NH, int MT, int STAGES>
+__global__ void __launch_bounds__(128)
+attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
+                       const __grid_constant__ CUtensorMap vmap, int log2_page) {
+  constexpr int NWARPS = 4, THREADS = 128, BLOCK_N = 64, ROWS = 16 * MT, HS_PAD = NH * 64;
+  constexpr int KT = HS_PAD / 16, DT = HS_PAD / 8;
+  constexpr int TILE = NH * BLOCK_N * 64;             // elements of one K (or V) tile
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ int s_last;
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);     // [STAGES][TILE]
+  bf16* Vs = Ks + STAGES * TILE;
+  bf16* Qs = Vs + STAGES * TILE;                     // [NH][ROWS][64]
+
+  const AttnItem item = p.items[blockIdx.x];
+  if (item.ntok <= 0) return;
+  const int g = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (item.seq < 0 || item.seq >= p.num_seqs) {
+    if (threadIdx.x == 0) set_status(p.status, SI_BAD_SEQ);
+    return;
+  }
+  const int* table = p.block_table + (size_t)item.seq * p.table_width;
+  const int kv_end_all = item.pos0 + item.ntok;
+  int kv_begin_all = 0;
+  if (p.window > 0) kv_begin_all = max(0, item.pos0 - p.window + 1) / BLOCK_N * BLOCK_N;
+  const int tiles_all = (kv_end_all - kv_begin_all + BLOCK_N - 1) / BLOCK_N;
+  const int tiles_per = (tiles_all + p.nsplit - 1) / p.nsplit;
+  const int t_begin = split * tiles_per;
+  const int t_end = min(tiles_all, t_begin + tiles_per);
+  const int ntiles = max(0, t_end - t_begin);
+  const int kv_begin = kv_begin_all + t_begin * BLOCK_N;
+  const int kv_end = min(kv_end_all, kv_begin_all + t_end * BLOCK_N);
+  const int page_rows = 1 << log2_page;
+  const int pages_per_tile = BLOCK_N >> log2_page;
+
+  // Issue the boxes of tile t (keys kv_begin + 64 t ...) into its stage; pages past the last
+  // key are not fetched. Called by one thread.
+  auto issue_tile = [&](int t) {
+    const int stage = t % STAGES;
+    const int j = kv_begin + t * BLOCK_N;
+    int pages[8];
+    int valid = 0;
+#pragma unroll
+    for (int pg = 0; pg < 8; ++pg) {
+      pages[pg] = -1;
+      if (pg < pages_per_tile && j + pg * page_rows < kv_end) {
+        const int slot = (j >> log2_page) + pg;
+        const int page = slot < p.table_width ? table[slot] : -1;
+        if (page < 0 || page >= p.num_pages) set_status(p.status, SI_BAD_PAGE);
+        else { pages[pg] = page; ++valid; }
+      }
+    }
+    mbar_expect_tx(&full_bar[stage], (unsigned)(valid * 2 * NH * page_rows * 128));
+#pragma unroll
+    for (int pg = 0; pg < 8; ++pg) {
+      if (pages[pg] < 0) continue;
+      const int row = (pages[pg] * p.KV + g) << log2_page;
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        const size_t off = (size_t)stage * TILE + (size_t)h * (BLOCK_N * 64) + (size_t)(pg * page_rows) * 64;
+        tma_load_2d(Ks + off, &kmap, &full_bar[stage], h * 64, row);
+        tma_load_2d(Vs + off, &vmap, &full_bar[stage], h * 64, row);
+      }
+    }
+  };
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // Rows of the last tile that no copy fills must hold finite numbers (they meet zero
+  // probabilities): clear the stage the last tile lands in.
+  if (ntiles > 0 && (kv_end - kv_begin) % BLOCK_N != 0) {
+    const int stage = (ntiles - 1) % STAGES;
+    uint4* kz = reinterpret_cast<uint4*>(Ks + (size_t)stage * TILE);
+    uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
+    for (int i = threadIdx.x; i < TILE / 8; i += THREADS) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
+  }
+  // query rows: tile row r is token r / G, head g*G + r % G
+  for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += THREADS) {
+    const int row = id / (HS_PAD / 8), c = id % (HS_PAD / 8);
+    const int tok = row / p.G, hh = row - tok * p.G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tok < item.ntok && c * 8 < p.hs)
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
+    *reinterpret_cast<uint4*>(half_tile_ptr<ROWS>(Qs, row, c)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int t = 0; t < STAGES && t < ntiles; ++t) issue_tile(t);
+
+  float o[MT][DT][4];
+  float m[MT][2], l[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    m[mt][0] = m[mt][1] = -INFINITY; l[mt][0] = l[mt][1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DT; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
+  }
+  int pos_of[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      const int r = mt * 16 + (lane >> 2) + 8 * h2;
+      const int tok = r / p.G;
+      pos_of[mt][h2] = tok < item.ntok ? item.pos0 + tok : -1;
+    }
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int j0 = kv_begin + t * BLOCK_N;
+    const int stage = t % STAGES;
+    bf16* Kt = Ks + (size_t)stage * TILE;
+    bf16* Vt = Vs + (size_t)stage * TILE;
+    const bool arrived = mbar_wait(&full_bar[stage], (unsigned)((t / STAGES) & 1));
+    const int jw = j0 + warp * 16;          // this warp's 16 keys
+    if (arrived && jw < kv_end) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KT; ++kk) {
+          unsigned a0, a1, a2, a3, b0, b1, b2, b3;
+          ldsm_x4(a0, a1, a2, a3, half_tile_ptr<ROWS>(Qs, mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+          ldsm_x4(b0, b1, b2, b3, half_tile_ptr<BLOCK_N>(Kt, warp * 16 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+          mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+          mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+        }
+        float mx[2] = {m[mt][0], m[mt][1]};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = jw + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const int pos = pos_of[mt][e >> 1];
+            const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
+            const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
+            s[nt][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
+        float corr[2], base[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
+          mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
+          base[h2] = mx[h2] == -INFINITY ? 0.f : mx[h2];
+          corr[h2] = exp2f(m[mt][h2] - base[h2]);
+          m[mt][h2] = mx[h2];
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[nt][e] = exp2f(s[nt][e] - base[e >> 1]);
+            sum[e >> 1] += s[nt][e];
+          }
+        l[mt][0] = l[mt][0] * corr[0] + sum[0];
+        l[mt][1] = l[mt][1] * corr[1] + sum[1];
+        const unsigned a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
+        const unsigned a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dt = 0; dt < DT; dt += 2) {
+          o[mt][dt][0] *= corr[0]; o[mt][dt][1] *= corr[0]; o[mt][dt][2] *= corr[1]; o[mt][dt][3] *= corr[1];
+          o[mt][dt + 1][0] *= corr[0]; o[mt][dt + 1][1] *= corr[0]; o[mt][dt + 1][2] *= corr[1]; o[mt][dt + 1][3] *= corr[1];
+          unsigned b0, b1, b2, b3;
+          ldsm_x4_t(b0, b1, b2, b3, half_tile_ptr<BLOCK_N>(Vt, warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dt + (lane >> 4)));
+          mma_bf16(o[mt][dt], a0, a1, a2, a3, b0, b1);
+          mma_bf16(o[mt][dt + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+    // everyone is done with this stage (or someone's wait ran out: then all leave together)
+    if (!__syncthreads_and(arrived ? 1 : 0)) {
+      if (threadIdx.x == 0) set_status(p.status, SI_WAIT_LIMIT);
+      return;
+    }
+    if (threadIdx.x == 0 && t + STAGES < ntiles) issue_tile(t + STAGES);
+  }
+
+  // merge the warps through shared memory (all tiles have been consumed and none is in flight)
+  float* fm = reinterpret_cast<float*>(smem_raw);
+  float* fl = fm + NWARPS * ROWS;
+  float* fo = fl + NWARPS * ROWS;
+  constexpr int OS = HS_PAD + 4;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      float lv = l[mt][h2];
+      lv += __shfl_xor_sync(0xffffffffu, lv, 1);
+      lv += __shfl_xor_sync(0xffffffffu, lv, 2);
+      const int r = mt * 16 + (lane >> 2) + 8 * h2;
+      if ((lane & 3) == 0) { fm[warp * ROWS + r] = m[mt][h2]; fl[warp * ROWS + r] = lv; }
+#pragma unroll
+      for (int dt = 0; dt < DT; ++dt) {
+        const int d = dt * 8 + (lane & 3) * 2;
+        fo[((size_t)warp * ROWS + r) * OS + d] = o[mt][dt][h2 * 2];
+        fo[((size_t)warp * ROWS + r) * OS + d + 1] = o[mt][dt][h2 * 2 + 1];
+      }
+    }
+  __syncthreads();
+  const int rows_used = min(ROWS, item.ntok * p.G);
+  const size_t slab0 = ((size_t)blockIdx.x * p.KV + g) * p.nsplit * ROWS;
+  for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
+    const int r = idx / p.hs, d = idx - r * p.hs;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, fm[w * ROWS + r]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      const float mw = fm[w * ROWS + r];
+      const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += fl[w * ROWS + r] * wgt;
+      acc += fo[((size_t)w * ROWS + r) * OS + d] * wgt;
+    }
+    if (p.nsplit == 1) {
+      const int tok = r / p.G, hh = r - tok * p.G;
+      p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
+          __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const size_t slab = slab0 + (size_t)split * ROWS + r;
+      __stcg(p.part_o + slab * p.hs + d, acc);
+      if (d == 0) { __stcg(p.part_ml + slab * 2, M); __stcg(p.part_ml + slab * 2 + 1, L); }
+    }
+  }
+  if (p.nsplit == 1) return;
+
+  // ticket: the last block of this (item, kv head) merges the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(p.counters + blockIdx.x * p.KV + g, 1);
+    s_last = ticket == p.nsplit - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
+    const int r = idx / p.hs, d = idx - r * p.hs;
+    float M = -INFINITY;
+    for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slab0 + (size_t)s * ROWS + r) * 2));
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const size_t slab = slab0 + (size_t)s * ROWS + r;
+      const float ms = __ldcg(p.part_ml + slab * 2);
+      const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      L += __ldcg(p.part_ml + slab * 2 + 1) * wgt;
+      acc += __ldcg(p.part_o + slab * p.hs + d) * wgt;
+    }
+    const int tok = r / p.G, hh = r - tok * p.G;
+    p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
+        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+  if (threadIdx.x == 0) p.counters[blockIdx.x * p.KV + g] = 0;      // ready for the next launch
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+static int rows_for(int H, int KV) {
+  const int G = H / KV;
+  return G <= 16 ? 16 : (G <= 32 ? 32 : 0);
+}
+
+// 1 when the TMA decode kernel takes this layout.
+SI_EXPORT int si_attn_decode_tma_ok(int H, int KV, int hs, int page_size) {
+  if (KV <= 0 || H % KV) return 0;
+  if (hs != 64 && hs != 128) return 0;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return 0;
+  return rows_for(H, KV) > 0 && encode_fn() != nullptr;
+}
+
+SI_EXPORT int si_attn_decode_tma_rows(int H, int KV) { return rows_for(H, KV); }
+
+// Describe one layer's K (or V) cache, [num_pages, KV, page_size, hs] bf16, as the 2-D tensor
+// [num_pages * KV * page_size, hs] with boxes of [page_size, 64]. `map_out`: 128 bytes, 64-byte aligned.
+SI_EXPORT int si_attn_encode_cache_map(void* map_out, const void* cache, long long num_pages, int KV,
+                                       int page_size, int hs) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -3;
+  const cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)num_pages * KV * page_size};
+  const cuuint64_t strides[1] = {(cuuint64_t)hs * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  const cuuint32_t estr[2] = {1, 1};
+  if (dims[1] >= (1ull << 31)) return -2;
+  CUresult r = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+SI_EXPORT long long si_attn_decode_tma_scratch_floats(int num_items, int H, int KV, int hs, int nsplit) {
+  if (nsplit <= 1) return 0;
+  const long long rows = rows_for(H, KV);
+  return (long long)num_items * KV * nsplit * rows * (hs + 2) + (long long)num_items * KV;
+}
+
+template <int NH, int MT>
+static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap& vm, int num_items, int log2_page,
+                  cudaStream_t stream) {
+  constexpr int STAGES = 3, ROWS = 16 * MT, HS_PAD = NH * 64;
+  size_t smem = (size_t)(2 * STAGES * 64 + ROWS) * HS_PAD * sizeof(bf16);
+  const size_t merge = (size_t)4 * ROWS * (2 + HS_PAD + 4) * sizeof(float);
+  if (merge > smem) smem = merge;
+  smem += 1024;                                   // room to align the tiles to 1024 bytes
+  auto k = attn_decode_tma_kernel<NH, MT, STAGES>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  k<<<dim3(num_items, p.KV, p.nsplit), 128, smem, stream>>>(p, km, vm, log2_page);
+  return si_last_error();
+}
+
+// Same contract as si_attn_decode, with the tensor maps of this layer's K and V cache.
+SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                 const void* kmap, const void* vmap, const int* block_table, int table_width,
+                                 const void* items, int num_items, void* out, long long out_stride, int num_pages,
+                                 int page_size, int num_seqs, int H, int KV, int hs, float scale, int window,
+                                 int nsplit, float* scratch, int* status, cudaStream_t stream) {
+  if (num_items <= 0) return 0;
+  if (!si_attn_decode_tma_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
+  if ((q_stride % 8) || nsplit < 1 || nsplit > 65535) return -2;
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_table = block_table; p.table_width = table_width;
+  p.items = (const AttnItem*)items;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
+  p.num_pages = num_pages; p.page_size = page_size; p.num_seqs = num_seqs;
+  p.H = H; p.KV = KV; p.G = H / KV; p.hs = hs;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window; p.nsplit = nsplit; p.status = status;
+  const int rows = rows_for(H, KV);
+  if (nsplit > 1) {
+    if (!scratch) return -2;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)num_items * KV * nsplit * rows * hs;
+    p.counters = reinterpret_cast<int*>(p.part_ml + (size_t)num_items * KV * nsplit * rows * 2);
+  }
+  int log2_page = 0;
+  while ((1 << log2_page) < page_size) ++log2_page;
+  const CUtensorMap& km = *(const CUtensorMap*)kmap;
+  const CUtensorMap& vm = *(const CUtensorMap*)vmap;
+  if (hs == 64) return rows == 16 ? launch<1, 1>(p, km, vm, num_items, log2_page, stream)
+                                  : launch<1, 2>(p, km, vm, num_items, log2_page, stream);
+  return rows == 16 ? launch<2, 1>(p, km, vm, num_items, log2_page, stream)
+                    : launch<2, 2>(p, km, vm, num_items, log2_page, stream);
+}

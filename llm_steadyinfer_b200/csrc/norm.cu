@@ -5,7 +5,96 @@
 // argument, the residual stream is fp32, and sum of squares, mean and rsqrt are fp32.
 // With `rows` given, output row r is computed from stream row rows[r] and the stream
 // is left untouched (used to normalise only the rows whose logits are wanted).
+//
+// One block per row. When the width is a multiple of 8 every thread moves 8 elements at a
+// time with 16-byte loads (all loads of a row are in flight before the first use) and keeps
+// them in registers between the two passes; other widths take the scalar kernel, which
+// stages the row in shared memory.
 #include "common.cuh"
+
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+  float v[8];
+  __device__ __forceinline__ void load(const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  __device__ __forceinline__ void store(float* p) const {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  float v[8];
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+
+// CHUNKS: 8-element chunks per thread (hidden <= CHUNKS * 8 * blockDim.x)
+template <typename TX, typename TW, int CHUNKS>
+__global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
+                                       const int* __restrict__ rows, const TW* __restrict__ weight,
+                                       TX* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* h = resid + (size_t)src * hidden;
+  const TX* dl = delta ? delta + (size_t)src * hidden : nullptr;
+  const int nchunks = hidden >> 3;
+  Vec8<float> x[CHUNKS];
+  Vec8<TX> dv[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      x[c].load(h + ch * 8);
+      if (dl) dv[c].load(dl + ch * 8);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      if (dl) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[c].v[i] += dv[c].v[i];
+        if (!rows) x[c].store(h + ch * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[c].v[i] * x[c].v[i];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TX* o = out + (size_t)r * hidden;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      Vec8<TW> w;
+      w.load(weight + ch * 8);
+      Vec8<TX> y;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y.v[i] = w.v[i] * (x[c].v[i] * inv);
+      y.store(o + ch * 8);
+    }
+  }
+}
 
 template <typename TX, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
@@ -32,24 +121,31 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restri
     o[i] = from_f32<TX>(to_f32<TW>(weight[i]) * (row_cache[i] * inv));
 }
 
-template <typename TX>
-static int launch(float* resid, const void* delta, const int* rows, const void* weight,
-                  int weight_dtype, void* out, int num_rows, int hidden, float eps,
-                  cudaStream_t stream) {
+template <typename TX, typename TW>
+static int launch2(float* resid, const void* delta, const int* rows, const void* weight, void* out,
+                   int num_rows, int hidden, float eps, cudaStream_t stream) {
+  const TX* d = (const TX*)delta;
+  const TW* w = (const TW*)weight;
+  TX* o = (TX*)out;
+  const bool aligned = ((uintptr_t)resid % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
+                       ((uintptr_t)weight % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  if (hidden % 8 == 0 && aligned && hidden <= 4 * 8 * 512) {
+    const int nchunks = hidden / 8;
+    // threads: a multiple of 32 that covers the row in at most 4 passes
+    int threads = nchunks > 256 ? 512 : (nchunks > 128 ? 256 : 128);
+    if (num_rows >= 1024 && nchunks <= 1024) threads = min(threads, 256);   // many rows: more blocks per SM
+    const int per = (nchunks + threads - 1) / threads;
+    if (per <= 1) add_rmsnorm_vec_kernel<TX, TW, 1><<<num_rows, threads, 0, stream>>>(resid, d, rows, w, o, hidden, eps);
+    else if (per <= 2) add_rmsnorm_vec_kernel<TX, TW, 2><<<num_rows, threads, 0, stream>>>(resid, d, rows, w, o, hidden, eps);
+    else add_rmsnorm_vec_kernel<TX, TW, 4><<<num_rows, threads, 0, stream>>>(resid, d, rows, w, o, hidden, eps);
+    return si_last_error();
+  }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return -2;           // hidden too large for the row cache
-  if (weight_dtype == SI_BF16) {
-    auto k = add_rmsnorm_kernel<TX, __nv_bfloat16>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<num_rows, threads, smem, stream>>>(resid, (const TX*)delta, rows,
-                                           (const __nv_bfloat16*)weight, (TX*)out, hidden, eps);
-  } else {
-    auto k = add_rmsnorm_kernel<TX, float>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<num_rows, threads, smem, stream>>>(resid, (const TX*)delta, rows, (const float*)weight,
-                                           (TX*)out, hidden, eps);
-  }
+  auto k = add_rmsnorm_kernel<TX, TW>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  k<<<num_rows, threads, smem, stream>>>(resid, d, rows, w, o, hidden, eps);
   return si_last_error();
 }
 
@@ -58,7 +154,12 @@ SI_EXPORT int si_add_rmsnorm(float* resid, const void* delta, const int* rows, c
                              int weight_dtype, void* out, int x_dtype, int num_rows, int hidden,
                              float eps, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  if (x_dtype == SI_BF16)
-    return launch<__nv_bfloat16>(resid, delta, rows, weight, weight_dtype, out, num_rows, hidden, eps, stream);
-  return launch<float>(resid, delta, rows, weight, weight_dtype, out, num_rows, hidden, eps, stream);
+  if (x_dtype == SI_BF16) {
+    if (weight_dtype == SI_BF16)
+      return launch2<__nv_bfloat16, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
+    return launch2<__nv_bfloat16, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
+  }
+  if (weight_dtype == SI_BF16)
+    return launch2<float, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
+  return launch2<float, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
 }

@@ -280,7 +280,8 @@ def attn_decode(q, k_cache, v_cache, block_table, items, out, page_size: int, nu
                 hs: int, scale: float, window: int = 0, nsplit: int = 1, scratch=None, status=None) -> None:
     """Tensor-core attention for decode rows and short portions (at most
     ``attn_decode_rows // (H // KV)`` tokens an item). With ``nsplit`` > 1 the key range is split
-    over blocks and ``scratch`` (fp32, ``attn_decode_scratch_floats`` elements) holds the partials."""
+    over blocks and ``scratch`` (fp32, ``attn_decode_scratch_floats`` elements, zero before its
+    first use) holds the partials and the tickets of the merge."""
     _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_decode")
     if nsplit > 1:
         _cuda(scratch)
@@ -293,4 +294,65 @@ def attn_decode(q, k_cache, v_cache, block_table, items, out, page_size: int, nu
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(items), items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs,
              H, KV, hs, float(scale), int(window or 0), int(nsplit), _ptr(scratch), _ptr(status), _stream()),
-           f"attn_decode(heads={H}, kv_heads={KV}, head_dim={hs})", kernels=2 if nsplit > 1 else 1)
+           f"attn_decode(heads={H}, kv_heads={KV}, head_dim={hs})")
+
+
+# ---- decode attention with TMA-fed tiles ----------------------------------------------------
+
+_tensor_maps = {}
+
+
+def attn_decode_tma_ok(H: int, KV: int, hs: int, page_size: int) -> bool:
+    """True when the TMA decode kernel takes this head layout and page size."""
+    lib = build.load("attention_tma")
+    lib.si_attn_decode_tma_ok.restype = _c_int
+    return bool(lib.si_attn_decode_tma_ok(_c_int(H), _c_int(KV), _c_int(hs), _c_int(page_size)))
+
+
+def attn_decode_tma_rows(H: int, KV: int) -> int:
+    lib = build.load("attention_tma")
+    lib.si_attn_decode_tma_rows.restype = _c_int
+    return lib.si_attn_decode_tma_rows(_c_int(H), _c_int(KV))
+
+
+def attn_decode_tma_scratch_floats(num_items: int, H: int, KV: int, hs: int, nsplit: int) -> int:
+    lib = build.load("attention_tma")
+    lib.si_attn_decode_tma_scratch_floats.restype = _c_llr
+    return lib.si_attn_decode_tma_scratch_floats(_c_int(num_items), _c_int(H), _c_int(KV), _c_int(hs), _c_int(nsplit))
+
+
+def _cache_map(cache: torch.Tensor):
+    """The TMA descriptor of one layer's K or V cache; made once per tensor and kept."""
+    key = (cache.data_ptr(), tuple(cache.shape))
+    ent = _tensor_maps.get(key)
+    if ent is None:
+        raw = ctypes.create_string_buffer(128 + 64)
+        addr = (ctypes.addressof(raw) + 63) & ~63
+        num_pages, KV, page_size, hs = cache.shape
+        f = _fn("attention_tma", "si_attn_encode_cache_map", [_c_p, _c_p, _c_ll, _c_int, _c_int, _c_int])
+        rc = f(_c_p(addr), _ptr(cache), num_pages, KV, page_size, hs)
+        if rc != 0:
+            raise KernelError(f"cannot describe the cache {tuple(cache.shape)} to the TMA unit (code {rc})")
+        ent = (raw, addr)
+        _tensor_maps[key] = ent
+    return _c_p(ent[1])
+
+
+def attn_decode_tma(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int,
+                    hs: int, scale: float, window: int = 0, nsplit: int = 1, scratch=None, status=None) -> None:
+    """``attn_decode`` with the K/V tiles fetched by TMA (head_dim 64 or 128, page sizes 8 to 64);
+    items hold at most ``attn_decode_tma_rows // (H // KV)`` tokens."""
+    _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_decode_tma")
+    if nsplit > 1:
+        _cuda(scratch)
+        need = attn_decode_tma_scratch_floats(items.shape[0], H, KV, hs, nsplit)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need,
+              f"attn_decode_tma: scratch must hold {need} floats")
+    f = _fn("attention_tma", "si_attn_decode_tma",
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _cache_map(k_cache), _cache_map(v_cache),
+             _ptr(block_table), block_table.shape[1], _ptr(items), items.shape[0], _ptr(out), out.stride(0),
+             k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), int(nsplit),
+             _ptr(scratch), _ptr(status), _stream()),
+           f"attn_decode_tma(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")

@@ -1,5 +1,5 @@
 // Rotary position encoding fused with the write of K and V into the paged cache.
-// One block per token row of the fused projection output
+// One or more blocks per token row of the fused projection output
 //   row = [ q: H*hs | k: KV*hs | v: KV*hs ]            (row stride given in elements)
 // q is rotated in place; k is rotated and stored, v is stored, at
 //   cache[page = table[seq, pos / page_size]][kv head][pos % page_size][:]
@@ -10,6 +10,8 @@
 // the offset here is pos % page_size. inv_freq == nullptr stores k unrotated.
 #include "common.cuh"
 
+// Block (t, hb) handles heads [hb * hpb, (hb + 1) * hpb) of token t, counted over the q heads,
+// then the k heads, then the v heads; the host picks hpb so that few rows still fill the GPU.
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long row_stride,
                                      const int* __restrict__ positions,
@@ -18,16 +20,16 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long row_stride,
                                      const int* __restrict__ block_table, int table_width,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      int num_pages, int page_size, int num_seqs, int H, int KV,
-                                     int hs, int* status) {
+                                     int hs, int hpb, int* status) {
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int seq = row_seq[t];
   T* row = qkv + (size_t)t * row_stride;
-  T* krow = row + (size_t)H * hs;
-  T* vrow = krow + (size_t)KV * hs;
+  const int head_begin = blockIdx.y * hpb;
+  const int head_end = min(H + 2 * KV, head_begin + hpb);
 
   long long page = -1;
-  if (k_cache) {
+  if (k_cache && head_end > H) {
     if (seq < 0) {
       // a padding row of a fixed-shape step: nothing is stored
     } else if (seq >= num_seqs) {
@@ -43,16 +45,17 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long row_stride,
     }
   }
   const int off = pos % page_size;
-  const int half = rot_dim / 2;
+  const int half = (inv_freq ? rot_dim : 0) / 2;
+  const int rot = 2 * half;
   const float fpos = (float)pos;
 
-  // rotated pairs of q heads (in place) and k heads (to the cache)
-  const int pairs = inv_freq ? (H + KV) * half : 0;
-  for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
-    const int head = idx / half, i = idx - head * half;
+  // rotated pairs of the q heads (in place) and the k heads (to the cache)
+  const int rot_end = min(head_end, H + KV);
+  for (int idx = threadIdx.x; idx < (rot_end - head_begin) * half; idx += blockDim.x) {
+    const int head = head_begin + idx / half, i = idx % half;
     float s, c;
     sincosf(fpos * inv_freq[i], &s, &c);
-    T* x = head < H ? row + (size_t)head * hs : krow + (size_t)(head - H) * hs;
+    T* x = row + (size_t)head * hs;
     const float x0 = to_f32<T>(x[i]), x1 = to_f32<T>(x[i + half]);
     const T y0 = from_f32<T>(x0 * c - x1 * s);
     const T y1 = from_f32<T>(x1 * c + x0 * s);
@@ -67,15 +70,16 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long row_stride,
   }
   if (page < 0) return;
   // dims of k outside the rotated part, and all of v
-  const int rot = inv_freq ? rot_dim : 0;
   const int rest = hs - rot;
-  for (int idx = threadIdx.x; idx < KV * rest; idx += blockDim.x) {
-    const int g = idx / rest, c = rot + (idx - g * rest);
-    k_cache[(((size_t)page * KV + g) * page_size + off) * hs + c] = krow[(size_t)g * hs + c];
+  const int k_begin = max(head_begin, H), k_end = rot_end;
+  for (int idx = threadIdx.x; idx < (k_end - k_begin) * rest; idx += blockDim.x) {
+    const int g = k_begin - H + idx / rest, c = rot + idx % rest;
+    k_cache[(((size_t)page * KV + g) * page_size + off) * hs + c] = row[(size_t)(H + g) * hs + c];
   }
-  for (int idx = threadIdx.x; idx < KV * hs; idx += blockDim.x) {
-    const int g = idx / hs, c = idx - g * hs;
-    v_cache[(((size_t)page * KV + g) * page_size + off) * hs + c] = vrow[idx];
+  const int v_begin = max(head_begin, H + KV);
+  for (int idx = threadIdx.x; idx < (head_end - v_begin) * hs; idx += blockDim.x) {
+    const int g = v_begin - H - KV + idx / hs, c = idx % hs;
+    v_cache[(((size_t)page * KV + g) * page_size + off) * hs + c] = row[(size_t)(H + KV + g) * hs + c];
   }
 }
 
@@ -87,16 +91,23 @@ SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const
                                cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (rot_dim < 0 || rot_dim > hs || (rot_dim & 1)) return -2;
-  const int work = (H + 2 * KV) * hs / 2;
-  const int threads = work >= 2048 ? 256 : 128;
+  const int heads = H + 2 * KV;
+  // heads per block: all of them when there are many rows, fewer when rows alone cannot fill the GPU
+  int hpb = heads;
+  while (hpb > 1 && (long long)num_tokens * ((heads + hpb - 1) / hpb) < 592) hpb = (hpb + 1) / 2;
+  const int blocks_y = (heads + hpb - 1) / hpb;
+  if (blocks_y > 65535) return -2;
+  const int work = hpb * hs / 2;
+  const int threads = work >= 2048 ? 256 : (work >= 128 ? 128 : 64);
+  dim3 grid(num_tokens, blocks_y);
   if (dtype == SI_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table,
         table_width, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_pages, page_size,
-        num_seqs, H, KV, hs, status);
+        num_seqs, H, KV, hs, hpb, status);
   else
-    rope_kv_write_kernel<float><<<num_tokens, threads, 0, stream>>>(
+    rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table, table_width,
-        (float*)k_cache, (float*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, status);
+        (float*)k_cache, (float*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, hpb, status);
   return si_last_error();
 }

@@ -17,7 +17,8 @@ from .linear import linear
 
 
 USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
-TARGET_BLOCKS = 2 * 148      # blocks wanted in flight for decode attention
+USE_TMA = True               # decode tiles by TMA where the layout allows
+TARGET_BLOCKS = 2 * 148      # decode attention blocks that run at once
 MAX_SPLITS = 32
 MIN_TILES_PER_SPLIT = 2      # a split covers at least this many 64-key tiles
 
@@ -83,10 +84,12 @@ class Attention(Mixer):
         if not self.uses_tensor_cores():
             return
         key = ("attention", self.H, self.KV, self.hs)
-        if key in ctx.plans:
+        if key in ctx.plans or cache.k is None:
             return
         G = self.H // self.KV
-        dec_tokens = ops.attn_decode_rows(self.H, self.KV, self.hs) // G
+        tma = USE_TMA and ops.attn_decode_tma_ok(self.H, self.KV, self.hs, cache.page_size)
+        dec_rows = ops.attn_decode_tma_rows(self.H, self.KV) if tma else ops.attn_decode_rows(self.H, self.KV, self.hs)
+        dec_tokens = dec_rows // G
         por_tokens = ops.attn_portion_tokens(self.H, self.KV, self.hs)
         if por_tokens <= 0:
             raise ops.KernelError(f"attention: {G} query heads per kv head do not fit the tensor-core kernels")
@@ -101,13 +104,13 @@ class Attention(Mixer):
             else:
                 for b in range(0, n, por_tokens):
                     por.append((s, row0 + b, min(por_tokens, n - b), pos0 + b))
-        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None}
+        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma}
         n_dec = len(dec)
         if ctx.seq_cap is not None:                   # fixed shapes: pad with empty items
             dec += [(0, 0, 0, 0)] * (ctx.seq_cap - n_dec)
         if dec:
-            # enough blocks to fill the GPU when few sequences decode
-            nsplit = max(1, min(MAX_SPLITS, -(-TARGET_BLOCKS // (len(dec) * self.KV))))
+            # as many blocks as run at once (two per SM), not more: a second wave would wait
+            nsplit = max(1, min(MAX_SPLITS, TARGET_BLOCKS // (len(dec) * self.KV)))
             if ctx.seq_cap is None:
                 longest = max(d[3] + d[2] for d in dec)
                 nsplit = min(nsplit, max(1, -(-longest // (64 * MIN_TILES_PER_SPLIT))))
@@ -115,7 +118,8 @@ class Attention(Mixer):
             plan["dec"] = ctx.upload_ints(f"attn_dec_{self.H}_{self.KV}_{self.hs}",
                                           np.asarray(dec, dtype=np.int32)).view(-1, 4)
             if nsplit > 1:
-                n = ops.attn_decode_scratch_floats(len(dec), self.H, self.KV, self.hs, nsplit)
+                floats = ops.attn_decode_tma_scratch_floats if tma else ops.attn_decode_scratch_floats
+                n = floats(len(dec), self.H, self.KV, self.hs, nsplit)
                 plan["scratch"] = ctx.buf("attn_split", (n,), torch.float32)
         if por:
             plan["por"] = ctx.upload_ints(f"attn_por_{self.H}_{self.KV}_{self.hs}",
@@ -131,7 +135,8 @@ class Attention(Mixer):
         plan = ctx.plans[("attention", self.H, self.KV, self.hs)]
         args = (cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs, self.scale, self.window or 0)
         if plan["dec"] is not None:
-            ops.attn_decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,
+            decode = ops.attn_decode_tma if plan["tma"] else ops.attn_decode
+            decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,
                             nsplit=plan["nsplit"], scratch=plan["scratch"], status=ctx.status)
         if plan["por"] is not None:
             ops.attn_portion(q, cache.k, cache.v, cache.block_table, plan["por"], out, *args, status=ctx.status)

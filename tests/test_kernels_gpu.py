@@ -242,10 +242,12 @@ def _items_for(lengths, tails, dec_tokens, por_tokens):
     return dec, por, rows
 
 
-def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit):
+def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit, tma=False):
     o = ops()
     G = H // KV
-    dec_tokens = o.attn_decode_rows(H, KV, hs) // G
+    if tma and not o.attn_decode_tma_ok(H, KV, hs, page_size):
+        pytest.skip("the TMA decode kernel does not take this layout")
+    dec_tokens = (o.attn_decode_tma_rows(H, KV) if tma else o.attn_decode_rows(H, KV, hs)) // G
     por_tokens = o.attn_portion_tokens(H, KV, hs)
     dec, por, rows = _items_for(lengths, tails, dec_tokens, por_tokens)
     q = torch.stack([seqs[s][0][p].reshape(-1) for s, p in rows]).to(torch.bfloat16).to(DEV)
@@ -256,10 +258,12 @@ def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size,
     if dec:
         items = torch.tensor(dec, dtype=torch.int32, device=DEV)
         scratch = None
+        floats = o.attn_decode_tma_scratch_floats if tma else o.attn_decode_scratch_floats
         if nsplit > 1:
-            scratch = torch.empty(o.attn_decode_scratch_floats(len(dec), H, KV, hs, nsplit), device=DEV)
-        o.attn_decode(q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0,
-                      nsplit=nsplit, scratch=scratch, status=status)
+            scratch = torch.zeros(floats(len(dec), H, KV, hs, nsplit), device=DEV)
+        (o.attn_decode_tma if tma else o.attn_decode)(
+            q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0,
+            nsplit=nsplit, scratch=scratch, status=status)
     if por:
         items = torch.tensor(por, dtype=torch.int32, device=DEV)
         o.attn_portion(q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0, status=status)
@@ -270,13 +274,15 @@ def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size,
 @pytest.mark.parametrize("H,KV,hs,page_size,window", [
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, None), (8, 2, 128, 16, None), (32, 8, 128, 16, None),
     (5, 5, 80, 32, 7), (2, 1, 256, 16, 40), (32, 1, 64, 16, None), (40, 1, 128, 16, None), (24, 8, 128, 16, 100),
-    (14, 2, 64, 64, None), (9, 3, 96, 16, 65)])
+    (14, 2, 64, 64, None), (9, 3, 96, 16, 65), (8, 8, 64, 8, None), (20, 1, 128, 32, 200), (16, 2, 64, 16, 70)])
 @pytest.mark.parametrize("nsplit", [1, 3])
-def test_attention_tensor_cores(H, KV, hs, page_size, window, nsplit):
+@pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
+def test_attention_tensor_cores(H, KV, hs, page_size, window, nsplit, tma):
     lengths = [1, 37, 130, 700, 64, 129]
     tails = [1, 1, 3, 700, 64, 2]           # decode rows, short runs, a whole long prompt, an exact tile
     seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page_size, seed=8)
-    out, rows, used_dec, used_por = _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit)
+    out, rows, used_dec, used_por = _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window,
+                                                      nsplit, tma)
     assert used_por
     scale = 1.0 / math.sqrt(hs)
     full = [plain_llama.attention(q.double(), k.double(), v.double(), scale, window) for q, k, v in seqs]
@@ -314,8 +320,10 @@ def test_attention_finds_one_far_key(hs, page_size):
             kc[table[0, b], :, :m] = seqs[0][1][b * page_size:b * page_size + m].transpose(0, 1)
             vc[table[0, b], :, :m] = seqs[0][2][b * page_size:b * page_size + m].transpose(0, 1)
         kc, vc = kc.to(torch.bfloat16), vc.to(torch.bfloat16)
-        for tails, nsplit in (([1], 1), ([1], 4), ([n], 1)):
-            out, rows, _, _ = _run_tc_attention(seqs, table, kc, vc, [n], tails, H, KV, hs, page_size, None, nsplit)
+        for tails, nsplit, tma in (([1], 1, False), ([1], 4, False), ([n], 1, False), ([1], 1, True), ([1], 4, True)):
+            if tma and not ops().attn_decode_tma_ok(H, KV, hs, page_size):
+                continue
+            out, rows, _, _ = _run_tc_attention(seqs, table, kc, vc, [n], tails, H, KV, hs, page_size, None, nsplit, tma)
             for r, (s, p) in enumerate(rows):
                 if p not in (n - 1, n - 5) or target > p:
                     continue
@@ -343,9 +351,55 @@ def test_attention_window_edge():
             m = min(page_size, n - b * page_size)
             kc[b, :, :m] = seqs[0][1][b * page_size:b * page_size + m].transpose(0, 1)
             vc[b, :, :m] = seqs[0][2][b * page_size:b * page_size + m].transpose(0, 1)
-        for tails in ([1], [n]):
+        for tails, tma in (([1], False), ([n], False), ([1], True)):
             out, rows, _, _ = _run_tc_attention(seqs, table, kc.to(torch.bfloat16), vc.to(torch.bfloat16), [n], tails,
-                                                H, KV, hs, page_size, window, 1)
+                                                H, KV, hs, page_size, window, 1, tma)
             got = out[-1].view(H, hs)
             hit = (got - seqs[0][2][target].double()).abs().max().item() < 0.02
             assert hit == visible, (target, tails)
+
+
+@pytest.mark.parametrize("batch,ctx,nsplit", [(8, 8192, 4), (64, 2048, 1)])
+@pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
+def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
+    """Decode rows at the Llama-3.1-8B head layout over long contexts (a cache larger than L2):
+    the tensor-core kernel against the plain kernel, and its achieved bandwidth (printed)."""
+    o = ops()
+    H, KV, hs, page_size = 32, 8, 128, 16
+    g = torch.Generator(device=DEV).manual_seed(11)
+    blocks = -(-ctx // page_size)
+    num_pages = batch * blocks
+    kc = torch.randn(num_pages, KV, page_size, hs, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    vc = torch.randn(num_pages, KV, page_size, hs, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    table = torch.randperm(num_pages, generator=g, device=DEV).to(torch.int32).view(batch, blocks)
+    q = torch.randn(batch, H * hs, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    lens = [ctx - 3 * i for i in range(batch)]
+    items = torch.tensor([(s, s, 1, lens[s] - 1) for s in range(batch)], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    rseq = torch.arange(batch, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    want = torch.empty_like(q)
+    o.paged_attention_ref(q, kc, vc, table, rseq, pos, want, page_size, batch, H, KV, hs, scale, 0, status)
+    out = torch.empty_like(q)
+    floats = o.attn_decode_tma_scratch_floats if tma else o.attn_decode_scratch_floats
+    scratch = torch.zeros(max(1, floats(batch, H, KV, hs, nsplit)), device=DEV)
+    decode = o.attn_decode_tma if tma else o.attn_decode
+    run = lambda: decode(q, kc, vc, table, items, out, page_size, batch, H, KV, hs, scale, 0,
+                         nsplit=nsplit, scratch=scratch if nsplit > 1 else None, status=status)
+    run()
+    assert status.item() == 0
+    assert (out.float() - want.float()).abs().max().item() <= 2 ** -8 * 4       # outputs of size up to ~4 in bf16
+    for _ in range(3):
+        run()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(10):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 100
+    gbs = sum(lens) * KV * hs * 2 * 2 / (us * 1e-6) / 1e9
+    print(f"attn_decode {'tma' if tma else 'cp.async'} batch {batch} ctx {ctx} nsplit {nsplit}: {us:.1f} us, "
+          f"{gbs:.0f} GB/s of cache read")
