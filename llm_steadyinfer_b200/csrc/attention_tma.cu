@@ -7,8 +7,11 @@
 // one KV head is a contiguous [page_size, head_dim] slab of the cache, so a 64-key tile is
 // 64 / page_size boxes per 64-column half of K and of V. One elected thread issues them as
 // `cp.async.bulk.tensor.2d` copies with the 128-byte swizzle (which is the XOR layout ldmatrix
-// wants) and an mbarrier per stage counts the bytes in. The other threads spend no instructions
-// on addresses, which the cp.async version pays about 400 of per thread and tile.
+// wants). A fifth warp is the producer: its lanes look up the pages and issue the boxes of a tile,
+// one box a lane, as soon as the four consumer warps have released the stage (`empty` mbarrier);
+// a `full` mbarrier per stage counts the bytes in. The consumer warps spend no instructions on
+// addresses, which the cp.async version pays about 400 of per thread and tile, and never meet
+// at a block-wide barrier inside the loop.
 //
 // Conditions: head_dim 64 or 128, page_size a power of two from 8 to 64, at most 32 rows per
 // item. Everything else stays with the cp.async kernel. Every wait on an mbarrier is bounded:
@@ -27,6 +30,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
   asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait: false when the phase did not complete within the limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
@@ -47,15 +53,17 @@ __device__ __forceinline__ bf16* half_tile_ptr(bf16* base, int row, int chunk) {
 }
 
 template <int NH, int MT, int STAGES>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(160)
 attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                        const __grid_constant__ CUtensorMap vmap, int log2_page) {
-  constexpr int NWARPS = 4, THREADS = 128, BLOCK_N = 64, ROWS = 16 * MT, HS_PAD = NH * 64;
+  constexpr int NWARPS = 4, THREADS = 128, BLOCK_N = 64, ROWS = 16 * MT, HS_PAD = NH * 64;   // consumer warps/threads
   constexpr int KT = HS_PAD / 16, DT = HS_PAD / 8;
   constexpr int TILE = NH * BLOCK_N * 64;             // elements of one K (or V) tile
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ int s_last;
+  __shared__ int s_abort;
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   bf16* Ks = reinterpret_cast<bf16*>(smem_raw);     // [STAGES][TILE]
   bf16* Vs = Ks + STAGES * TILE;
@@ -83,40 +91,10 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   const int page_rows = 1 << log2_page;
   const int pages_per_tile = BLOCK_N >> log2_page;
 
-  // Issue the boxes of tile t (keys kv_begin + 64 t ...) into its stage; pages past the last
-  // key are not fetched. Called by one thread.
-  auto issue_tile = [&](int t) {
-    const int stage = t % STAGES;
-    const int j = kv_begin + t * BLOCK_N;
-    int pages[8];
-    int valid = 0;
-#pragma unroll
-    for (int pg = 0; pg < 8; ++pg) {
-      pages[pg] = -1;
-      if (pg < pages_per_tile && j + pg * page_rows < kv_end) {
-        const int slot = (j >> log2_page) + pg;
-        const int page = slot < p.table_width ? table[slot] : -1;
-        if (page < 0 || page >= p.num_pages) set_status(p.status, SI_BAD_PAGE);
-        else { pages[pg] = page; ++valid; }
-      }
-    }
-    mbar_expect_tx(&full_bar[stage], (unsigned)(valid * 2 * NH * page_rows * 128));
-#pragma unroll
-    for (int pg = 0; pg < 8; ++pg) {
-      if (pages[pg] < 0) continue;
-      const int row = (pages[pg] * p.KV + g) << log2_page;
-#pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        const size_t off = (size_t)stage * TILE + (size_t)h * (BLOCK_N * 64) + (size_t)(pg * page_rows) * 64;
-        tma_load_2d(Ks + off, &kmap, &full_bar[stage], h * 64, row);
-        tma_load_2d(Vs + off, &vmap, &full_bar[stage], h * 64, row);
-      }
-    }
-  };
-
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NWARPS); }
+    s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   // Rows of the last tile that no copy fills must hold finite numbers (they meet zero
@@ -125,10 +103,10 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     const int stage = (ntiles - 1) % STAGES;
     uint4* kz = reinterpret_cast<uint4*>(Ks + (size_t)stage * TILE);
     uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
-    for (int i = threadIdx.x; i < TILE / 8; i += THREADS) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
+    for (int i = threadIdx.x; i < TILE / 8; i += blockDim.x) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
   }
   // query rows: tile row r is token r / G, head g*G + r % G
-  for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += THREADS) {
+  for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += blockDim.x) {
     const int row = id / (HS_PAD / 8), c = id % (HS_PAD / 8);
     const int tok = row / p.G, hh = row - tok * p.G;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -138,8 +116,36 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   __syncthreads();
-  if (threadIdx.x == 0)
-    for (int t = 0; t < STAGES && t < ntiles; ++t) issue_tile(t);
+
+  if (warp == NWARPS) {
+    // ---- producer warp: lane l fetches box (page l / (2 NH), half (l / 2) % NH, K or V) of each tile
+    const int boxes = pages_per_tile * NH * 2;
+    const int pg = lane / (2 * NH), h = (lane >> 1) % NH, is_v = lane & 1;
+    for (int t = 0; t < ntiles; ++t) {
+      const int stage = t % STAGES;
+      const int j = kv_begin + t * BLOCK_N;
+      int page = -1;
+      if (lane < boxes && j + pg * page_rows < kv_end) {       // pages past the last key are not fetched
+        const int slot = (j >> log2_page) + pg;
+        page = slot < p.table_width ? table[slot] : -1;
+        if (page < 0 || page >= p.num_pages) { set_status(p.status, SI_BAD_PAGE); page = -1; }
+      }
+      const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
+      bool ok = true;
+      if (t >= STAGES) ok = mbar_wait(&empty_bar[stage], (unsigned)(((t / STAGES) - 1) & 1));
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
+        break;
+      }
+      if (lane == 0) mbar_expect_tx(&full_bar[stage], (unsigned)(__popc(have) * page_rows * 128));
+      __syncwarp();
+      if (page >= 0) {
+        const int row = (page * p.KV + g) << log2_page;
+        const size_t off = (size_t)stage * TILE + (size_t)h * (BLOCK_N * 64) + (size_t)(pg * page_rows) * 64;
+        tma_load_2d((is_v ? Vs : Ks) + off, is_v ? &vmap : &kmap, &full_bar[stage], h * 64, row);
+      }
+    }
+  }
 
   float o[MT][DT][4];
   float m[MT][2], l[MT][2];
@@ -159,14 +165,18 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
       pos_of[mt][h2] = tok < item.ntok ? item.pos0 + tok : -1;
     }
 
-  for (int t = 0; t < ntiles; ++t) {
+  for (int t = 0; warp < NWARPS && t < ntiles; ++t) {
     const int j0 = kv_begin + t * BLOCK_N;
     const int stage = t % STAGES;
     bf16* Kt = Ks + (size_t)stage * TILE;
     bf16* Vt = Vs + (size_t)stage * TILE;
     const bool arrived = mbar_wait(&full_bar[stage], (unsigned)((t / STAGES) & 1));
+    if (!__all_sync(0xffffffffu, arrived)) {
+      if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
+      break;
+    }
     const int jw = j0 + warp * 16;          // this warp's 16 keys
-    if (arrived && jw < kv_end) {
+    if (jw < kv_end) {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         float s[2][4];
@@ -224,13 +234,12 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
         }
       }
     }
-    // everyone is done with this stage (or someone's wait ran out: then all leave together)
-    if (!__syncthreads_and(arrived ? 1 : 0)) {
-      if (threadIdx.x == 0) set_status(p.status, SI_WAIT_LIMIT);
-      return;
-    }
-    if (threadIdx.x == 0 && t + STAGES < ntiles) issue_tile(t + STAGES);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[stage]);      // this warp is done with the stage
   }
+  __syncthreads();
+  if (s_abort) return;              // a bounded wait ran out somewhere: the status word says so
+  if (warp == NWARPS) return;       // the producer has nothing to merge
 
   // merge the warps through shared memory (all tiles have been consumed and none is in flight)
   float* fm = reinterpret_cast<float*>(smem_raw);
@@ -253,7 +262,7 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
         fo[((size_t)warp * ROWS + r) * OS + d + 1] = o[mt][dt][h2 * 2 + 1];
       }
     }
-  __syncthreads();
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
   const int rows_used = min(ROWS, item.ntok * p.G);
   const size_t slab0 = ((size_t)blockIdx.x * p.KV + g) * p.nsplit * ROWS;
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
@@ -283,12 +292,12 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
 
   // ticket: the last block of this (item, kv head) merges the splits
   __threadfence();
-  __syncthreads();
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
   if (threadIdx.x == 0) {
     const int ticket = atomicAdd(p.counters + blockIdx.x * p.KV + g, 1);
     s_last = ticket == p.nsplit - 1;
   }
-  __syncthreads();
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
   if (!s_last) return;
   __threadfence();
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
@@ -378,7 +387,7 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  k<<<dim3(num_items, p.KV, p.nsplit), 128, smem, stream>>>(p, km, vm, log2_page);
+  k<<<dim3(num_items, p.KV, p.nsplit), 160, smem, stream>>>(p, km, vm, log2_page);
   return si_last_error();
 }
 
