@@ -95,6 +95,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed region of --section with cudaProfilerStart/Stop "
+                         "(for ncu --profile-from-start off)")
     ap.add_argument("--section", default="all", choices=["all", "decode", "prefill"],
                     help="run only the device-timed decode steps or only the prefill (for profiling)")
     args = ap.parse_args()
@@ -143,12 +146,16 @@ def main() -> int:
 
     def timed(fn, n):
         torch.cuda.synchronize()
+        if args.profiler_range:
+            torch.cuda.cudart().cudaProfilerStart()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for i in range(n):
             fn(i)
         b.record()
         torch.cuda.synchronize()
+        if args.profiler_range:
+            torch.cuda.cudart().cudaProfilerStop()
         return a.elapsed_time(b)
 
     clocks = ClockSampler()

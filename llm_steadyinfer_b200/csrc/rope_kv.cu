@@ -83,6 +83,88 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long row_stride,
   }
 }
 
+// bf16 with 16-byte accesses: thread (head lane, chunk c) owns elements [8c, 8c+8) of the first
+// and of the second half of the rotated part; it forms the 8 sines and cosines once and walks
+// its heads with them. Same block-to-heads mapping as the scalar kernel.
+__global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride,
+                                         const int* __restrict__ positions, const int* __restrict__ row_seq,
+                                         const float* __restrict__ inv_freq, int rot_dim,
+                                         const int* __restrict__ block_table, int table_width,
+                                         __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                         int num_pages, int page_size, int num_seqs, int H, int KV, int hs,
+                                         int hpb, int* status) {
+  typedef __nv_bfloat16 T;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int seq = row_seq[t];
+  T* row = qkv + (size_t)t * row_stride;
+  const int head_begin = blockIdx.y * hpb;
+  const int head_end = min(H + 2 * KV, head_begin + hpb);
+  long long page = -1;
+  if (k_cache && head_end > H) {
+    if (seq < 0) {
+    } else if (seq >= num_seqs) {
+      if (threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+    } else {
+      const int slot = pos / page_size;
+      const int p = (pos >= 0 && slot < table_width) ? block_table[(size_t)seq * table_width + slot] : -1;
+      if (p < 0 || p >= num_pages) {
+        if (threadIdx.x == 0) set_status(status, SI_BAD_PAGE);
+      } else {
+        page = p;
+      }
+    }
+  }
+  const int off = pos % page_size;
+  const int half = rot_dim / 2;
+  const int cpr = half / 8;                       // chunks per half
+  const int lanes_h = blockDim.x / cpr;           // head lanes
+  const int c = threadIdx.x % cpr, hl = threadIdx.x / cpr;
+  const int rot_end = min(head_end, H + KV);
+  if (hl < lanes_h && head_begin + hl < rot_end) {
+    float sn[8], cs[8];
+    const float fpos = (float)pos;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sincosf(fpos * inv_freq[c * 8 + i], &sn[i], &cs[i]);
+    for (int head = head_begin + hl; head < rot_end; head += lanes_h) {
+      T* x = row + (size_t)head * hs;
+      uint4 lo = *reinterpret_cast<const uint4*>(x + c * 8);
+      uint4 hi = *reinterpret_cast<const uint4*>(x + half + c * 8);
+      __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(l2[i]), b = __bfloat1622float2(h2[i]);
+        l2[i] = __floats2bfloat162_rn(a.x * cs[2 * i] - b.x * sn[2 * i], a.y * cs[2 * i + 1] - b.y * sn[2 * i + 1]);
+        h2[i] = __floats2bfloat162_rn(b.x * cs[2 * i] + a.x * sn[2 * i], b.y * cs[2 * i + 1] + a.y * sn[2 * i + 1]);
+      }
+      if (head < H) {
+        *reinterpret_cast<uint4*>(x + c * 8) = lo;
+        *reinterpret_cast<uint4*>(x + half + c * 8) = hi;
+      } else if (page >= 0) {
+        T* dst = k_cache + (((size_t)page * KV + (head - H)) * page_size + off) * hs;
+        *reinterpret_cast<uint4*>(dst + c * 8) = lo;
+        *reinterpret_cast<uint4*>(dst + half + c * 8) = hi;
+      }
+    }
+  }
+  if (page < 0) return;
+  // dims of k outside the rotated part (8 at a time), and all of v
+  const int rest8 = (hs - rot_dim) / 8, hs8 = hs / 8;
+  const int k_begin = max(head_begin, H), k_end = rot_end;
+  for (int idx = threadIdx.x; idx < (k_end - k_begin) * rest8; idx += blockDim.x) {
+    const int g = k_begin - H + idx / rest8, cc = rot_dim + (idx % rest8) * 8;
+    *reinterpret_cast<uint4*>(k_cache + (((size_t)page * KV + g) * page_size + off) * hs + cc) =
+        *reinterpret_cast<const uint4*>(row + (size_t)(H + g) * hs + cc);
+  }
+  const int v_begin = max(head_begin, H + KV);
+  for (int idx = threadIdx.x; idx < (head_end - v_begin) * hs8; idx += blockDim.x) {
+    const int g = v_begin - H - KV + idx / hs8, cc = (idx % hs8) * 8;
+    *reinterpret_cast<uint4*>(v_cache + (((size_t)page * KV + g) * page_size + off) * hs + cc) =
+        *reinterpret_cast<const uint4*>(row + (size_t)(H + KV + g) * hs + cc);
+  }
+}
+
 SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const int* positions,
                                const int* row_seq, const float* inv_freq, int rot_dim,
                                const int* block_table, int table_width, void* k_cache,
@@ -100,6 +182,19 @@ SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const
   const int work = hpb * hs / 2;
   const int threads = work >= 2048 ? 256 : (work >= 128 ? 128 : 64);
   dim3 grid(num_tokens, blocks_y);
+  const bool vec = dtype == SI_BF16 && inv_freq && rot_dim >= 16 && rot_dim % 16 == 0 && hs % 8 == 0 &&
+                   row_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) &&
+                   ((uintptr_t)v_cache % 16 == 0);
+  if (vec) {
+    const int cpr = rot_dim / 16;
+    int vthreads = 256;
+    while (vthreads > 32 && vthreads / cpr > hpb && vthreads / 2 >= cpr) vthreads /= 2;
+    if (vthreads < cpr) vthreads = ((cpr + 31) / 32) * 32;
+    rope_kv_write_vec_kernel<<<grid, vthreads, 0, stream>>>(
+        (__nv_bfloat16*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table, table_width,
+        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, hpb, status);
+    return si_last_error();
+  }
   if (dtype == SI_BF16)
     rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table,

@@ -91,7 +91,13 @@ class ScheduledItem:
 
     @property
     def tokens(self) -> List[int]:
-        return self.seq.tokens[self.start:self.start + self.count]
+        seq, a, b = self.seq, self.start, self.start + self.count
+        n = len(seq.prompt)
+        if b <= n:
+            return seq.prompt[a:b]
+        if a >= n:
+            return seq.outputs[a - n:b - n]
+        return seq.prompt[a:] + seq.outputs[:b - n]
 
 
 class RequestRejected(ValueError):
