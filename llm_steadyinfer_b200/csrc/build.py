@@ -45,11 +45,23 @@ def _nvcc() -> str:
                      "the CUDA kernels of this package cannot be built")
 
 
+def _included_sources(name: str) -> List[str]:
+    """Other .cu files that <name>.cu pulls in with #include "x.cu"."""
+    out = []
+    with open(os.path.join(CSRC_DIR, name + ".cu"), "r", encoding="utf-8") as f:
+        for line in f:
+            line = line.strip()
+            if line.startswith("#include") and line.endswith('.cu"'):
+                out.append(line.split('"')[1])
+    return out
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
+    own = [name + ".cu"] + _included_sources(name)
     for fn in sorted(os.listdir(CSRC_DIR)):
-        if fn == name + ".cu" or fn.endswith(".cuh") or fn.endswith(".h"):
+        if fn in own or fn.endswith(".cuh") or fn.endswith(".h"):
             with open(os.path.join(CSRC_DIR, fn), "rb") as f:
                 h.update(fn.encode())
                 h.update(f.read())
