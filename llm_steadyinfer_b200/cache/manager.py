@@ -53,8 +53,8 @@ class RequestCache:
 
 
 class CacheLayout:
-    """Groups layers by their cache need. ``cache_from[i]`` names the layer whose cache layer i
-    reads instead of owning one."""
+    """Groups the places of the run order ("layers" below) by their cache need.
+    ``cache_from[i]`` names the place whose cache place i reads instead of owning one."""
 
     def __init__(self, needs: Sequence[Optional[CacheNeed]], states: Sequence[Optional[StateNeed]],
                  cache_from: Optional[Sequence[Optional[int]]] = None):
@@ -85,6 +85,9 @@ class CacheLayout:
                 raise ValueError(f"layer {i} reads the cache of layer {src}, which owns none")
             if needs[i] is None or needs[i].group_key()[:3] != needs[src].group_key()[:3]:
                 raise ValueError(f"layer {i} cannot read layer {src}'s cache: their head layouts differ")
+            sw, rw = needs[src].window, needs[i].window
+            if sw is not None and (rw is None or rw > sw):
+                raise ValueError(f"layer {i} would read further back than layer {src}'s window of {sw} keeps")
             self.layer_group[i] = self.layer_group[src]
             self.layer_index_in_group[i] = self.layer_index_in_group[src]
 

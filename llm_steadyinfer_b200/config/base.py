@@ -57,7 +57,8 @@ class LayerSpec:
 
     ``weight_prefix`` is the checkpoint prefix of this layer ("model.layers.3.").
     ``cache_from`` is None when the layer owns its cache, or the index of the layer
-    whose cache it reads (it then writes nothing).
+    whose cache it reads (it then writes nothing): that of the latest run of that layer
+    before it in the run order.
     """
     mixer: MixerSpec
     feed_forward: FeedForwardSpec

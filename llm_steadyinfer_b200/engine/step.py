@@ -109,9 +109,21 @@ class ModelRunner:
         self.model = model
         self.device = model.device
         spec = model.spec
-        self.layout = CacheLayout([b.mixer.cache_need() for b in model.blocks],
-                                  [b.mixer.state_need() for b in model.blocks],
-                                  [ls.cache_from for ls in spec.layers])
+        # Caches and state belong to the places of the run order: a layer that runs twice keeps a
+        # cache per run; "cache_from = j" reads the cache of the latest earlier run of layer j.
+        order = spec.order
+        cache_from = []
+        for o, i in enumerate(order):
+            src = spec.layers[i].cache_from
+            if src is None:
+                cache_from.append(None)
+                continue
+            earlier = [o2 for o2 in range(o) if order[o2] == src]
+            if not earlier:
+                raise StepError(f"layer {i} reads the cache of layer {src}, which does not run before it")
+            cache_from.append(earlier[-1])
+        self.layout = CacheLayout([model.blocks[i].mixer.cache_need() for i in order],
+                                  [model.blocks[i].mixer.state_need() for i in order], cache_from)
         self.manager = CacheManager(self.layout, page_size, num_pages, max_requests, prefix_reuse)
         self.storage = CacheStorage(self.layout, self.manager, model.dtype, self.device)
         self.page_size = page_size

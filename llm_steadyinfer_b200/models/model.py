@@ -86,18 +86,19 @@ class Model:
     def prepare(self, ctx, caches) -> None:
         """Host-side planning of the parts for this step (work lists, uploads); runs before
         ``forward`` and also before a captured step is replayed."""
-        for i in sorted(set(self.spec.order)):
-            self.blocks[i].mixer.prepare(ctx, caches[i])
+        for o, i in enumerate(self.spec.order):
+            self.blocks[i].mixer.prepare(ctx, caches[o])
 
     def forward(self, ctx, caches) -> Optional[torch.Tensor]:
         """Run the step's rows through all layers; returns fp32 logits [R, vocab] for
-        ``ctx.logit_rows`` or None when no row is wanted. ``caches[i]`` is layer i's view."""
+        ``ctx.logit_rows`` or None when no row is wanted. ``caches[o]`` is the view of the o-th
+        place in the run order (a layer that runs twice has a cache per run)."""
         T, d = ctx.num_tokens, self.spec.hidden_size
         resid = ctx.buf("resid", (T, d), torch.float32)
         ops.embedding_gather(ctx.tokens, self.embed, resid, status=ctx.status)
         delta = None
-        for i in self.spec.order:
-            delta = self.blocks[i].forward(resid, delta, ctx, caches[i])
+        for o, i in enumerate(self.spec.order):
+            delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
         R = ctx.num_logit_rows
         if R == 0:
             return None
