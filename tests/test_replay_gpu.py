@@ -99,3 +99,56 @@ def test_trace_run_program(folders, plains, tmp_path):
                 assert (got[r].double() - ref).abs().max().item() <= ATOL[torch.float32]
                 r += 1
             pos[e["id"]] = base + len(e["tokens"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_long_decoding(folders, plains, dtype):
+    """A short prompt, then 450 tokens one by one (given tokens, every row compared): positions far
+    beyond the original range of the scaled rotary frequencies, many page edges."""
+    name = "B"
+    cfg = CONFIGS[name][0]
+    reqs = {"long": ru.random_tokens(cfg["vocab_size"], 460, 77)}
+    steps = ru.trace_tail(reqs, tail=450)
+    rp = replayer(folders[name], name, dtype, 512)
+    worst = ru.compare(rp, steps, reqs, plains[name], ATOL[dtype], f"long decode {dtype}")
+    assert len(steps) == 451
+    print(f"long decoding {dtype}: worst difference {worst:.2e}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_one_by_one(folders, plains, name, dtype):
+    """A sequence fed from its very first token in single-token steps, beside another that starts
+    two steps later: position 0, the first page, the first page edge."""
+    cfg, _, page = CONFIGS[name]
+    reqs = {"p": ru.random_tokens(cfg["vocab_size"], 2 * page + 3, 5), "q": ru.random_tokens(cfg["vocab_size"], page + 2, 6)}
+    steps = []
+    for i in range(len(reqs["p"])):
+        entries = [{"id": "p", "tokens": [reqs["p"][i]], "want": [0]}]
+        j = i - 2
+        if 0 <= j < len(reqs["q"]):
+            entries.append({"id": "q", "tokens": [reqs["q"][j]], "want": [0]})
+        end = [r for r, k in (("p", i), ("q", j)) if k == len(reqs[r]) - 1]
+        steps.append({"step": i, "entries": entries, "end": end})
+    rp = replayer(folders[name], name, dtype, 256)
+    ru.compare(rp, steps, reqs, plains[name], ATOL[dtype], f"first tokens {name} {dtype}")
+    assert not rp.runner.manager.requests
+
+
+def test_step_rejects_what_it_cannot_hold(folders):
+    """Too many tokens for the pool: one clear error, nothing taken, and the engine goes on."""
+    from llm_steadyinfer_b200.cache import OutOfPages
+    from llm_steadyinfer_b200.engine.step import StepError
+    rp = replayer(folders["A"], "A", torch.float32, 64)
+    toks = ru.random_tokens(512, 60, 1)
+    rp.run_step([{"id": "a", "tokens": toks[:40], "want": []}], [])
+    with pytest.raises(OutOfPages):
+        rp.run_step([{"id": "b", "tokens": toks[:40], "want": []}], [])
+    assert rp.runner.manager.free_pages(0) == 1 and rp.runner.manager.table(0, "b") == []
+    with pytest.raises(StepError):
+        rp.run_step([{"id": "a", "tokens": [1], "want": [3]}], [])
+    with pytest.raises(StepError):
+        rp.run_step([{"id": "a", "tokens": [999999], "want": [0]}], [])      # outside the vocabulary: flagged
+    rp.run_step([], ["a", "b"])
+    rp.runner.manager.check_invariant()
+    assert rp.runner.manager.free_pages(0) == 4
