@@ -118,6 +118,7 @@ class CacheManager:
         if self.prefix_reuse:
             self.groups[0].pool.on_evict = self._forget_page
         self.new_slots: List[int] = []     # slots admitted since the storage last zeroed state
+        self.versions: Dict[Hashable, int] = {}     # bumped whenever a request's tables change
 
     # ---- queries -------------------------------------------------------------------
     def has(self, req) -> bool:
@@ -157,6 +158,7 @@ class CacheManager:
             raise OutOfSlots(f"all {self.slots.num_slots} state slots are in use")
         rc = RequestCache(slot=slot)
         self.requests[req] = rc
+        self.versions[req] = 0
         self.new_slots.append(slot)
         for g in self.groups:
             g.tables[req] = []
@@ -179,7 +181,9 @@ class CacheManager:
         for m, g in zip(missing, self.groups):
             got = g.pool.allocate(m)
             assert got is not None
-            g.tables[req].extend(got)
+            if got:
+                g.tables[req].extend(got)
+                self.versions[req] += 1
 
     def commit(self, req, new_length: int) -> None:
         """The request now holds ``new_length`` tokens; windowed groups give back the pages
@@ -196,6 +200,7 @@ class CacheManager:
                 if t[b] >= 0:
                     g.pool.release(t[b])
                     t[b] = -1
+                    self.versions[req] += 1
 
     def can_truncate_to(self, keep_length: int) -> int:
         """Preemption keeps a whole number of pages; with windows or fixed-size state nothing
@@ -217,6 +222,7 @@ class CacheManager:
                     self._release(g, p)
             del t[nb:]
         rc.length = keep
+        self.versions[req] += 1
         rc.shared_pages = min(rc.shared_pages, nb)
         if keep == 0:
             self.new_slots.append(rc.slot)           # state starts over
@@ -225,6 +231,7 @@ class CacheManager:
     def release(self, req) -> None:
         """The request has ended: all its pages and its slot go back."""
         rc = self.requests.pop(req)
+        self.versions.pop(req, None)
         for g in self.groups:
             for p in g.tables.pop(req):
                 if p >= 0:

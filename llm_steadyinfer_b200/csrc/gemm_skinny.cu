@@ -1,0 +1,139 @@
+// Matrix product for few rows (decode): out[m, n] = sum_k x[m, k] * W[n, k], M <= 16, bf16
+// inputs, fp32 accumulation, bf16 or fp32 output. At these sizes the product is a stream of the
+// weight matrix through the SMs; the reference sends it to cuBLAS like every other product
+// (src/source/op/kernels/cuda/matmul_kernel.cu:128-150). Here the weights go from global memory
+// straight into the A fragments of mma.sync m16n8k16 (rows of W are the 16 "m" of the
+// instruction, the rows of x its 8 "n"), 16 bytes per lane and load, without a pass through
+// shared memory:
+//   lane (g, t) loads W[n0 + g][k .. k+8) and W[n0 + g + 8][k .. k+8) with k = 32 c + 8 t, and
+//   x[g][k .. k+8). The sum over k does not care in which order k is visited, so the 8
+//   consecutive k of a lane are fed as logical columns (2t, 2t+1, 2t+8, 2t+9) of two mma steps,
+//   the same mapping for A and B.
+// A block owns 16 output columns; its warps take the 32-wide k chunks in turn (adjacent warps
+// read adjacent 64 bytes of a row) and their partial sums are added in a fixed order.
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TO> __device__ __forceinline__ void store_out(TO* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ uint4 ld_stream(const bf16* p) {      // weights: read once, keep out of L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached(const bf16* p) {      // x: small, shared by every block
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Rows of W or x beyond N or M are replaced by row 0: their products land in output elements
+// that are never stored, so the loads need no predicate.
+template <int MT, int WARPS, int UNROLL, typename TO>
+__global__ void __launch_bounds__(WARPS * 32, 512 / (WARPS * 32))
+gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W, long long ldw,
+                   TO* __restrict__ out, long long ldo, int M, int N, int K) {
+  __shared__ float red[WARPS][MT][32][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const bf16* w0 = W + (size_t)(n0 + g < N ? n0 + g : 0) * ldw + t * 8;
+  const bf16* w1 = W + (size_t)(n0 + g + 8 < N ? n0 + g + 8 : 0) * ldw + t * 8;
+  const bf16* xr[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) xr[mt] = x + (size_t)(mt * 8 + g < M ? mt * 8 + g : 0) * ldx + t * 8;
+  float acc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+
+  const int full = K >> 5;                      // whole 32-wide chunks
+  int c = warp;
+  for (; c + (UNROLL - 1) * WARPS < full; c += WARPS * UNROLL) {
+    uint4 a_lo[UNROLL], a_hi[UNROLL], xb[UNROLL][MT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (c + u * WARPS) * 32;
+      a_lo[u] = ld_stream(w0 + k);
+      a_hi[u] = ld_stream(w1 + k);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) xb[u][mt] = ld_cached(xr[mt] + k);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma16816(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, xb[u][mt].x, xb[u][mt].y);
+        mma16816(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, xb[u][mt].z, xb[u][mt].w);
+      }
+  }
+  // what is left: whole chunks one at a time, then the part of a chunk (K is a multiple of 8).
+  // Lanes past the end load nothing and feed zeros; every lane of the warp issues the same mma
+  // (mma.sync must not sit in a divergent branch).
+  const int nchunks = (K + 31) >> 5;
+  for (; c < nchunks; c += WARPS) {
+    const int k = c * 32;
+    const bool in = k + t * 8 < K;
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, xv[MT];
+    if (in) { lo = ld_stream(w0 + k); hi = ld_stream(w1 + k); }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      xv[mt] = make_uint4(0, 0, 0, 0);
+      if (in) xv[mt] = ld_cached(xr[mt] + k);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      mma16816(acc[mt], lo.x, hi.x, lo.y, hi.y, xv[mt].x, xv[mt].y);
+      mma16816(acc[mt], lo.z, hi.z, lo.w, hi.w, xv[mt].z, xv[mt].w);
+    }
+  }
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) red[warp][mt][lane][e] = acc[mt][e];
+  __syncthreads();
+  // threads (mt, lane, e) add the warps' partial sums in warp order and store
+  for (int idx = threadIdx.x; idx < MT * 32 * 4; idx += WARPS * 32) {
+    const int mt = idx / 128, ln = (idx >> 2) & 31, e = idx & 3;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) s += red[w][mt][ln][e];
+    const int n = n0 + (ln >> 2) + ((e >> 1) ? 8 : 0);
+    const int m = mt * 8 + (ln & 3) * 2 + (e & 1);
+    if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, s);
+  }
+}
+
+// Largest M this kernel takes.
+SI_EXPORT int si_gemm_skinny_max_rows() { return 16; }
+
+// out_dtype: SI_BF16 or SI_F32. Returns -2 when the sizes or alignments are not supported.
+SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
+                             int out_dtype, int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -2;
+  if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
+  constexpr int WARPS = 8, UNROLL = 8;
+  const unsigned blocks = (unsigned)((N + 15) / 16);
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  if (out_dtype == SI_BF16) {
+    if (M <= 8) gemm_skinny_kernel<1, WARPS, UNROLL, bf16><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
+    else gemm_skinny_kernel<2, WARPS, UNROLL, bf16><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
+  } else {
+    if (M <= 8) gemm_skinny_kernel<1, WARPS, UNROLL, float><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
+    else gemm_skinny_kernel<2, WARPS, UNROLL, float><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
+  }
+  return si_last_error();
+}

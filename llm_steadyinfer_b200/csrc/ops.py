@@ -356,3 +356,29 @@ def attn_decode_tma(q, k_cache, v_cache, block_table, items, out, page_size: int
              k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), int(nsplit),
              _ptr(scratch), _ptr(status), _stream()),
            f"attn_decode_tma(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")
+
+
+# ---- few-row matrix product (decode) ----------------------------------------------------------
+
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny_ok(a, w, out) -> bool:
+    """True when the few-row kernel takes these tensors (bf16, at most 16 rows, K a multiple of 8)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and a.shape[0] <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and out.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a, w, out) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weights stream through mma.sync fragments."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm_skinny: shapes")
+    _need(gemm_skinny_ok(a, w, out), "gemm_skinny: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_skinny", "si_gemm_skinny",
+            [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _dt(out), M, N, K, _stream()),
+           f"gemm_skinny(M={M}, N={N}, K={K})")

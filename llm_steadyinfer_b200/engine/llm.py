@@ -117,8 +117,8 @@ class LLM:
             self.runner.check_status()
             return {}
         rows = [(it.seq.params, it.seq.seed, len(it.seq.outputs)) for it in wanted]
-        tokens = self.sampler.to_host(self.sampler.sample(logits, rows))
-        self.runner.check_status()
+        tokens, code = self.sampler.to_host(self.sampler.sample(logits, rows), status=self.runner.status)
+        self.runner.raise_status(code)
         self.stats["tokens_out"] += len(tokens)
         return {it.seq.id: t for it, t in zip(wanted, tokens)}
 

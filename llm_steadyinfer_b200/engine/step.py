@@ -137,6 +137,7 @@ class ModelRunner:
         G = max(1, len(self.manager.groups))
         T, S, W = self.max_step_tokens, max_requests, self.max_width
         self._stage = _PinnedRing(4 * (T + 4) + 3 * (S + 4) + 8 + G * S * W, self.device)
+        self._table_arrays: Dict[Tuple[int, Hashable], Tuple[int, np.ndarray]] = {}
         self._graphs: Dict[Tuple[int, int], dict] = {}
         self._generation = 0              # bumped when a captured address may have changed
         self.ctx = StepContext(self)
@@ -331,8 +332,8 @@ class ModelRunner:
         tabs[:] = -1
         for g in range(G):
             for s, e in enumerate(entries):
-                t = mgr.table(g, e.req)
-                tabs[g, s, :len(t)] = t
+                t = self._table_array(g, e.req)
+                tabs[g, s, :t.size] = t
         self._stage.send(o)
         self.h2d_bytes_last_step = 4 * o       # parts add their uploads in prepare()
 
@@ -354,6 +355,24 @@ class ModelRunner:
         dtabs = dev[table_off:table_off + G * S_cap * W_cap].view(G, S_cap, W_cap)
         self._tables = [dtabs[g] for g in range(G)]
         return ctx
+
+    def _table_array(self, group: int, req) -> np.ndarray:
+        """A request's block table as an int32 array, rebuilt only when the table has changed."""
+        mgr = self.manager
+        version = mgr.versions[req]
+        ent = self._table_arrays.get((group, req))
+        if ent is None or ent[0] != version:
+            ent = (version, np.asarray(mgr.table(group, req), dtype=np.int32))
+            if len(self._table_arrays) > 8 * self.max_requests + 64:       # forget requests that have ended
+                self._table_arrays = {k: v for k, v in self._table_arrays.items() if mgr.has(k[1])}
+            self._table_arrays[(group, req)] = ent
+        return ent[1]
+
+    def raise_status(self, code: int) -> None:
+        """Turn a non-zero status word (already read) into an error and clear the word."""
+        if code:
+            self.status.zero_()
+            raise StepError(f"a kernel reported status {code}: {STATUS_TEXT.get(code, 'unknown')}")
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel reported a fault (it never traps)."""

@@ -1,8 +1,9 @@
 """Matrix products of the parts: ``out[M, N] = x[M, K] @ w[N, K]^T``.
 
 fp32 tensors go through this package's own FFMA kernel (true 32-bit, no reduced-precision
-mode). bf16 tensors go to the cuBLAS GEMM behind ``torch.mm`` with fp32 accumulation, as the
-reference sends every projection and the LM head to ``cublasGemmEx``
+mode). bf16 products of at most 16 rows (decode) go through the package's weight-streaming
+kernel (``gemm_skinny.cu``). Other bf16 products go to the cuBLAS GEMM behind ``torch.mm`` with
+fp32 accumulation, as the reference sends every projection and the LM head to ``cublasGemmEx``
 (src/source/op/kernels/cuda/matmul_kernel.cu:128-150).
 """
 from __future__ import annotations
@@ -10,6 +11,9 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+
+
+USE_SKINNY = True      # few-row products (decode) through this package's weight-streaming kernel
 
 
 def configure_library_gemm() -> None:
@@ -23,6 +27,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise ops.KernelError("linear: CUDA tensors only; there is no CPU path")
     if x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32:
         ops.gemm_f32(x, w, out)
+    elif USE_SKINNY and ops.gemm_skinny_ok(x, w, out):
+        ops.gemm_skinny(x, w, out)
     elif x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

@@ -21,6 +21,7 @@ class Sampler:
         self._dev = torch.empty(max_rows * 8, dtype=torch.int32, device=self.device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, int, int]]) -> torch.Tensor:
         """``rows[r] = (params, seed, index of the output token)``; returns int32 [R] on the device."""
@@ -46,9 +47,14 @@ class Sampler:
                    counter=d[6 * n:6 * n + 2 * R].view(torch.int64))
         return out
 
-    def to_host(self, tokens: torch.Tensor) -> List[int]:
-        """Device-to-host read of the sampled ids (synchronises the stream)."""
+    def to_host(self, tokens: torch.Tensor, status: torch.Tensor = None):
+        """Device-to-host read of the sampled ids (synchronises the stream). With ``status`` (the
+        engine's int32 status word) both travel before the one synchronisation and
+        ``(ids, status code)`` is returned."""
         R = tokens.numel()
         self._out_host[:R].copy_(tokens, non_blocking=True)
+        if status is not None:
+            self._status_host.copy_(status, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return self._out_host[:R].tolist()
+        ids = self._out_host[:R].tolist()
+        return ids if status is None else (ids, int(self._status_host[0]))

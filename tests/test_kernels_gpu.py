@@ -403,3 +403,57 @@ def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
     gbs = sum(lens) * KV * hs * 2 * 2 / (us * 1e-6) / 1e9
     print(f"attn_decode {'tma' if tma else 'cp.async'} batch {batch} ctx {ctx} nsplit {nsplit}: {us:.1f} us, "
           f"{gbs:.0f} GB/s of cache read")
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (3, 513, 320), (8, 200, 1336), (16, 64, 16), (9, 37, 8), (5, 4096, 4096)])
+def test_gemm_skinny(M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(12)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops().gemm_skinny(a, w, out)
+    want = a.double() @ w.double().T
+    tol = 1e-4 * math.sqrt(K) if out_dtype == torch.float32 else 2 ** -8 * want.abs().max().item()
+    assert (out.double() - want).abs().max().item() <= tol
+    # a row does not depend on the rows beside it; a strided view of x works
+    wide = torch.zeros(M, K + 24, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = a
+    one = torch.empty(1, N, dtype=out_dtype, device=DEV)
+    ops().gemm_skinny(wide[M - 1:M, :K], w, one)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def test_gemm_skinny_at_serving_size():
+    """The four projections of the Llama-3.1-8B block at 8 rows: achieved weight bandwidth (printed)
+    beside the library product."""
+    g = torch.Generator(device=DEV).manual_seed(13)
+    for name, N, K in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+        a = torch.randn(8, K, generator=g, device=DEV).to(torch.bfloat16)
+        # several copies of the weight so that consecutive runs do not find it in L2
+        ws = [(0.02 * torch.randn(N, K, generator=g, device=DEV)).to(torch.bfloat16) for _ in range(4)]
+        out = torch.empty(8, N, dtype=torch.bfloat16, device=DEV)
+        res = {}
+        for label, fn in (("skinny", lambda w: ops().gemm_skinny(a, w, out)), ("library", lambda w: torch.mm(a, w.t(), out=out))):
+            for w in ws:
+                fn(w)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()           # replayed from a graph: the host's launch cost stays out
+            with torch.cuda.graph(graph):
+                for _ in range(5):
+                    for w in ws:
+                        fn(w)
+            graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            res[label] = e0.elapsed_time(e1) * 1e3 / 20
+        want = a.double() @ ws[-1].double().T
+        ops().gemm_skinny(a, ws[-1], out)
+        assert (out.double() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item()
+        mb = N * K * 2 / 1e6
+        print(f"{name}: skinny {res['skinny']:.1f} us ({mb / res['skinny']:.2f} TB/s), "
+              f"library {res['library']:.1f} us ({mb / res['library']:.2f} TB/s)")
