@@ -17,33 +17,7 @@
 // item. Everything else stays with the cp.async kernel. Every wait on an mbarrier is bounded:
 // when it runs out the block reports SI_WAIT_LIMIT in the status word and leaves.
 #include "attention_common.cuh"
-#include <cuda.h>
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false when the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  for (int it = 0; it < (1 << 20); ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
+#include "tma_common.cuh"
 
 // Tile of NROWS rows stored as 64-column halves; inside a half, row r holds its eight 16-byte
 // chunks at positions chunk ^ (r % 8): the layout the 128-byte TMA swizzle writes.
@@ -320,22 +294,6 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
 }
 
 // ---- host side --------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
 static int rows_for(int H, int KV) {
   const int G = H / KV;
   return G <= 16 ? 16 : (G <= 32 ? 32 : 0);
@@ -346,7 +304,7 @@ SI_EXPORT int si_attn_decode_tma_ok(int H, int KV, int hs, int page_size) {
   if (KV <= 0 || H % KV) return 0;
   if (hs != 64 && hs != 128) return 0;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return 0;
-  return rows_for(H, KV) > 0 && encode_fn() != nullptr;
+  return rows_for(H, KV) > 0 && si_encode_fn() != nullptr;
 }
 
 SI_EXPORT int si_attn_decode_tma_rows(int H, int KV) { return rows_for(H, KV); }
@@ -355,17 +313,10 @@ SI_EXPORT int si_attn_decode_tma_rows(int H, int KV) { return rows_for(H, KV); }
 // [num_pages * KV * page_size, hs] with boxes of [page_size, 64]. `map_out`: 128 bytes, 64-byte aligned.
 SI_EXPORT int si_attn_encode_cache_map(void* map_out, const void* cache, long long num_pages, int KV,
                                        int page_size, int hs) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -3;
-  const cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)num_pages * KV * page_size};
-  const cuuint64_t strides[1] = {(cuuint64_t)hs * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
-  const cuuint32_t estr[2] = {1, 1};
-  if (dims[1] >= (1ull << 31)) return -2;
-  CUresult r = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+  const unsigned long long rows = (unsigned long long)num_pages * KV * page_size;
+  if (rows >= (1ull << 31)) return -2;
+  return si_encode_bf16_2d((CUtensorMap*)map_out, cache, rows, (unsigned long long)hs, (unsigned long long)hs,
+                           (unsigned)page_size);
 }
 
 SI_EXPORT long long si_attn_decode_tma_scratch_floats(int num_items, int H, int KV, int hs, int nsplit) {

@@ -382,3 +382,43 @@ def gemm_skinny(a, w, out) -> None:
             [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _dt(out), M, N, K, _stream()),
            f"gemm_skinny(M={M}, N={N}, K={K})")
+
+
+# ---- tcgen05 matrix product (many rows) -------------------------------------------------------
+
+_weight_maps = {}
+
+
+def gemm_tc05_ok(a, w, out) -> bool:
+    """True when the tcgen05 kernel takes these tensors (bf16, K a multiple of 8, aligned rows)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and a.shape[1] % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def _weight_map(w: torch.Tensor):
+    key = (w.data_ptr(), tuple(w.shape), w.stride(0))
+    ent = _weight_maps.get(key)
+    if ent is None:
+        raw = ctypes.create_string_buffer(128 + 64)
+        addr = (ctypes.addressof(raw) + 63) & ~63
+        f = _fn("gemm_tc05", "si_gemm_tc05_encode_weight", [_c_p, _c_p, _c_int, _c_int, _c_ll])
+        rc = f(_c_p(addr), _ptr(w), w.shape[0], w.shape[1], w.stride(0))
+        if rc != 0:
+            raise KernelError(f"cannot describe the weight {tuple(w.shape)} to the TMA unit (code {rc})")
+        ent = (raw, addr)
+        _weight_maps[key] = ent
+    return _c_p(ent[1])
+
+
+def gemm_tc05(a, w, out, status=None) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory)."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm_tc05: shapes")
+    _need(gemm_tc05_ok(a, w, out), "gemm_tc05: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_tc05", "si_gemm_tc05",
+            [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), _ptr(out), out.stride(0), _dt(out), M, N, K, _ptr(status),
+             _stream()), f"gemm_tc05(M={M}, N={N}, K={K})")

@@ -457,3 +457,21 @@ def test_gemm_skinny_at_serving_size():
         mb = N * K * 2 / 1e6
         print(f"{name}: skinny {res['skinny']:.1f} us ({mb / res['skinny']:.2f} TB/s), "
               f"library {res['library']:.1f} us ({mb / res['library']:.2f} TB/s)")
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (256, 384, 512), (200, 1000, 320), (33, 96, 1336),
+                                   (1, 128, 64), (2048, 512, 4096)])
+def test_gemm_tc05(M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(14)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().gemm_tc05(a, w, out, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    want = a.double() @ w.double().T
+    tol = 1e-4 * math.sqrt(K) if out_dtype == torch.float32 else 2 ** -8 * want.abs().max().item()
+    assert not torch.isnan(out).any()
+    assert (out.double() - want).abs().max().item() <= tol
