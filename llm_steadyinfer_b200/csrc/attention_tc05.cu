@@ -1,0 +1,306 @@
+// Attention for prompt portions on the 5th-generation tensor cores (tcgen05), bf16, over the
+// paged cache. One block handles one work item (a run of consecutive query tokens of a sequence)
+// for one KV head: 128 rows = tokens x the G query heads of the KV head (row r = token r / G,
+// head r % G), against key tiles of 128.
+//
+//   warp 4 (producer)  looks up the pages of a tile and issues its K and V boxes by TMA
+//                      (128-byte swizzle) into one of two stages;
+//   warp 5 (issuer)    S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major), then, once the
+//                      probabilities are in shared memory, T = P V (V is the MN-major operand, as
+//                      it lies in the cache), each completion signalled by tcgen05.commit;
+//   warps 0-3          one thread per row: read the row of S from tensor memory (tcgen05.ld), mask,
+//                      online softmax in fp32 (exp2 of scale*log2e-scaled scores), write the bf16
+//                      probabilities into the swizzled P tile, then add the tile's T row into the
+//                      fp32 accumulators kept in registers, rescaled by the change of the maximum.
+//
+// The reference computes prompt attention row by row with its scalar split kernel
+// (src/source/op/kernels/cuda/paged_kernels.cu:96-206). Conditions here: head_dim 64 or 128, page size
+// a power of two from 8 to 64, G <= 128; other layouts use the mma.sync kernel. Every mbarrier wait
+// is bounded; when one runs out the block sets SI_WAIT_LIMIT and leaves without storing.
+#include "attention_common.cuh"
+#include "tma_common.cuh"
+
+template <int NROWS>
+__device__ __forceinline__ bf16* half_ptr(bf16* base, int row, int chunk) {
+  return base + (size_t)(chunk >> 3) * (NROWS * 64) + (size_t)row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+}
+
+template <int NH>
+__global__ void __launch_bounds__(192)
+attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
+                         const __grid_constant__ CUtensorMap vmap, int log2_page) {
+  constexpr int BM = 128, BN = 128, HS = NH * 64, STAGES = 2;
+  constexpr int TILE = NH * BN * 64;                 // elements of a K (or V) tile: NH halves of [128][64]
+  constexpr int TM_S = 0, TM_T = BN;                 // tensor-memory columns of S and of T = P V
+  constexpr int TM_COLS = 256;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t kv_full[STAGES], kv_empty[STAGES];
+  __shared__ __align__(8) uint64_t s_full, p_full, t_full;
+  __shared__ unsigned tmem_slot;
+  __shared__ int s_abort;
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [NH][128][64]
+  bf16* Ps = Qs + BM * HS;                           // [2][128][64]   (keys 0-63, 64-127)
+  bf16* Ks = Ps + BM * BN;                           // [STAGES][TILE]
+  bf16* Vs = Ks + STAGES * TILE;
+
+  const AttnItem item = p.items[blockIdx.x];
+  if (item.ntok <= 0) return;
+  const int g = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (item.seq < 0 || item.seq >= p.num_seqs) {
+    if (threadIdx.x == 0) set_status(p.status, SI_BAD_SEQ);
+    return;
+  }
+  const int* table = p.block_table + (size_t)item.seq * p.table_width;
+  const int kv_end = item.pos0 + item.ntok;
+  int kv_begin = 0;
+  if (p.window > 0) kv_begin = max(0, item.pos0 - p.window + 1) / BN * BN;
+  const int ntiles = (kv_end - kv_begin + BN - 1) / BN;
+  const int page_rows = 1 << log2_page;
+  const int pages_per_tile = BN >> log2_page;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(&s_full, 1);
+    mbar_init(&p_full, 128);
+    mbar_init(&t_full, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) tmem_alloc(&tmem_slot, TM_COLS);
+  // rows of the last tile that no copy fills must hold finite numbers (they meet zero probabilities)
+  if ((kv_end - kv_begin) % BN != 0) {
+    const int stage = (ntiles - 1) % STAGES;
+    uint4* kz = reinterpret_cast<uint4*>(Ks + (size_t)stage * TILE);
+    uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
+    for (int i = threadIdx.x; i < TILE / 8; i += blockDim.x) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
+  }
+  // query rows: tile row r is token r / G, head g*G + r % G
+  for (int id = threadIdx.x; id < BM * (HS / 8); id += blockDim.x) {
+    const int row = id / (HS / 8), c = id % (HS / 8);
+    const int tok = row / p.G, hh = row - tok * p.G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tok < item.ntok)
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
+    *reinterpret_cast<uint4*>(half_ptr<BM>(Qs, row, c)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  tc05_fence_before_sync();
+  __syncthreads();
+  tc05_fence_after_sync();
+  const unsigned tmem = tmem_slot;
+
+  if (warp == 4) {
+    // ---- producer: box b = (page, half, K or V) of each tile, boxes spread over the lanes
+    const int boxes = pages_per_tile * NH * 2;
+    for (int t = 0; t < ntiles; ++t) {
+      const int stage = t % STAGES;
+      const int j = kv_begin + t * BN;
+      int cnt = 0;
+      int page_of[2] = {-1, -1};
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int b = lane + 32 * i;
+        const int pg = b / (2 * NH);
+        if (b < boxes && j + pg * page_rows < kv_end) {           // pages past the last key are not fetched
+          const int slot = (j >> log2_page) + pg;
+          int page = slot < p.table_width ? table[slot] : -1;
+          if (page < 0 || page >= p.num_pages) { set_status(p.status, SI_BAD_PAGE); page = -1; }
+          page_of[i] = page;
+          cnt += page >= 0;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+      bool ok = true;
+      if (t >= STAGES) ok = mbar_wait(&kv_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
+        break;
+      }
+      if (lane == 0) mbar_expect_tx(&kv_full[stage], (unsigned)(cnt * page_rows * 128));
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (page_of[i] < 0) continue;
+        const int b = lane + 32 * i;
+        const int pg = b / (2 * NH), h = (b >> 1) % NH, is_v = b & 1;
+        const int row = (page_of[i] * p.KV + g) << log2_page;
+        const size_t off = (size_t)stage * TILE + (size_t)h * (BN * 64) + (size_t)(pg * page_rows) * 64;
+        tma_load_2d((is_v ? Vs : Ks) + off, is_v ? &vmap : &kmap, &kv_full[stage], h * 64, row);
+      }
+    }
+  } else if (warp == 5) {
+    // ---- issuer: one lane issues the tensor-core instructions
+    if (lane == 0) {
+      constexpr unsigned idesc_s = umma_idesc_bf16(BM, BN, false);
+      constexpr unsigned idesc_t = umma_idesc_bf16(BM, HS, true);
+      for (int t = 0; t < ntiles; ++t) {
+        const int stage = t % STAGES;
+        if (!mbar_wait(&kv_full[stage], (unsigned)((t / STAGES) & 1))) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; break; }
+        tc05_fence_after_sync();
+        // S[128, 128] = Q[128, HS] K[128 keys, HS]^T: HS / 16 steps, 4 per 64-column half
+#pragma unroll
+        for (int kk = 0; kk < HS / 16; ++kk) {
+          const unsigned long long qd = umma_desc_sw128(Qs + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
+          const unsigned long long kd = umma_desc_sw128(Ks + (size_t)stage * TILE + (size_t)(kk >> 2) * (BN * 64), 16, 1024) + 2 * (kk & 3);
+          tc05_mma_bf16(tmem + TM_S, qd, kd, idesc_s, kk != 0 ? 1u : 0u);
+        }
+        tc05_commit(&s_full);
+        if (!mbar_wait(&p_full, (unsigned)(t & 1))) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; break; }
+        tc05_fence_after_sync();
+        // T[128, HS] = P[128, 128 keys] V[128 keys, HS]: 8 steps of 16 keys; V rows are keys (MN-major B)
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const unsigned long long pd = umma_desc_sw128(Ps + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
+          const unsigned long long vd = umma_desc_sw128(Vs + (size_t)stage * TILE, BN * 128, 1024) + 128 * kk;
+          tc05_mma_bf16(tmem + TM_T, pd, vd, idesc_t, kk != 0 ? 1u : 0u);
+        }
+        tc05_commit(&t_full);
+        tc05_commit(&kv_empty[stage]);
+      }
+    }
+  } else {
+    // ---- one row per thread
+    const int r = threadIdx.x;                       // tile row = tensor-memory lane
+    const int tok = r / p.G, hh = r - tok * p.G;
+    const int pos = tok < item.ntok ? item.pos0 + tok : -1;
+    const unsigned lane_base = (unsigned)(warp * 32) << 16;
+    float acc[HS];
+#pragma unroll
+    for (int i = 0; i < HS; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool alive = true;
+    for (int t = 0; t < ntiles; ++t) {
+      const int j0 = kv_begin + t * BN;
+      bool ok = mbar_wait(&s_full, (unsigned)(t & 1));
+      if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; } alive = false; break; }
+      tc05_fence_after_sync();
+      // pass 1: the row maximum of the visible, scaled scores
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld_32x32(tmem + lane_base + TM_S + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int j = j0 + c * 32 + i;
+          const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
+          if (vis) mx = fmaxf(mx, v[i] * p.scale_log2);
+        }
+      }
+      const float base = mx == -INFINITY ? 0.f : mx;
+      const float corr = exp2f(m - base);
+      m = mx;
+      // pass 2: probabilities, their sum, and the bf16 row of P (16 bytes per 8 keys, swizzled)
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        tmem_ld_32x32(tmem + lane_base + TM_S + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int j = j0 + c * 32 + i;
+          const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
+          v[i] = vis ? exp2f(v[i] * p.scale_log2 - base) : 0.f;
+          sum += v[i];
+        }
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint4 raw;
+          raw.x = pack_bf16(v[8 * q8], v[8 * q8 + 1]);
+          raw.y = pack_bf16(v[8 * q8 + 2], v[8 * q8 + 3]);
+          raw.z = pack_bf16(v[8 * q8 + 4], v[8 * q8 + 5]);
+          raw.w = pack_bf16(v[8 * q8 + 6], v[8 * q8 + 7]);
+          *reinterpret_cast<uint4*>(half_ptr<BM>(Ps, r, c * 4 + q8)) = raw;
+        }
+      }
+      l = l * corr + sum;
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      tc05_fence_before_sync();
+      mbar_arrive(&p_full);
+      // the tile's contribution T = P V, added to the rescaled accumulators
+      ok = mbar_wait(&t_full, (unsigned)(t & 1));
+      if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; } alive = false; break; }
+      tc05_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < HS / 32; ++c) {
+        float v[32];
+        tmem_ld_32x32(tmem + lane_base + TM_T + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * corr + v[i];
+      }
+      tc05_fence_before_sync();
+    }
+    if (alive && tok < item.ntok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs;
+#pragma unroll
+      for (int c = 0; c < HS / 8; ++c) {
+        uint4 raw;
+        raw.x = pack_bf16(acc[8 * c] * inv, acc[8 * c + 1] * inv);
+        raw.y = pack_bf16(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
+        raw.z = pack_bf16(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
+        raw.w = pack_bf16(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 8) = raw;
+      }
+    }
+  }
+  tc05_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, TM_COLS);
+}
+
+// ---- host side --------------------------------------------------------------------------------
+// 1 when this kernel takes the layout.
+SI_EXPORT int si_attn_portion_tc05_ok(int H, int KV, int hs, int page_size) {
+  if (KV <= 0 || H % KV || H / KV > 128) return 0;
+  if (hs != 64 && hs != 128) return 0;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return 0;
+  return si_encode_fn() != nullptr;
+}
+
+// Tokens of one item: floor(128 / G).
+SI_EXPORT int si_attn_portion_tc05_tokens(int H, int KV) { return 128 / (H / KV); }
+
+template <int NH>
+static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap& vm, int num_items, int log2_page,
+                  cudaStream_t stream) {
+  constexpr int HS = NH * 64;
+  const size_t smem = (size_t)(128 * HS + 128 * 128 + 2 * 2 * NH * 128 * 64) * sizeof(bf16) + 1024;
+  auto k = attn_portion_tc05_kernel<NH>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  k<<<dim3(num_items, p.KV), 192, smem, stream>>>(p, km, vm, log2_page);
+  return si_last_error();
+}
+
+// Same contract as si_attn_portion (attention_mma.cu) with the tensor maps of the layer's K and V cache
+// (made by si_attn_encode_cache_map of attention_tma.cu); items hold at most si_attn_portion_tc05_tokens().
+SI_EXPORT int si_attn_portion_tc05(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                   const void* kmap, const void* vmap, const int* block_table, int table_width,
+                                   const void* items, int num_items, void* out, long long out_stride, int num_pages,
+                                   int page_size, int num_seqs, int H, int KV, int hs, float scale, int window,
+                                   int* status, cudaStream_t stream) {
+  if (num_items <= 0) return 0;
+  if (!si_attn_portion_tc05_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
+  if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)out % 16)) return -2;
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_table = block_table; p.table_width = table_width;
+  p.items = (const AttnItem*)items;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
+  p.num_pages = num_pages; p.page_size = page_size; p.num_seqs = num_seqs;
+  p.H = H; p.KV = KV; p.G = H / KV; p.hs = hs;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window; p.nsplit = 1; p.status = status;
+  int log2_page = 0;
+  while ((1 << log2_page) < page_size) ++log2_page;
+  const CUtensorMap& km = *(const CUtensorMap*)kmap;
+  const CUtensorMap& vm = *(const CUtensorMap*)vmap;
+  return hs == 64 ? launch<1>(p, km, vm, num_items, log2_page, stream) : launch<2>(p, km, vm, num_items, log2_page, stream);
+}

@@ -422,3 +422,29 @@ def gemm_tc05(a, w, out, status=None) -> None:
             [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(a), a.stride(0), _weight_map(w), _ptr(out), out.stride(0), _dt(out), M, N, K, _ptr(status),
              _stream()), f"gemm_tc05(M={M}, N={N}, K={K})")
+
+
+# ---- prompt-portion attention on tcgen05 ---------------------------------------------------------
+
+def attn_portion_tc05_ok(H: int, KV: int, hs: int, page_size: int) -> bool:
+    lib = build.load("attention_tc05")
+    lib.si_attn_portion_tc05_ok.restype = _c_int
+    return bool(lib.si_attn_portion_tc05_ok(_c_int(H), _c_int(KV), _c_int(hs), _c_int(page_size)))
+
+
+def attn_portion_tc05_tokens(H: int, KV: int) -> int:
+    return 128 // (H // KV)
+
+
+def attn_portion_tc05(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int,
+                      KV: int, hs: int, scale: float, window: int = 0, status=None) -> None:
+    """``attn_portion`` on the tcgen05 tensor cores (TMA-fed K/V tiles, S and P V in tensor memory);
+    head_dim 64 or 128, page sizes 8 to 64, items of at most ``128 // (H // KV)`` tokens."""
+    _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_portion_tc05")
+    f = _fn("attention_tc05", "si_attn_portion_tc05",
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _cache_map(k_cache), _cache_map(v_cache),
+             _ptr(block_table), block_table.shape[1], _ptr(items), items.shape[0], _ptr(out), out.stride(0),
+             k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), _ptr(status),
+             _stream()), f"attn_portion_tc05(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")

@@ -242,13 +242,15 @@ def _items_for(lengths, tails, dec_tokens, por_tokens):
     return dec, por, rows
 
 
-def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit, tma=False):
+def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window, nsplit, tma=False, tc05=False):
     o = ops()
     G = H // KV
+    if tc05 and not o.attn_portion_tc05_ok(H, KV, hs, page_size):
+        pytest.skip("the tcgen05 portion kernel does not take this layout")
     if tma and not o.attn_decode_tma_ok(H, KV, hs, page_size):
         pytest.skip("the TMA decode kernel does not take this layout")
     dec_tokens = (o.attn_decode_tma_rows(H, KV) if tma else o.attn_decode_rows(H, KV, hs)) // G
-    por_tokens = o.attn_portion_tokens(H, KV, hs)
+    por_tokens = o.attn_portion_tc05_tokens(H, KV) if tc05 else o.attn_portion_tokens(H, KV, hs)
     dec, por, rows = _items_for(lengths, tails, dec_tokens, por_tokens)
     q = torch.stack([seqs[s][0][p].reshape(-1) for s, p in rows]).to(torch.bfloat16).to(DEV)
     out = torch.full_like(q, float("nan"))
@@ -266,7 +268,8 @@ def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size,
             nsplit=nsplit, scratch=scratch, status=status)
     if por:
         items = torch.tensor(por, dtype=torch.int32, device=DEV)
-        o.attn_portion(q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0, status=status)
+        (o.attn_portion_tc05 if tc05 else o.attn_portion)(
+            q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0, status=status)
     assert status.item() == 0
     return out.double().cpu(), rows, bool(dec), bool(por)
 
@@ -276,13 +279,17 @@ def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size,
     (5, 5, 80, 32, 7), (2, 1, 256, 16, 40), (32, 1, 64, 16, None), (40, 1, 128, 16, None), (24, 8, 128, 16, 100),
     (14, 2, 64, 64, None), (9, 3, 96, 16, 65), (8, 8, 64, 8, None), (20, 1, 128, 32, 200), (16, 2, 64, 16, 70)])
 @pytest.mark.parametrize("nsplit", [1, 3])
-@pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
+@pytest.mark.parametrize("tma", [False, True, "tc05"], ids=["cp_async", "tma", "tcgen05"])
 def test_attention_tensor_cores(H, KV, hs, page_size, window, nsplit, tma):
+    tc05 = tma == "tc05"
+    tma = bool(tma)
+    if tc05 and nsplit != 1:
+        pytest.skip("splits concern the decode kernel only")
     lengths = [1, 37, 130, 700, 64, 129]
     tails = [1, 1, 3, 700, 64, 2]           # decode rows, short runs, a whole long prompt, an exact tile
     seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page_size, seed=8)
     out, rows, used_dec, used_por = _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window,
-                                                      nsplit, tma)
+                                                      nsplit, tma, tc05)
     assert used_por
     scale = 1.0 / math.sqrt(hs)
     full = [plain_llama.attention(q.double(), k.double(), v.double(), scale, window) for q, k, v in seqs]
@@ -320,10 +327,13 @@ def test_attention_finds_one_far_key(hs, page_size):
             kc[table[0, b], :, :m] = seqs[0][1][b * page_size:b * page_size + m].transpose(0, 1)
             vc[table[0, b], :, :m] = seqs[0][2][b * page_size:b * page_size + m].transpose(0, 1)
         kc, vc = kc.to(torch.bfloat16), vc.to(torch.bfloat16)
-        for tails, nsplit, tma in (([1], 1, False), ([1], 4, False), ([n], 1, False), ([1], 1, True), ([1], 4, True)):
+        for tails, nsplit, tma, tc05 in (([1], 1, False, False), ([1], 4, False, False), ([n], 1, False, False),
+                                         ([1], 1, True, False), ([1], 4, True, False), ([n], 1, True, True)):
             if tma and not ops().attn_decode_tma_ok(H, KV, hs, page_size):
                 continue
-            out, rows, _, _ = _run_tc_attention(seqs, table, kc, vc, [n], tails, H, KV, hs, page_size, None, nsplit, tma)
+            if tc05 and not ops().attn_portion_tc05_ok(H, KV, hs, page_size):
+                continue
+            out, rows, _, _ = _run_tc_attention(seqs, table, kc, vc, [n], tails, H, KV, hs, page_size, None, nsplit, tma, tc05)
             for r, (s, p) in enumerate(rows):
                 if p not in (n - 1, n - 5) or target > p:
                     continue
@@ -351,9 +361,9 @@ def test_attention_window_edge():
             m = min(page_size, n - b * page_size)
             kc[b, :, :m] = seqs[0][1][b * page_size:b * page_size + m].transpose(0, 1)
             vc[b, :, :m] = seqs[0][2][b * page_size:b * page_size + m].transpose(0, 1)
-        for tails, tma in (([1], False), ([n], False), ([1], True)):
+        for tails, tma, tc05 in (([1], False, False), ([n], False, False), ([1], True, False), ([n], True, True)):
             out, rows, _, _ = _run_tc_attention(seqs, table, kc.to(torch.bfloat16), vc.to(torch.bfloat16), [n], tails,
-                                                H, KV, hs, page_size, window, 1, tma)
+                                                H, KV, hs, page_size, window, 1, tma, tc05)
             got = out[-1].view(H, hs)
             hit = (got - seqs[0][2][target].double()).abs().max().item() < 0.02
             assert hit == visible, (target, tails)
@@ -475,3 +485,33 @@ def test_gemm_tc05(M, N, K, out_dtype):
     tol = 1e-4 * math.sqrt(K) if out_dtype == torch.float32 else 2 ** -8 * want.abs().max().item()
     assert not torch.isnan(out).any()
     assert (out.double() - want).abs().max().item() <= tol
+
+
+def test_gemm_tc05_at_prefill_size():
+    """The projections of the Llama-3.1-8B block at 2,048 rows: achieved TFLOP/s (printed) beside the library."""
+    g = torch.Generator(device=DEV).manual_seed(15)
+    M = 2048
+    for name, N, K in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+        a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+        w = (0.02 * torch.randn(N, K, generator=g, device=DEV)).to(torch.bfloat16)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        res = {}
+        for label, fn in (("tcgen05", lambda: ops().gemm_tc05(a, w, out, status)), ("library", lambda: torch.mm(a, w.t(), out=out))):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            res[label] = e0.elapsed_time(e1) * 100
+        assert status.item() == 0
+        ops().gemm_tc05(a, w, out, status)
+        want = a[:64].double() @ w.double().T
+        assert (out[:64].double() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item()
+        tf = 2.0 * M * N * K / 1e6
+        print(f"{name}: tcgen05 {res['tcgen05']:.1f} us ({tf / res['tcgen05']:.0f} TFLOP/s), "
+              f"library {res['library']:.1f} us ({tf / res['library']:.0f} TFLOP/s)")
