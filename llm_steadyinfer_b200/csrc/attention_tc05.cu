@@ -5,13 +5,15 @@
 //
 //   warp 4 (producer)  looks up the pages of a tile and issues its K and V boxes by TMA
 //                      (128-byte swizzle) into one of two stages;
-//   warp 5 (issuer)    S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major), then, once the
-//                      probabilities are in shared memory, T = P V (V is the MN-major operand, as
-//                      it lies in the cache), each completion signalled by tcgen05.commit;
+//   warp 5 (issuer)    S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major) and, once the
+//                      probabilities are in shared memory, O += P V (V is the MN-major operand, as
+//                      it lies in the cache); the next tile's S is issued as soon as the rows of the
+//                      current one are in registers, so it runs under the softmax;
 //   warps 0-3          one thread per row: read the row of S from tensor memory (tcgen05.ld), mask,
-//                      online softmax in fp32 (exp2 of scale*log2e-scaled scores), write the bf16
-//                      probabilities into the swizzled P tile, then add the tile's T row into the
-//                      fp32 accumulators kept in registers, rescaled by the change of the maximum.
+//                      softmax in fp32 (exp2 of scale*log2e-scaled scores) against a base that is
+//                      raised only when the row maximum has grown by more than 2^8 (then the row of
+//                      O in tensor memory is rescaled with tcgen05.ld/st), write the bf16 probabilities
+//                      into the swizzled P tile; at the end read O and divide by the row sum.
 //
 // The reference computes prompt attention row by row with its scalar split kernel
 // (src/source/op/kernels/cuda/paged_kernels.cu:96-206). Conditions here: head_dim 64 or 128, page size
@@ -19,6 +21,13 @@
 // is bounded; when one runs out the block sets SI_WAIT_LIMIT and leaves without storing.
 #include "attention_common.cuh"
 #include "tma_common.cuh"
+
+// 2^x in fp32 by the hardware approximation (2 ulp); exp2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int NROWS>
 __device__ __forceinline__ bf16* half_ptr(bf16* base, int row, int chunk) {
@@ -35,7 +44,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   constexpr int TM_COLS = 256;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t kv_full[STAGES], kv_empty[STAGES];
-  __shared__ __align__(8) uint64_t s_full, p_full, t_full;
+  __shared__ __align__(8) uint64_t s_full, s_free, p_full, t_full;
   __shared__ unsigned tmem_slot;
   __shared__ int s_abort;
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -65,6 +74,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(&s_full, 1);
     mbar_init(&p_full, 128);
+    mbar_init(&s_free, 128);
     mbar_init(&t_full, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -137,11 +147,8 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     if (lane == 0) {
       constexpr unsigned idesc_s = umma_idesc_bf16(BM, BN, false);
       constexpr unsigned idesc_t = umma_idesc_bf16(BM, HS, true);
-      for (int t = 0; t < ntiles; ++t) {
+      auto issue_s = [&](int t) {       // S[128, 128] = Q[128, HS] K_t[128 keys, HS]^T: 4 steps per 64-column half
         const int stage = t % STAGES;
-        if (!mbar_wait(&kv_full[stage], (unsigned)((t / STAGES) & 1))) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; break; }
-        tc05_fence_after_sync();
-        // S[128, 128] = Q[128, HS] K[128 keys, HS]^T: HS / 16 steps, 4 per 64-column half
 #pragma unroll
         for (int kk = 0; kk < HS / 16; ++kk) {
           const unsigned long long qd = umma_desc_sw128(Qs + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
@@ -149,18 +156,31 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
           tc05_mma_bf16(tmem + TM_S, qd, kd, idesc_s, kk != 0 ? 1u : 0u);
         }
         tc05_commit(&s_full);
-        if (!mbar_wait(&p_full, (unsigned)(t & 1))) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; break; }
+      };
+      bool ok = ntiles > 0 && mbar_wait(&kv_full[0], 0);
+      if (ok) { tc05_fence_after_sync(); issue_s(0); }
+      for (int t = 0; t < ntiles && ok; ++t) {
+        const int stage = t % STAGES;
+        if (t + 1 < ntiles) {              // the next S runs while the rows of this one are being worked on
+          ok = mbar_wait(&kv_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1)) && mbar_wait(&s_free, (unsigned)(t & 1));
+          if (!ok) break;
+          tc05_fence_after_sync();
+          issue_s(t + 1);
+        }
+        ok = mbar_wait(&p_full, (unsigned)(t & 1));
+        if (!ok) break;
         tc05_fence_after_sync();
-        // T[128, HS] = P[128, 128 keys] V[128 keys, HS]: 8 steps of 16 keys; V rows are keys (MN-major B)
+        // O[128, HS] (+)= P[128, 128 keys] V_t[128 keys, HS]: 8 steps of 16 keys; V rows are keys (MN-major B)
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const unsigned long long pd = umma_desc_sw128(Ps + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
           const unsigned long long vd = umma_desc_sw128(Vs + (size_t)stage * TILE, BN * 128, 1024) + 128 * kk;
-          tc05_mma_bf16(tmem + TM_T, pd, vd, idesc_t, kk != 0 ? 1u : 0u);
+          tc05_mma_bf16(tmem + TM_T, pd, vd, idesc_t, (t | kk) != 0 ? 1u : 0u);
         }
         tc05_commit(&t_full);
         tc05_commit(&kv_empty[stage]);
       }
+      if (!ok && ntiles > 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
     }
   } else {
     // ---- one row per thread
@@ -168,83 +188,96 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     const int tok = r / p.G, hh = r - tok * p.G;
     const int pos = tok < item.ntok ? item.pos0 + tok : -1;
     const unsigned lane_base = (unsigned)(warp * 32) << 16;
-    float acc[HS];
-#pragma unroll
-    for (int i = 0; i < HS; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;                    // base of the exponentials (log2 domain), row sum
     bool alive = true;
     for (int t = 0; t < ntiles; ++t) {
       const int j0 = kv_begin + t * BN;
       bool ok = mbar_wait(&s_full, (unsigned)(t & 1));
-      if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; } alive = false; break; }
+      if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
       tc05_fence_after_sync();
-      // pass 1: the row maximum of the visible, scaled scores
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld_32x32(tmem + lane_base + TM_S + c * 32, v);
+      float s[BN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int j = j0 + c * 32 + i;
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32_issue(tmem + lane_base + TM_S + c * 32, s + c * 32);
+      tmem_ld_wait();
+      tc05_fence_before_sync();
+      mbar_arrive(&s_free);                          // S may be overwritten by the next tile's product
+      float mx = -INFINITY;
+      const bool all_visible = j0 + BN - 1 <= pos && (p.window <= 0 || j0 > pos - p.window);
+      if (all_visible) {                             // most tiles lie wholly before the row's position
+#pragma unroll
+        for (int i = 0; i < BN; ++i) { s[i] *= p.scale_log2; mx = fmaxf(mx, s[i]); }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int j = j0 + i;
           const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
-          if (vis) mx = fmaxf(mx, v[i] * p.scale_log2);
+          s[i] = vis ? s[i] * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, s[i]);
         }
       }
-      const float base = mx == -INFINITY ? 0.f : mx;
-      const float corr = exp2f(m - base);
-      m = mx;
-      // pass 2: probabilities, their sum, and the bf16 row of P (16 bytes per 8 keys, swizzled)
+      // raise the base only when the maximum has outgrown it by 2^8; then O and l are rescaled
+      float factor = 1.f;
+      const bool raise = mx > m + 8.f;
+      if (raise) { factor = exp2f(m - mx); m = mx; }
+      const float base = m == -INFINITY ? 0.f : m;
       float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) { s[i] = fast_exp2(s[i] - base); sum += s[i]; }
+      l = l * factor + sum;
+      // P and O belong to the previous product until it has completed
+      if (t > 0) {
+        ok = mbar_wait(&t_full, (unsigned)((t - 1) & 1));
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        tc05_fence_after_sync();
+        if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld_32x32(tmem + lane_base + TM_S + c * 32, v);
+          for (int c = 0; c < HS / 32; ++c) {
+            float v[32];
+            tmem_ld_32x32(tmem + lane_base + TM_T + c * 32, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int j = j0 + c * 32 + i;
-          const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
-          v[i] = vis ? exp2f(v[i] * p.scale_log2 - base) : 0.f;
-          sum += v[i];
-        }
-#pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
-          uint4 raw;
-          raw.x = pack_bf16(v[8 * q8], v[8 * q8 + 1]);
-          raw.y = pack_bf16(v[8 * q8 + 2], v[8 * q8 + 3]);
-          raw.z = pack_bf16(v[8 * q8 + 4], v[8 * q8 + 5]);
-          raw.w = pack_bf16(v[8 * q8 + 6], v[8 * q8 + 7]);
-          *reinterpret_cast<uint4*>(half_ptr<BM>(Ps, r, c * 4 + q8)) = raw;
+            for (int i = 0; i < 32; ++i) v[i] *= factor;
+            tmem_st_32x32(tmem + lane_base + TM_T + c * 32, v);
+          }
         }
       }
-      l = l * corr + sum;
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        uint4 raw;
+        raw.x = pack_bf16(s[8 * c], s[8 * c + 1]);
+        raw.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
+        raw.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
+        raw.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
+        *reinterpret_cast<uint4*>(half_ptr<BM>(Ps, r, c)) = raw;
+      }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       tc05_fence_before_sync();
       mbar_arrive(&p_full);
-      // the tile's contribution T = P V, added to the rescaled accumulators
-      ok = mbar_wait(&t_full, (unsigned)(t & 1));
-      if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; } alive = false; break; }
+    }
+    if (alive && ntiles > 0) {
+      const bool ok = mbar_wait(&t_full, (unsigned)((ntiles - 1) & 1));
+      if (!__all_sync(0xffffffffu, ok)) alive = false;
+    }
+    if (!alive) {
+      if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
+    } else {
       tc05_fence_after_sync();
-#pragma unroll
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs;
+#pragma unroll 1
       for (int c = 0; c < HS / 32; ++c) {
         float v[32];
         tmem_ld_32x32(tmem + lane_base + TM_T + c * 32, v);
+        if (tok < item.ntok) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * corr + v[i];
-      }
-      tc05_fence_before_sync();
-    }
-    if (alive && tok < item.ntok) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs;
-#pragma unroll
-      for (int c = 0; c < HS / 8; ++c) {
-        uint4 raw;
-        raw.x = pack_bf16(acc[8 * c] * inv, acc[8 * c + 1] * inv);
-        raw.y = pack_bf16(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
-        raw.z = pack_bf16(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
-        raw.w = pack_bf16(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 8) = raw;
+          for (int q8 = 0; q8 < 4; ++q8) {
+            uint4 raw;
+            raw.x = pack_bf16(v[8 * q8] * inv, v[8 * q8 + 1] * inv);
+            raw.y = pack_bf16(v[8 * q8 + 2] * inv, v[8 * q8 + 3] * inv);
+            raw.z = pack_bf16(v[8 * q8 + 4] * inv, v[8 * q8 + 5] * inv);
+            raw.w = pack_bf16(v[8 * q8 + 6] * inv, v[8 * q8 + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q8 * 8) = raw;
+          }
+        }
       }
     }
   }

@@ -18,6 +18,7 @@ from .linear import linear
 
 USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
 USE_TMA = True               # decode tiles by TMA where the layout allows
+USE_TC05 = True              # prompt portions on tcgen05 where the layout allows
 TARGET_BLOCKS = 2 * 148      # decode attention blocks that run at once
 MAX_SPLITS = 32
 MIN_TILES_PER_SPLIT = 2      # a split covers at least this many 64-key tiles
@@ -104,7 +105,8 @@ class Attention(Mixer):
             else:
                 for b in range(0, n, por_tokens):
                     por.append((s, row0 + b, min(por_tokens, n - b), pos0 + b))
-        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma}
+        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma,
+                "tc05": USE_TC05 and ops.attn_portion_tc05_ok(self.H, self.KV, self.hs, cache.page_size)}
         n_dec = len(dec)
         if ctx.seq_cap is not None:                   # fixed shapes: pad with empty items
             dec += [(0, 0, 0, 0)] * (ctx.seq_cap - n_dec)
@@ -139,7 +141,8 @@ class Attention(Mixer):
             decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,
                             nsplit=plan["nsplit"], scratch=plan["scratch"], status=ctx.status)
         if plan["por"] is not None:
-            ops.attn_portion(q, cache.k, cache.v, cache.block_table, plan["por"], out, *args, status=ctx.status)
+            portion = ops.attn_portion_tc05 if plan["tc05"] else ops.attn_portion
+            portion(q, cache.k, cache.v, cache.block_table, plan["por"], out, *args, status=ctx.status)
 
 
 register_mixer("attention", Attention)

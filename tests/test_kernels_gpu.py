@@ -515,3 +515,42 @@ def test_gemm_tc05_at_prefill_size():
         tf = 2.0 * M * N * K / 1e6
         print(f"{name}: tcgen05 {res['tcgen05']:.1f} us ({tf / res['tcgen05']:.0f} TFLOP/s), "
               f"library {res['library']:.1f} us ({tf / res['library']:.0f} TFLOP/s)")
+
+
+def test_attention_portion_at_prefill_size():
+    """A 2,048-token prompt at the Llama-3.1-8B head layout: both portion kernels against the plain
+    kernel on sampled rows, and their times (printed)."""
+    o = ops()
+    H, KV, hs, page_size, T = 32, 8, 128, 16, 2048
+    g = torch.Generator(device=DEV).manual_seed(16)
+    blocks = T // page_size
+    kc = torch.randn(blocks + 5, KV, page_size, hs, generator=g, device=DEV).to(torch.bfloat16)
+    vc = torch.randn(blocks + 5, KV, page_size, hs, generator=g, device=DEV).to(torch.bfloat16)
+    table = torch.randperm(blocks + 5, generator=g, device=DEV)[:blocks].to(torch.int32).view(1, blocks)
+    q = torch.randn(T, H * hs, generator=g, device=DEV).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    rows = torch.tensor([0, 1, 15, 16, 127, 128, 129, 1000, 2046, 2047], device=DEV)
+    want = torch.empty(len(rows), H * hs, dtype=torch.bfloat16, device=DEV)
+    o.paged_attention_ref(q[rows], kc, vc, table, torch.zeros(len(rows), dtype=torch.int32, device=DEV),
+                          rows.to(torch.int32), want, page_size, 1, H, KV, hs, scale, 0, status)
+    tok = o.attn_portion_tokens(H, KV, hs)
+    items = torch.tensor([(0, b, min(tok, T - b), b) for b in range(0, T, tok)], dtype=torch.int32, device=DEV)
+    for label, fn in (("mma.sync", o.attn_portion), ("tcgen05", o.attn_portion_tc05)):
+        out = torch.full_like(q, float("nan"))
+        run = lambda: fn(q, kc, vc, table, items, out, page_size, 1, H, KV, hs, scale, 0, status=status)
+        run()
+        assert status.item() == 0 and not torch.isnan(out).any()
+        assert (out[rows].float() - want.float()).abs().max().item() <= 2 ** -8 * 4
+        for _ in range(2):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(10):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 100
+        flops = 4.0 * H * hs * T * (T + 1) / 2
+        print(f"attn_portion {label}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
