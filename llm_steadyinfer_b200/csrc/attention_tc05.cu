@@ -3,17 +3,18 @@
 // for one KV head: 128 rows = tokens x the G query heads of the KV head (row r = token r / G,
 // head r % G), against key tiles of 128.
 //
-//   warp 4 (producer)  looks up the pages of a tile and issues its K and V boxes by TMA
+//   warp 8 (producer)  looks up the pages of a tile and issues its K and V boxes by TMA
 //                      (128-byte swizzle) into one of two stages;
-//   warp 5 (issuer)    S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major) and, once the
+//   warp 9 (issuer)    S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major) and, once the
 //                      probabilities are in shared memory, O += P V (V is the MN-major operand, as
 //                      it lies in the cache); the next tile's S is issued as soon as the rows of the
 //                      current one are in registers, so it runs under the softmax;
-//   warps 0-3          one thread per row: read the row of S from tensor memory (tcgen05.ld), mask,
-//                      softmax in fp32 (exp2 of scale*log2e-scaled scores) against a base that is
-//                      raised only when the row maximum has grown by more than 2^8 (then the row of
-//                      O in tensor memory is rescaled with tcgen05.ld/st), write the bf16 probabilities
-//                      into the swizzled P tile; at the end read O and divide by the row sum.
+//   warps 0-7          two threads per row (warps 0-3 take keys 0-63 of a tile, warps 4-7 keys 64-127):
+//                      read the row of S from tensor memory (tcgen05.ld), mask, exchange the row
+//                      maximum, softmax in fp32 (exp2 of scale*log2e-scaled scores) against a base
+//                      that is raised only when the maximum has grown by more than 2^8 (then the row
+//                      of O in tensor memory is rescaled with tcgen05.ld/st), write the bf16
+//                      probabilities into the swizzled P tile; at the end read O, divide by the row sum.
 //
 // The reference computes prompt attention row by row with its scalar split kernel
 // (src/source/op/kernels/cuda/paged_kernels.cu:96-206). Conditions here: head_dim 64 or 128, page size
@@ -35,7 +36,7 @@ __device__ __forceinline__ bf16* half_ptr(bf16* base, int row, int chunk) {
 }
 
 template <int NH>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320)
 attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                          const __grid_constant__ CUtensorMap vmap, int log2_page) {
   constexpr int BM = 128, BN = 128, HS = NH * 64, STAGES = 2;
@@ -43,17 +44,20 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   constexpr int TM_S = 0, TM_T = BN;                 // tensor-memory columns of S and of T = P V
   constexpr int TM_COLS = 256;
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ __align__(8) uint64_t kv_full[STAGES], kv_empty[STAGES];
+  __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
   __shared__ __align__(8) uint64_t s_full, s_free, p_full, t_full;
   __shared__ unsigned tmem_slot;
   __shared__ int s_abort;
+  __shared__ float xmax[2][2][BM];                   // [tile parity][column half][row]: row maxima to exchange
+  __shared__ float xsum[2][BM];
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [NH][128][64]
   bf16* Ps = Qs + BM * HS;                           // [2][128][64]   (keys 0-63, 64-127)
   bf16* Ks = Ps + BM * BN;                           // [STAGES][TILE]
   bf16* Vs = Ks + STAGES * TILE;
 
-  const AttnItem item = p.items[blockIdx.x];
+  // items of a prompt come in order of position, so the last ones have the most keys: start with those
+  const AttnItem item = p.items[gridDim.x - 1 - blockIdx.x];
   if (item.ntok <= 0) return;
   const int g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -71,15 +75,17 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
 
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
     mbar_init(&s_full, 1);
-    mbar_init(&p_full, 128);
-    mbar_init(&s_free, 128);
+    mbar_init(&p_full, 8);                           // one arrival per softmax warp
+    mbar_init(&s_free, 8);
     mbar_init(&t_full, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) tmem_alloc(&tmem_slot, TM_COLS);
+  if (warp == 9) tmem_alloc(&tmem_slot, TM_COLS);
   // rows of the last tile that no copy fills must hold finite numbers (they meet zero probabilities)
   if ((kv_end - kv_begin) % BN != 0) {
     const int stage = (ntiles - 1) % STAGES;
@@ -102,13 +108,15 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   tc05_fence_after_sync();
   const unsigned tmem = tmem_slot;
 
-  if (warp == 4) {
-    // ---- producer: box b = (page, half, K or V) of each tile, boxes spread over the lanes
+  if (warp == 8) {
+    // ---- producer: box b = (page, half, K or V) of each tile, boxes spread over the lanes. K and V
+    // have barriers of their own: a K stage is free as soon as S has been computed from it, long
+    // before the V stage of the same tile, so the next keys arrive under the softmax.
     const int boxes = pages_per_tile * NH * 2;
     for (int t = 0; t < ntiles; ++t) {
       const int stage = t % STAGES;
       const int j = kv_begin + t * BN;
-      int cnt = 0;
+      int cnt = 0;                                   // boxes of K (the same number of V) this lane group fetches
       int page_of[2] = {-1, -1};
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
@@ -119,30 +127,46 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
           int page = slot < p.table_width ? table[slot] : -1;
           if (page < 0 || page >= p.num_pages) { set_status(p.status, SI_BAD_PAGE); page = -1; }
           page_of[i] = page;
-          cnt += page >= 0;
+          cnt += (page >= 0) && !(b & 1);
         }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
       bool ok = true;
-      if (t >= STAGES) ok = mbar_wait(&kv_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
+      if (t >= STAGES) ok = mbar_wait(&k_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
         break;
       }
-      if (lane == 0) mbar_expect_tx(&kv_full[stage], (unsigned)(cnt * page_rows * 128));
+      if (lane == 0) mbar_expect_tx(&k_full[stage], (unsigned)(cnt * page_rows * 128));
       __syncwarp();
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        if (page_of[i] < 0) continue;
         const int b = lane + 32 * i;
-        const int pg = b / (2 * NH), h = (b >> 1) % NH, is_v = b & 1;
+        if (page_of[i] < 0 || (b & 1)) continue;
+        const int pg = b / (2 * NH), h = (b >> 1) % NH;
         const int row = (page_of[i] * p.KV + g) << log2_page;
         const size_t off = (size_t)stage * TILE + (size_t)h * (BN * 64) + (size_t)(pg * page_rows) * 64;
-        tma_load_2d((is_v ? Vs : Ks) + off, is_v ? &vmap : &kmap, &kv_full[stage], h * 64, row);
+        tma_load_2d(Ks + off, &kmap, &k_full[stage], h * 64, row);
+      }
+      if (t >= STAGES) ok = mbar_wait(&v_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
+        break;
+      }
+      if (lane == 0) mbar_expect_tx(&v_full[stage], (unsigned)(cnt * page_rows * 128));
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int b = lane + 32 * i;
+        if (page_of[i] < 0 || !(b & 1)) continue;
+        const int pg = b / (2 * NH), h = (b >> 1) % NH;
+        const int row = (page_of[i] * p.KV + g) << log2_page;
+        const size_t off = (size_t)stage * TILE + (size_t)h * (BN * 64) + (size_t)(pg * page_rows) * 64;
+        tma_load_2d(Vs + off, &vmap, &v_full[stage], h * 64, row);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---- issuer: one lane issues the tensor-core instructions
     if (lane == 0) {
       constexpr unsigned idesc_s = umma_idesc_bf16(BM, BN, false);
@@ -156,18 +180,19 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
           tc05_mma_bf16(tmem + TM_S, qd, kd, idesc_s, kk != 0 ? 1u : 0u);
         }
         tc05_commit(&s_full);
+        tc05_commit(&k_empty[stage]);                // the keys of this tile are not needed again
       };
-      bool ok = ntiles > 0 && mbar_wait(&kv_full[0], 0);
+      bool ok = ntiles > 0 && mbar_wait(&k_full[0], 0);
       if (ok) { tc05_fence_after_sync(); issue_s(0); }
       for (int t = 0; t < ntiles && ok; ++t) {
         const int stage = t % STAGES;
         if (t + 1 < ntiles) {              // the next S runs while the rows of this one are being worked on
-          ok = mbar_wait(&kv_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1)) && mbar_wait(&s_free, (unsigned)(t & 1));
+          ok = mbar_wait(&k_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1)) && mbar_wait(&s_free, (unsigned)(t & 1));
           if (!ok) break;
           tc05_fence_after_sync();
           issue_s(t + 1);
         }
-        ok = mbar_wait(&p_full, (unsigned)(t & 1));
+        ok = mbar_wait(&p_full, (unsigned)(t & 1)) && mbar_wait(&v_full[stage], (unsigned)((t / STAGES) & 1));
         if (!ok) break;
         tc05_fence_after_sync();
         // O[128, HS] (+)= P[128, 128 keys] V_t[128 keys, HS]: 8 steps of 16 keys; V rows are keys (MN-major B)
@@ -178,43 +203,53 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
           tc05_mma_bf16(tmem + TM_T, pd, vd, idesc_t, (t | kk) != 0 ? 1u : 0u);
         }
         tc05_commit(&t_full);
-        tc05_commit(&kv_empty[stage]);
+        tc05_commit(&v_empty[stage]);
       }
       if (!ok && ntiles > 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
     }
   } else {
-    // ---- one row per thread
-    const int r = threadIdx.x;                       // tile row = tensor-memory lane
+    // ---- two threads per row: column half `wg` of every tile
+    constexpr int HALF = BN / 2, OH = HS / 2;        // keys of S and columns of O per thread
+    const int wg = warp >> 2;
+    const int r = threadIdx.x & (BM - 1);            // tile row = tensor-memory lane
     const int tok = r / p.G, hh = r - tok * p.G;
     const int pos = tok < item.ntok ? item.pos0 + tok : -1;
-    const unsigned lane_base = (unsigned)(warp * 32) << 16;
-    float m = -INFINITY, l = 0.f;                    // base of the exponentials (log2 domain), row sum
+    const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
+    float m = -INFINITY, l = 0.f;                    // base of the exponentials (log2 domain), this half's sum
     bool alive = true;
+    // Every warp runs all iterations and meets the others at the named barrier in each of them, also
+    // after a wait has run out (`alive` false: it then skips the work), so nobody is left waiting there.
     for (int t = 0; t < ntiles; ++t) {
-      const int j0 = kv_begin + t * BN;
-      bool ok = mbar_wait(&s_full, (unsigned)(t & 1));
-      if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-      tc05_fence_after_sync();
-      float s[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32_issue(tmem + lane_base + TM_S + c * 32, s + c * 32);
-      tmem_ld_wait();
-      tc05_fence_before_sync();
-      mbar_arrive(&s_free);                          // S may be overwritten by the next tile's product
+      const int j0 = kv_begin + t * BN + wg * HALF;
+      if (alive) alive = __all_sync(0xffffffffu, mbar_wait(&s_full, (unsigned)(t & 1)));
+      float s[HALF];
       float mx = -INFINITY;
-      const bool all_visible = j0 + BN - 1 <= pos && (p.window <= 0 || j0 > pos - p.window);
-      if (all_visible) {                             // most tiles lie wholly before the row's position
+      if (alive) {
+        tc05_fence_after_sync();
 #pragma unroll
-        for (int i = 0; i < BN; ++i) { s[i] *= p.scale_log2; mx = fmaxf(mx, s[i]); }
-      } else {
+        for (int c = 0; c < HALF / 32; ++c) tmem_ld_32x32_issue(tmem + lane_base + TM_S + wg * HALF + c * 32, s + c * 32);
+        tmem_ld_wait();
+        tc05_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free);         // S may be overwritten by the next tile's product
+        const bool all_visible = j0 + HALF - 1 <= pos && (p.window <= 0 || j0 > pos - p.window);
+        if (all_visible) {                           // most tiles lie wholly before the row's position
 #pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const int j = j0 + i;
-          const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
-          s[i] = vis ? s[i] * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[i]);
+          for (int i = 0; i < HALF; ++i) { s[i] *= p.scale_log2; mx = fmaxf(mx, s[i]); }
+        } else {
+#pragma unroll
+          for (int i = 0; i < HALF; ++i) {
+            const int j = j0 + i;
+            const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
+            s[i] = vis ? s[i] * p.scale_log2 : -INFINITY;
+            mx = fmaxf(mx, s[i]);
+          }
         }
       }
+      xmax[t & 1][wg][r] = mx;
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      if (!alive) continue;
+      mx = fmaxf(mx, xmax[t & 1][wg ^ 1][r]);
       // raise the base only when the maximum has outgrown it by 2^8; then O and l are rescaled
       float factor = 1.f;
       const bool raise = mx > m + 8.f;
@@ -222,51 +257,55 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       const float base = m == -INFINITY ? 0.f : m;
       float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < BN; ++i) { s[i] = fast_exp2(s[i] - base); sum += s[i]; }
+      for (int i = 0; i < HALF; ++i) { s[i] = fast_exp2(s[i] - base); sum += s[i]; }
       l = l * factor + sum;
       // P and O belong to the previous product until it has completed
       if (t > 0) {
-        ok = mbar_wait(&t_full, (unsigned)((t - 1) & 1));
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        alive = __all_sync(0xffffffffu, mbar_wait(&t_full, (unsigned)((t - 1) & 1)));
+        if (!alive) continue;
         tc05_fence_after_sync();
         if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-          for (int c = 0; c < HS / 32; ++c) {
+          for (int c = 0; c < OH / 32; ++c) {
             float v[32];
-            tmem_ld_32x32(tmem + lane_base + TM_T + c * 32, v);
+            tmem_ld_32x32(tmem + lane_base + TM_T + wg * OH + c * 32, v);
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] *= factor;
-            tmem_st_32x32(tmem + lane_base + TM_T + c * 32, v);
+            tmem_st_32x32(tmem + lane_base + TM_T + wg * OH + c * 32, v);
           }
         }
       }
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
+      for (int c = 0; c < HALF / 8; ++c) {
         uint4 raw;
         raw.x = pack_bf16(s[8 * c], s[8 * c + 1]);
         raw.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
         raw.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
         raw.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-        *reinterpret_cast<uint4*>(half_ptr<BM>(Ps, r, c)) = raw;
+        *reinterpret_cast<uint4*>(half_ptr<BM>(Ps, r, wg * (HALF / 8) + c)) = raw;
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       tc05_fence_before_sync();
-      mbar_arrive(&p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
     }
     if (alive && ntiles > 0) {
       const bool ok = mbar_wait(&t_full, (unsigned)((ntiles - 1) & 1));
       if (!__all_sync(0xffffffffu, ok)) alive = false;
     }
-    if (!alive) {
-      if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
-    } else {
+    // the two halves of a row add their sums (a failed wait anywhere is seen by all through s_abort)
+    if (!alive && lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
+    xsum[wg][r] = l;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (!s_abort) {
       tc05_fence_after_sync();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs;
+      const float lt = l + xsum[wg ^ 1][r];
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + wg * OH;
 #pragma unroll 1
-      for (int c = 0; c < HS / 32; ++c) {
+      for (int c = 0; c < OH / 32; ++c) {
         float v[32];
-        tmem_ld_32x32(tmem + lane_base + TM_T + c * 32, v);
+        tmem_ld_32x32(tmem + lane_base + TM_T + wg * OH + c * 32, v);
         if (tok < item.ntok) {
 #pragma unroll
           for (int q8 = 0; q8 < 4; ++q8) {
@@ -283,7 +322,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   }
   tc05_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, TM_COLS);
+  if (warp == 9) tmem_dealloc(tmem, TM_COLS);
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -306,7 +345,7 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
   auto k = attn_portion_tc05_kernel<NH>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  k<<<dim3(num_items, p.KV), 192, smem, stream>>>(p, km, vm, log2_page);
+  k<<<dim3(num_items, p.KV), 320, smem, stream>>>(p, km, vm, log2_page);
   return si_last_error();
 }
 
