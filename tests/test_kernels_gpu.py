@@ -534,9 +534,9 @@ def test_attention_portion_at_prefill_size():
     want = torch.empty(len(rows), H * hs, dtype=torch.bfloat16, device=DEV)
     o.paged_attention_ref(q[rows], kc, vc, table, torch.zeros(len(rows), dtype=torch.int32, device=DEV),
                           rows.to(torch.int32), want, page_size, 1, H, KV, hs, scale, 0, status)
-    tok = o.attn_portion_tokens(H, KV, hs)
-    items = torch.tensor([(0, b, min(tok, T - b), b) for b in range(0, T, tok)], dtype=torch.int32, device=DEV)
-    for label, fn in (("mma.sync", o.attn_portion), ("tcgen05", o.attn_portion_tc05)):
+    for label, fn, tok in (("mma.sync", o.attn_portion, o.attn_portion_tokens(H, KV, hs)),
+                           ("tcgen05", o.attn_portion_tc05, o.attn_portion_tc05_tokens(H, KV))):
+        items = torch.tensor([(0, b, min(tok, T - b), b) for b in range(0, T, tok)], dtype=torch.int32, device=DEV)
         out = torch.full_like(q, float("nan"))
         run = lambda: fn(q, kc, vc, table, items, out, page_size, 1, H, KV, hs, scale, 0, status=status)
         run()
