@@ -43,6 +43,7 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   bf16* Vs = Ks + STAGES * TILE;
   bf16* Qs = Vs + STAGES * TILE;                     // [NH][ROWS][64]
 
+  pdl_prologue();
   const AttnItem item = p.items[blockIdx.x];
   if (item.ntok <= 0) return;
   const int g = blockIdx.y, split = blockIdx.z;
@@ -338,7 +339,7 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  k<<<dim3(num_items, p.KV, p.nsplit), 160, smem, stream>>>(p, km, vm, log2_page);
+  si_launch(k, dim3(num_items, p.KV, p.nsplit), dim3(160), smem, stream, p, km, vm, log2_page);
   return si_last_error();
 }
 

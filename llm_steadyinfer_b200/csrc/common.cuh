@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define SI_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -63,6 +64,42 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status) atomicMax(status, code);
+}
+
+// Programmatic dependent launch: a kernel that starts with pdl_prologue() lets the next kernel of
+// the stream begin launching while it still runs, and itself waits for the previous kernel's
+// results before touching any memory. Launched through si_launch() the kernel carries the
+// attribute that allows this overlap of launch latency; launched with <<<>>> both instructions
+// do nothing. SI_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_prologue() {
+#ifdef SI_PDL_EARLY_TRIGGER
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+#endif
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+
+static inline bool si_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("SI_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... P, typename... A>
+static inline void si_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = si_pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, P(args)...);
 }
 
 static inline int si_last_error() {

@@ -8,6 +8,7 @@ template <typename TW>
 __global__ void embedding_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
                                         int* status) {
+  pdl_prologue();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   float* o = out + (size_t)t * hidden;
@@ -26,10 +27,10 @@ SI_EXPORT int si_embedding_gather(const int* tokens, const void* table, int tabl
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == SI_BF16)
-    embedding_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
-        tokens, (const __nv_bfloat16*)table, out, hidden, vocab, status);
+    si_launch(embedding_gather_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream,
+              tokens, (const __nv_bfloat16*)table, out, hidden, vocab, status);
   else
-    embedding_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(
-        tokens, (const float*)table, out, hidden, vocab, status);
+    si_launch(embedding_gather_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
+              tokens, (const float*)table, out, hidden, vocab, status);
   return si_last_error();
 }

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(WARPS * 32, 512 / (WARPS * 32))
 gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W, long long ldw,
                    TO* __restrict__ out, long long ldo, int M, int N, int K) {
   __shared__ float red[WARPS][MT][32][4];
+  pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -129,11 +130,11 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
   if (out_dtype == SI_BF16) {
-    if (M <= 8) gemm_skinny_kernel<1, WARPS, UNROLL, bf16><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
-    else gemm_skinny_kernel<2, WARPS, UNROLL, bf16><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
   } else {
-    if (M <= 8) gemm_skinny_kernel<1, WARPS, UNROLL, float><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
-    else gemm_skinny_kernel<2, WARPS, UNROLL, float><<<blocks, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
   }
   return si_last_error();
 }

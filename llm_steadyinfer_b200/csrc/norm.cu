@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict_
                                        const int* __restrict__ rows, const TW* __restrict__ weight,
                                        TX* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_prologue();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* h = resid + (size_t)src * hidden;
@@ -135,9 +136,9 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
     int threads = nchunks > 256 ? 512 : (nchunks > 128 ? 256 : 128);
     if (num_rows >= 1024 && nchunks <= 1024) threads = min(threads, 256);   // many rows: more blocks per SM
     const int per = (nchunks + threads - 1) / threads;
-    if (per <= 1) add_rmsnorm_vec_kernel<TX, TW, 1><<<num_rows, threads, 0, stream>>>(resid, d, rows, w, o, hidden, eps);
-    else if (per <= 2) add_rmsnorm_vec_kernel<TX, TW, 2><<<num_rows, threads, 0, stream>>>(resid, d, rows, w, o, hidden, eps);
-    else add_rmsnorm_vec_kernel<TX, TW, 4><<<num_rows, threads, 0, stream>>>(resid, d, rows, w, o, hidden, eps);
+    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, dim3(num_rows), dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps);
+    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, dim3(num_rows), dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps);
+    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, dim3(num_rows), dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps);
     return si_last_error();
   }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);

@@ -94,6 +94,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, long l
                                          int num_pages, int page_size, int num_seqs, int H, int KV, int hs,
                                          int hpb, int* status) {
   typedef __nv_bfloat16 T;
+  pdl_prologue();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int seq = row_seq[t];
@@ -190,9 +191,9 @@ SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const
     int vthreads = 256;
     while (vthreads > 32 && vthreads / cpr > hpb && vthreads / 2 >= cpr) vthreads /= 2;
     if (vthreads < cpr) vthreads = ((cpr + 31) / 32) * 32;
-    rope_kv_write_vec_kernel<<<grid, vthreads, 0, stream>>>(
-        (__nv_bfloat16*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table, table_width,
-        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, hpb, status);
+    si_launch(rope_kv_write_vec_kernel, grid, dim3(vthreads), 0, stream,
+              (__nv_bfloat16*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table, table_width,
+              (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, hpb, status);
     return si_last_error();
   }
   if (dtype == SI_BF16)

@@ -55,6 +55,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   __shared__ float sh[33];
   __shared__ float chunk_sum[SAMPLE_THREADS];
   __shared__ int s_idx;
+  pdl_prologue();
   const int r = blockIdx.x;
   const float* x = logits + (size_t)r * row_stride;
   const int tid = threadIdx.x;
@@ -160,7 +161,7 @@ SI_EXPORT int si_sample(const float* logits, long long row_stride, int num_rows,
                         const unsigned long long* seed, const unsigned long long* counter,
                         int* out, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  sample_kernel<<<num_rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature,
-                                                         top_k, top_p, seed, counter, out);
+  si_launch(sample_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, vocab, temperature,
+            top_k, top_p, seed, counter, out);
   return si_last_error();
 }

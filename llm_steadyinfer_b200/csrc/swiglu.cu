@@ -19,6 +19,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 __global__ void swiglu_vec_bf16_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                        int F, long long total_chunks) {
+  pdl_prologue();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total_chunks) return;
   const int cpr = F >> 3;                       // 8-element chunks per row
@@ -61,8 +62,8 @@ SI_EXPORT int si_swiglu(const void* gu, void* out, int dtype, int num_tokens, in
   const bool aligned = ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
   if (dtype == SI_BF16 && aligned && F % 8 == 0) {
     const long long chunks = total / 8;
-    swiglu_vec_bf16_kernel<<<(unsigned)((chunks + threads - 1) / threads), threads, 0, stream>>>(
-        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, chunks);
+    si_launch(swiglu_vec_bf16_kernel, dim3((unsigned)((chunks + threads - 1) / threads)), dim3(threads), 0, stream,
+              (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, chunks);
   } else if (dtype == SI_F32 && aligned && F % 4 == 0) {
     const long long chunks = total / 4;
     swiglu_vec_f32_kernel<<<(unsigned)((chunks + threads - 1) / threads), threads, 0, stream>>>(
