@@ -1,20 +1,25 @@
 // Attention for prompt portions on the 5th-generation tensor cores (tcgen05), bf16, over the
 // paged cache. One block handles one work item (a run of consecutive query tokens of a sequence)
-// for one KV head: 128 rows = tokens x the G query heads of the KV head (row r = token r / G,
-// head r % G), against key tiles of 128.
+// for one KV head as TWO query tiles of 128 rows each (row r of a tile = token r / G of the tile,
+// head r % G; a tile holds floor(128 / G) tokens), against key tiles of 128. The two query tiles
+// share every K and V tile and take turns: while the rows of one are in the softmax, the tensor
+// cores work for the other.
 //
-//   warp 8 (producer)  looks up the pages of a tile and issues its K and V boxes by TMA
+//   warp 8 (producer)  looks up the pages of a key tile and issues its K and V boxes by TMA
 //                      (128-byte swizzle) into one of two stages;
-//   warp 9 (issuer)    S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major) and, once the
-//                      probabilities are in shared memory, O += P V (V is the MN-major operand, as
-//                      it lies in the cache); the next tile's S is issued as soon as the rows of the
-//                      current one are in registers, so it runs under the softmax;
-//   warps 0-7          two threads per row (warps 0-3 take keys 0-63 of a tile, warps 4-7 keys 64-127):
-//                      read the row of S from tensor memory (tcgen05.ld), mask, exchange the row
-//                      maximum, softmax in fp32 (exp2 of scale*log2e-scaled scores) against a base
-//                      that is raised only when the maximum has grown by more than 2^8 (then the row
-//                      of O in tensor memory is rescaled with tcgen05.ld/st), write the bf16
-//                      probabilities into the swizzled P tile; at the end read O, divide by the row sum.
+//   warp 9 (issuer)    per query tile: S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major),
+//                      and, once the probabilities stand in tensor memory, O += P V with P as the
+//                      tensor-memory A operand and V the MN-major B operand, as it lies in the cache;
+//   warps 0-3 / 4-7    one thread per row of query tile 0 / 1: a first pass over the row of S
+//                      (tcgen05.ld) finds its maximum, a second one computes exp2 of the scaled scores
+//                      in fp32 against a base that is raised only when the maximum has grown by more
+//                      than 2^8 (then the row of O in tensor memory is rescaled first), and writes the
+//                      bf16 probabilities over the columns of S that it has consumed (tcgen05.st);
+//                      at the end it reads O and divides by the row sum.
+//
+// The tensor cores run a thread's instructions in the order of issue, which is what keeps this
+// simple: S of the next key tile is issued behind P V of the current one, so it overwrites P only
+// after P has been read, and when S is complete so is every earlier product into O.
 //
 // The reference computes prompt attention row by row with its scalar split kernel
 // (src/source/op/kernels/cuda/paged_kernels.cu:96-206). Conditions here: head_dim 64 or 128, page size
@@ -22,6 +27,7 @@
 // is bounded; when one runs out the block sets SI_WAIT_LIMIT and leaves without storing.
 #include "attention_common.cuh"
 #include "tma_common.cuh"
+#include <limits.h>
 
 // 2^x in fp32 by the hardware approximation (2 ulp); exp2(-inf) = 0.
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -41,31 +47,31 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
                          const __grid_constant__ CUtensorMap vmap, int log2_page) {
   constexpr int BM = 128, BN = 128, HS = NH * 64, STAGES = 2;
   constexpr int TILE = NH * BN * 64;                 // elements of a K (or V) tile: NH halves of [128][64]
-  constexpr int TM_S = 0, TM_T = BN;                 // tensor-memory columns of S and of T = P V
-  constexpr int TM_COLS = 256;
+  constexpr int TM_S = 0, TM_O = 2 * BN;             // tensor-memory columns: S of tile q at TM_S + q*BN, O at TM_O + q*HS
+  constexpr int TM_COLS = 512;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-  __shared__ __align__(8) uint64_t s_full, s_free, p_full, t_full;
+  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_full[2];
   __shared__ unsigned tmem_slot;
   __shared__ int s_abort;
-  __shared__ float xmax[2][2][BM];                   // [tile parity][column half][row]: row maxima to exchange
-  __shared__ float xsum[2][BM];
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [NH][128][64]
-  bf16* Ps = Qs + BM * HS;                           // [2][128][64]   (keys 0-63, 64-127)
-  bf16* Ks = Ps + BM * BN;                           // [STAGES][TILE]
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [2 tiles][NH][128][64]
+  bf16* Ks = Qs + 2 * BM * HS;                       // [STAGES][TILE]
   bf16* Vs = Ks + STAGES * TILE;
 
-  // items of a prompt come in order of position, so the last ones have the most keys: start with those
-  const AttnItem item = p.items[gridDim.x - 1 - blockIdx.x];
+  // Items of a prompt come in order of position, so the last ones have the most keys: start with those,
+  // for all KV heads alike (blocks are handed out with x running fastest, and x is the KV head).
+  const AttnItem item = p.items[gridDim.y - 1 - blockIdx.y];
   if (item.ntok <= 0) return;
-  const int g = blockIdx.y;
+  const int g = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (item.seq < 0 || item.seq >= p.num_seqs) {
     if (threadIdx.x == 0) set_status(p.status, SI_BAD_SEQ);
     return;
   }
   const int* table = p.block_table + (size_t)item.seq * p.table_width;
+  const int tile_tokens = BM / p.G;                  // tokens of one query tile
+  const bool two = item.ntok > tile_tokens;          // the second query tile has rows
   const int kv_end = item.pos0 + item.ntok;
   int kv_begin = 0;
   if (p.window > 0) kv_begin = max(0, item.pos0 - p.window + 1) / BN * BN;
@@ -78,10 +84,12 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    mbar_init(&s_full, 1);
-    mbar_init(&p_full, 8);                           // one arrival per softmax warp
-    mbar_init(&s_free, 8);
-    mbar_init(&t_full, 1);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(&s_full[q], 1);
+      mbar_init(&p_full[q], 4);                      // one arrival per warp of the tile's rows
+      mbar_init(&o_full[q], 1);
+    }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -93,14 +101,16 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
     for (int i = threadIdx.x; i < TILE / 8; i += blockDim.x) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
   }
-  // query rows: tile row r is token r / G, head g*G + r % G
-  for (int id = threadIdx.x; id < BM * (HS / 8); id += blockDim.x) {
+  // query rows: row r of tile q is token q * tile_tokens + r / G, head g*G + r % G
+  for (int id = threadIdx.x; id < 2 * BM * (HS / 8); id += blockDim.x) {
     const int row = id / (HS / 8), c = id % (HS / 8);
-    const int tok = row / p.G, hh = row - tok * p.G;
+    const int q = row / BM, r = row % BM;
+    const int tl = r / p.G, hh = r - tl * p.G;
+    const int tok = q * tile_tokens + tl;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (tok < item.ntok)
+    if (tl < tile_tokens && tok < item.ntok)
       v = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
-    *reinterpret_cast<uint4*>(half_ptr<BM>(Qs, row, c)) = v;
+    *reinterpret_cast<uint4*>(half_ptr<BM>(Qs + (size_t)q * BM * HS, r, c)) = v;
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   tc05_fence_before_sync();
@@ -110,7 +120,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
 
   if (warp == 8) {
     // ---- producer: box b = (page, half, K or V) of each tile, boxes spread over the lanes. K and V
-    // have barriers of their own: a K stage is free as soon as S has been computed from it, long
+    // have barriers of their own: a K stage is free as soon as both S have been computed from it, long
     // before the V stage of the same tile, so the next keys arrive under the softmax.
     const int boxes = pages_per_tile * NH * 2;
     for (int t = 0; t < ntiles; ++t) {
@@ -133,8 +143,8 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
       bool ok = true;
-      if (t >= STAGES) ok = mbar_wait(&k_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
-      if (!__all_sync(0xffffffffu, ok)) {
+      if (t >= STAGES) ok = mbar_wait_warp(&k_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
+      if (!ok) {
         if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
         break;
       }
@@ -149,8 +159,8 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
         const size_t off = (size_t)stage * TILE + (size_t)h * (BN * 64) + (size_t)(pg * page_rows) * 64;
         tma_load_2d(Ks + off, &kmap, &k_full[stage], h * 64, row);
       }
-      if (t >= STAGES) ok = mbar_wait(&v_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
-      if (!__all_sync(0xffffffffu, ok)) {
+      if (t >= STAGES) ok = mbar_wait_warp(&v_empty[stage], (unsigned)(((t / STAGES) - 1) & 1));
+      if (!ok) {
         if (lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
         break;
       }
@@ -170,143 +180,155 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     // ---- issuer: one lane issues the tensor-core instructions
     if (lane == 0) {
       constexpr unsigned idesc_s = umma_idesc_bf16(BM, BN, false);
-      constexpr unsigned idesc_t = umma_idesc_bf16(BM, HS, true);
-      auto issue_s = [&](int t) {       // S[128, 128] = Q[128, HS] K_t[128 keys, HS]^T: 4 steps per 64-column half
+      constexpr unsigned idesc_o = umma_idesc_bf16(BM, HS, true);
+      const int nq = two ? 2 : 1;
+      auto issue_s = [&](int q, int t) {  // S_q[128, 128] = Q_q[128, HS] K_t[128 keys, HS]^T: 4 steps per 64-column half
         const int stage = t % STAGES;
 #pragma unroll
         for (int kk = 0; kk < HS / 16; ++kk) {
-          const unsigned long long qd = umma_desc_sw128(Qs + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
+          const unsigned long long qd = umma_desc_sw128(Qs + (size_t)q * BM * HS + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
           const unsigned long long kd = umma_desc_sw128(Ks + (size_t)stage * TILE + (size_t)(kk >> 2) * (BN * 64), 16, 1024) + 2 * (kk & 3);
-          tc05_mma_bf16(tmem + TM_S, qd, kd, idesc_s, kk != 0 ? 1u : 0u);
+          tc05_mma_bf16(tmem + TM_S + q * BN, qd, kd, idesc_s, kk != 0 ? 1u : 0u);
         }
-        tc05_commit(&s_full);
-        tc05_commit(&k_empty[stage]);                // the keys of this tile are not needed again
+        tc05_commit(&s_full[q]);
       };
       bool ok = ntiles > 0 && mbar_wait(&k_full[0], 0);
-      if (ok) { tc05_fence_after_sync(); issue_s(0); }
+      if (ok) {
+        tc05_fence_after_sync();
+        for (int q = 0; q < nq; ++q) issue_s(q, 0);
+        tc05_commit(&k_empty[0]);
+      }
       for (int t = 0; t < ntiles && ok; ++t) {
         const int stage = t % STAGES;
-        if (t + 1 < ntiles) {              // the next S runs while the rows of this one are being worked on
-          ok = mbar_wait(&k_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1)) && mbar_wait(&s_free, (unsigned)(t & 1));
+        const bool more = t + 1 < ntiles;
+        ok = mbar_wait(&v_full[stage], (unsigned)((t / STAGES) & 1));
+        for (int q = 0; q < nq && ok; ++q) {
+          ok = mbar_wait(&p_full[q], (unsigned)(t & 1));
           if (!ok) break;
           tc05_fence_after_sync();
-          issue_s(t + 1);
-        }
-        ok = mbar_wait(&p_full, (unsigned)(t & 1)) && mbar_wait(&v_full[stage], (unsigned)((t / STAGES) & 1));
-        if (!ok) break;
-        tc05_fence_after_sync();
-        // O[128, HS] (+)= P[128, 128 keys] V_t[128 keys, HS]: 8 steps of 16 keys; V rows are keys (MN-major B)
+          // O_q[128, HS] (+)= P_q[128, 128 keys] V_t[128 keys, HS]: 8 steps of 16 keys; P lies packed in the first
+          // 64 columns of S_q, V rows are keys (MN-major B)
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const unsigned long long pd = umma_desc_sw128(Ps + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
-          const unsigned long long vd = umma_desc_sw128(Vs + (size_t)stage * TILE, BN * 128, 1024) + 128 * kk;
-          tc05_mma_bf16(tmem + TM_T, pd, vd, idesc_t, (t | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            const unsigned long long vd = umma_desc_sw128(Vs + (size_t)stage * TILE, BN * 128, 1024) + 128 * kk;
+            tc05_mma_bf16_tmem_a(tmem + TM_O + q * HS, tmem + TM_S + q * BN + 8 * kk, vd, idesc_o, (t | kk) != 0 ? 1u : 0u);
+          }
+          if (!more) tc05_commit(&o_full[q]);
+          if (more) {                      // behind P V in the order of issue: S overwrites P only after it was read
+            if (q == 0) ok = mbar_wait(&k_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1));
+            if (!ok) break;
+            tc05_fence_after_sync();
+            issue_s(q, t + 1);
+          }
         }
-        tc05_commit(&t_full);
+        if (!ok) break;
         tc05_commit(&v_empty[stage]);
+        if (more) tc05_commit(&k_empty[(t + 1) % STAGES]);
       }
       if (!ok && ntiles > 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
     }
-  } else {
-    // ---- two threads per row: column half `wg` of every tile
-    constexpr int HALF = BN / 2, OH = HS / 2;        // keys of S and columns of O per thread
-    const int wg = warp >> 2;
+  } else if (warp < 4 || two) {
+    // ---- one thread per row of query tile q
+    const int q = warp >> 2;
     const int r = threadIdx.x & (BM - 1);            // tile row = tensor-memory lane
-    const int tok = r / p.G, hh = r - tok * p.G;
-    const int pos = tok < item.ntok ? item.pos0 + tok : -1;
+    const int tl = r / p.G, hh = r - tl * p.G;
+    const int tok = q * tile_tokens + tl;
+    const bool valid = tl < tile_tokens && tok < item.ntok;
+    const int pos = valid ? item.pos0 + tok : -1;
+    const int lo = p.window > 0 ? pos - p.window + 1 : INT_MIN;     // visible keys: lo <= j <= pos
     const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
-    float m = -INFINITY, l = 0.f;                    // base of the exponentials (log2 domain), this half's sum
+    const unsigned ts = tmem + lane_base + TM_S + q * BN, to = tmem + lane_base + TM_O + q * HS;
+    float m = -INFINITY, l = 0.f;                    // base of the exponentials (log2 domain), the row's sum
     bool alive = true;
-    // Every warp runs all iterations and meets the others at the named barrier in each of them, also
-    // after a wait has run out (`alive` false: it then skips the work), so nobody is left waiting there.
     for (int t = 0; t < ntiles; ++t) {
-      const int j0 = kv_begin + t * BN + wg * HALF;
-      if (alive) alive = __all_sync(0xffffffffu, mbar_wait(&s_full, (unsigned)(t & 1)));
-      float s[HALF];
-      float mx = -INFINITY;
-      if (alive) {
-        tc05_fence_after_sync();
+      const int j0 = kv_begin + t * BN;
+      alive = mbar_wait_warp(&s_full[q], (unsigned)(t & 1));
+      if (!alive) break;
+      tc05_fence_after_sync();
+      // most tiles lie wholly inside every row's visible range: then nothing is masked
+      const bool masked = __any_sync(0xffffffffu, !(j0 >= lo && j0 + BN - 1 <= pos));
+      float s[64];
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < HALF / 32; ++c) tmem_ld_32x32_issue(tmem + lane_base + TM_S + wg * HALF + c * 32, s + c * 32);
+      for (int b = 0; b < 2; ++b) {
+        tmem_ld_32x32_issue(ts + 64 * b, s);
+        tmem_ld_32x32_issue(ts + 64 * b + 32, s + 32);
         tmem_ld_wait();
-        tc05_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_free);         // S may be overwritten by the next tile's product
-        const bool all_visible = j0 + HALF - 1 <= pos && (p.window <= 0 || j0 > pos - p.window);
-        if (all_visible) {                           // most tiles lie wholly before the row's position
+        if (masked) {
 #pragma unroll
-          for (int i = 0; i < HALF; ++i) { s[i] *= p.scale_log2; mx = fmaxf(mx, s[i]); }
-        } else {
-#pragma unroll
-          for (int i = 0; i < HALF; ++i) {
-            const int j = j0 + i;
-            const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
-            s[i] = vis ? s[i] * p.scale_log2 : -INFINITY;
-            mx = fmaxf(mx, s[i]);
+          for (int i = 0; i < 64; ++i) {
+            const int j = j0 + 64 * b + i;
+            if (j < lo || j > pos) s[i] = -INFINITY;
           }
         }
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          m4[0] = fmaxf(m4[0], s[i]); m4[1] = fmaxf(m4[1], s[i + 1]);
+          m4[2] = fmaxf(m4[2], s[i + 2]); m4[3] = fmaxf(m4[3], s[i + 3]);
+        }
       }
-      xmax[t & 1][wg][r] = mx;
-      asm volatile("bar.sync 1, 256;\n" ::: "memory");
-      if (!alive) continue;
-      mx = fmaxf(mx, xmax[t & 1][wg ^ 1][r]);
-      // raise the base only when the maximum has outgrown it by 2^8; then O and l are rescaled
+      // the scale is positive, so the maximum may be taken before it
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      // raise the base only when the maximum has outgrown it by 2^8; then O and l are rescaled. S being
+      // complete, so is every earlier product into O.
       float factor = 1.f;
       const bool raise = mx > m + 8.f;
       if (raise) { factor = exp2f(m - mx); m = mx; }
-      const float base = m == -INFINITY ? 0.f : m;
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < HALF; ++i) { s[i] = fast_exp2(s[i] - base); sum += s[i]; }
-      l = l * factor + sum;
-      // P and O belong to the previous product until it has completed
-      if (t > 0) {
-        alive = __all_sync(0xffffffffu, mbar_wait(&t_full, (unsigned)((t - 1) & 1)));
-        if (!alive) continue;
-        tc05_fence_after_sync();
-        if (__any_sync(0xffffffffu, raise)) {
+      if (t > 0 && __any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-          for (int c = 0; c < OH / 32; ++c) {
-            float v[32];
-            tmem_ld_32x32(tmem + lane_base + TM_T + wg * OH + c * 32, v);
+        for (int c = 0; c < HS / 32; ++c) {
+          float v[32];
+          tmem_ld_32x32(to + c * 32, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= factor;
-            tmem_st_32x32(tmem + lane_base + TM_T + wg * OH + c * 32, v);
-          }
+          for (int i = 0; i < 32; ++i) v[i] *= factor;
+          tmem_st_32x32(to + c * 32, v);
         }
       }
+      const float base = m == -INFINITY ? 0.f : m;
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < HALF / 8; ++c) {
-        uint4 raw;
-        raw.x = pack_bf16(s[8 * c], s[8 * c + 1]);
-        raw.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
-        raw.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
-        raw.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-        *reinterpret_cast<uint4*>(half_ptr<BM>(Ps, r, wg * (HALF / 8) + c)) = raw;
+      for (int b = 0; b < 2; ++b) {
+        tmem_ld_32x32_issue(ts + 64 * b, s);
+        tmem_ld_32x32_issue(ts + 64 * b + 32, s + 32);
+        tmem_ld_wait();
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int j = j0 + 64 * b + i;
+            if (j < lo || j > pos) s[i] = -INFINITY;
+          }
+        }
+        unsigned pk[32];
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            s[i + u] = fast_exp2(fmaf(s[i + u], p.scale_log2, -base));    // exp2(-inf) = 0 for masked keys
+            s4[u] += s[i + u];
+          }
+          pk[i / 2] = pack_bf16(s[i], s[i + 1]);
+          pk[i / 2 + 1] = pack_bf16(s[i + 2], s[i + 3]);
+        }
+        // the probabilities of keys 64b .. 64b+63 go over columns 32b .. 32b+31 of S, which have been read
+        tmem_st_32x32_issue(ts + 32 * b, pk);
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      l = l * factor + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+      tmem_st_wait();
       tc05_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
+      if (lane == 0) mbar_arrive(&p_full[q]);
     }
-    if (alive && ntiles > 0) {
-      const bool ok = mbar_wait(&t_full, (unsigned)((ntiles - 1) & 1));
-      if (!__all_sync(0xffffffffu, ok)) alive = false;
-    }
-    // the two halves of a row add their sums (a failed wait anywhere is seen by all through s_abort)
+    if (alive && ntiles > 0) alive = mbar_wait_warp(&o_full[q], 0);
     if (!alive && lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
-    xsum[wg][r] = l;
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
-    if (!s_abort) {
+    if (alive) {
       tc05_fence_after_sync();
-      const float lt = l + xsum[wg ^ 1][r];
-      const float inv = lt > 0.f ? 1.f / lt : 0.f;
-      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + wg * OH;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs;
 #pragma unroll 1
-      for (int c = 0; c < OH / 32; ++c) {
+      for (int c = 0; c < HS / 32; ++c) {
         float v[32];
-        tmem_ld_32x32(tmem + lane_base + TM_T + wg * OH + c * 32, v);
-        if (tok < item.ntok) {
+        tmem_ld_32x32(to + c * 32, v);
+        if (valid) {
 #pragma unroll
           for (int q8 = 0; q8 < 4; ++q8) {
             uint4 raw;
@@ -334,18 +356,21 @@ SI_EXPORT int si_attn_portion_tc05_ok(int H, int KV, int hs, int page_size) {
   return si_encode_fn() != nullptr;
 }
 
-// Tokens of one item: floor(128 / G).
-SI_EXPORT int si_attn_portion_tc05_tokens(int H, int KV) { return 128 / (H / KV); }
+// Tokens of one item: two query tiles of floor(128 / G) each.
+SI_EXPORT int si_attn_portion_tc05_tokens(int H, int KV) { return 2 * (128 / (H / KV)); }
 
 template <int NH>
 static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap& vm, int num_items, int log2_page,
                   cudaStream_t stream) {
   constexpr int HS = NH * 64;
-  const size_t smem = (size_t)(128 * HS + 128 * 128 + 2 * 2 * NH * 128 * 64) * sizeof(bf16) + 1024;
+  // Q of both query tiles, two stages of K and of V. The block takes all of tensor memory, so a second
+  // block on the same SM could only wait for it: ask for more than half of the shared memory.
+  size_t smem = (size_t)(2 * 128 * HS + 2 * 2 * NH * 128 * 64) * sizeof(bf16) + 1024;
+  if (smem < 120 * 1024) smem = 120 * 1024;
   auto k = attn_portion_tc05_kernel<NH>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  k<<<dim3(num_items, p.KV), 320, smem, stream>>>(p, km, vm, log2_page);
+  k<<<dim3(p.KV, num_items), 320, smem, stream>>>(p, km, vm, log2_page);
   return si_last_error();
 }
 
@@ -357,6 +382,7 @@ SI_EXPORT int si_attn_portion_tc05(const void* q, long long q_stride, const void
                                    int page_size, int num_seqs, int H, int KV, int hs, float scale, int window,
                                    int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
+  if (num_items > 65535) return -2;                  // the grid's second dimension
   if (!si_attn_portion_tc05_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
   if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)out % 16)) return -2;
   AttnParams p;

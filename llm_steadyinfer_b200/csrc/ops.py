@@ -433,13 +433,16 @@ def attn_portion_tc05_ok(H: int, KV: int, hs: int, page_size: int) -> bool:
 
 
 def attn_portion_tc05_tokens(H: int, KV: int) -> int:
-    return 128 // (H // KV)
+    """Most tokens of one work item of ``attn_portion_tc05``."""
+    lib = build.load("attention_tc05")
+    lib.si_attn_portion_tc05_tokens.restype = _c_int
+    return lib.si_attn_portion_tc05_tokens(_c_int(H), _c_int(KV))
 
 
 def attn_portion_tc05(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int,
                       KV: int, hs: int, scale: float, window: int = 0, status=None) -> None:
     """``attn_portion`` on the tcgen05 tensor cores (TMA-fed K/V tiles, S and P V in tensor memory);
-    head_dim 64 or 128, page sizes 8 to 64, items of at most ``128 // (H // KV)`` tokens."""
+    head_dim 64 or 128, page sizes 8 to 64, items of at most ``attn_portion_tc05_tokens`` tokens."""
     _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_portion_tc05")
     f = _fn("attention_tc05", "si_attn_portion_tc05",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int,

@@ -28,6 +28,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+// The same wait for a whole warp: one lane polls (32 lanes polling one barrier take turns at it and
+// cost hundreds of cycles even when the phase is long complete), the others get its answer.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, unsigned parity) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                ::"r"(tma_smem_u32(dst)), "l"(map), "r"(tma_smem_u32(bar)), "r"(x), "r"(y) : "memory");
@@ -99,6 +106,28 @@ __device__ __forceinline__ void tmem_st_32x32(unsigned taddr, const float (&v)[3
                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
                : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
+// 32 lanes x 32 columns of raw 32-bit words into tensor memory without waiting; tmem_st_wait() after the
+// last one. Packed bf16 pairs written this way form the A operand of tc05_mma_bf16_tmem_a.
+__device__ __forceinline__ void tmem_st_32x32_issue(unsigned taddr, const unsigned* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+               :: "r"(taddr),
+                  "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                  "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                  "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                  "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem desc]: A is 128 rows (tensor-memory lanes) x 16 bf16, two to a 32-bit
+// column (element 2c in the low half of column c), so one step reads 8 columns from `a_tmem`.
+__device__ __forceinline__ void tc05_mma_bf16_tmem_a(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
+                                                     unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // Shared-memory matrix descriptor of a bf16 tile whose rows are 128 bytes (64 elements) apart and

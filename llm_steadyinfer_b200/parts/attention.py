@@ -80,8 +80,8 @@ class Attention(Mixer):
 
     def prepare(self, ctx, cache):
         """Cut the step's sequences into work items for the tensor-core kernels: runs of few
-        tokens (decode rows) for the decode kernel, longer portions in runs of
-        ``attn_portion_tokens``. One plan serves every layer with the same head layout."""
+        tokens (decode rows) for the decode kernel, longer portions in runs of the portion
+        kernel's item size. One plan serves every layer with the same head layout."""
         if not self.uses_tensor_cores():
             return
         key = ("attention", self.H, self.KV, self.hs)
@@ -91,7 +91,9 @@ class Attention(Mixer):
         tma = USE_TMA and ops.attn_decode_tma_ok(self.H, self.KV, self.hs, cache.page_size)
         dec_rows = ops.attn_decode_tma_rows(self.H, self.KV) if tma else ops.attn_decode_rows(self.H, self.KV, self.hs)
         dec_tokens = dec_rows // G
-        por_tokens = ops.attn_portion_tokens(self.H, self.KV, self.hs)
+        tc05 = USE_TC05 and ops.attn_portion_tc05_ok(self.H, self.KV, self.hs, cache.page_size)
+        por_tokens = (ops.attn_portion_tc05_tokens(self.H, self.KV) if tc05
+                      else ops.attn_portion_tokens(self.H, self.KV, self.hs))
         if por_tokens <= 0:
             raise ops.KernelError(f"attention: {G} query heads per kv head do not fit the tensor-core kernels")
         dec, por = [], []
@@ -106,7 +108,7 @@ class Attention(Mixer):
                 for b in range(0, n, por_tokens):
                     por.append((s, row0 + b, min(por_tokens, n - b), pos0 + b))
         plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma,
-                "tc05": USE_TC05 and ops.attn_portion_tc05_ok(self.H, self.KV, self.hs, cache.page_size)}
+                "tc05": tc05}
         n_dec = len(dec)
         if ctx.seq_cap is not None:                   # fixed shapes: pad with empty items
             dec += [(0, 0, 0, 0)] * (ctx.seq_cap - n_dec)
