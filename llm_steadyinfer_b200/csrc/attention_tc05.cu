@@ -7,17 +7,18 @@
 //
 //   warp 8 (producer)  looks up the pages of a key tile and issues its K and V boxes by TMA
 //                      (128-byte swizzle) into one of two stages;
-//   warp 9 (issuer)    per query tile: S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major),
-//                      and, once the probabilities stand in tensor memory, O += P V with P as the
-//                      tensor-memory A operand and V the MN-major B operand, as it lies in the cache;
-//   warps 0-3 / 4-7    one thread per row of query tile 0 / 1: a first pass over the row of S
-//                      (tcgen05.ld) finds its maximum, a second one computes exp2 of the scaled scores
-//                      in fp32 against a base that is raised only when the maximum has grown by more
-//                      than 2^8 (then the row of O in tensor memory is rescaled first), and writes the
-//                      bf16 probabilities over the columns of S that it has consumed (tcgen05.st);
-//                      at the end it reads O and divides by the row sum.
+//   warp 9 (issuer)    per query tile: S = Q K^T with tcgen05.mma into tensor memory (Q, K K-major) and,
+//                      once the probabilities stand in tensor memory, O += P V with P as the
+//                      tensor-memory A operand and V the MN-major B operand, as it lies in the cache.
+//                      Its order of issue, P V and the next S of tile 0, then of tile 1, keeps the two
+//                      tiles in opposite phases: one in the softmax while the tensor cores serve the other;
+//   warps 0-3 / 4-7    one thread per row of query tile 0 / 1: reads the row of S (tcgen05.ld), takes its
+//                      maximum, computes exp2 of the scaled scores in fp32 against a base that is raised
+//                      only when the maximum has grown by more than 2^8 (then the row of O in tensor
+//                      memory is rescaled first), and writes the bf16 probabilities over the first
+//                      columns of S (tcgen05.st); at the end it reads O and divides by the row sum.
 //
-// The tensor cores run a thread's instructions in the order of issue, which is what keeps this
+// The tensor cores run one thread's instructions in the order of issue, which is what keeps this
 // simple: S of the next key tile is issued behind P V of the current one, so it overwrites P only
 // after P has been read, and when S is complete so is every earlier product into O.
 //
@@ -51,7 +52,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   constexpr int TM_COLS = 512;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_full[2];
+  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_full[2];   // per query tile
   __shared__ unsigned tmem_slot;
   __shared__ int s_abort;
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -101,22 +102,38 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
     for (int i = threadIdx.x; i < TILE / 8; i += blockDim.x) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
   }
-  // query rows: row r of tile q is token q * tile_tokens + r / G, head g*G + r % G
-  for (int id = threadIdx.x; id < 2 * BM * (HS / 8); id += blockDim.x) {
-    const int row = id / (HS / 8), c = id % (HS / 8);
-    const int q = row / BM, r = row % BM;
-    const int tl = r / p.G, hh = r - tl * p.G;
-    const int tok = q * tile_tokens + tl;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tl < tile_tokens && tok < item.ntok)
-      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
-    *reinterpret_cast<uint4*>(half_ptr<BM>(Qs + (size_t)q * BM * HS, r, c)) = v;
-  }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   tc05_fence_before_sync();
-  __syncthreads();
+  __syncthreads();                                   // barriers, tensor memory and the zeroed rows stand
   tc05_fence_after_sync();
   const unsigned tmem = tmem_slot;
+  if (warp != 8) {
+    // Query rows, while the producer already fetches the first keys: row r of tile q is token
+    // q * tile_tokens + r / G, head g*G + r % G. All loads of a thread are issued before its stores.
+    constexpr int NT = 288, PER = (2 * BM * (HS / 8) + NT - 1) / NT;
+    const int tid = warp == 9 ? 256 + lane : threadIdx.x;
+    const int rows = two ? 2 * BM : BM;              // the second tile is not read when it has no token
+    uint4 v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int id = tid + i * NT;
+      const int row = id / (HS / 8), c = id % (HS / 8);
+      const int q = row / BM, r = row % BM;
+      const int tl = r / p.G, hh = r - tl * p.G;
+      const int tok = q * tile_tokens + tl;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (row < rows && tl < tile_tokens && tok < item.ntok)
+        v[i] = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int id = tid + i * NT;
+      const int row = id / (HS / 8), c = id % (HS / 8);
+      if (row < rows) *reinterpret_cast<uint4*>(half_ptr<BM>(Qs + (size_t)(row / BM) * BM * HS, row % BM, c)) = v[i];
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    asm volatile("bar.sync 1, 288;\n" ::: "memory");   // warps 0-7 and 9
+  }
 
   if (warp == 8) {
     // ---- producer: box b = (page, half, K or V) of each tile, boxes spread over the lanes. K and V
@@ -177,56 +194,65 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       }
     }
   } else if (warp == 9) {
-    // ---- issuer: one lane issues the tensor-core instructions
-    if (lane == 0) {
-      constexpr unsigned idesc_s = umma_idesc_bf16(BM, BN, false);
-      constexpr unsigned idesc_o = umma_idesc_bf16(BM, HS, true);
-      const int nq = two ? 2 : 1;
-      auto issue_s = [&](int q, int t) {  // S_q[128, 128] = Q_q[128, HS] K_t[128 keys, HS]^T: 4 steps per 64-column half
-        const int stage = t % STAGES;
+    // ---- issuer: S_0(0) S_1(0) | P V_0(0) S_0(1) | P V_1(0) S_1(1) | P V_0(1) S_0(2) | ...
+    // The whole warp runs this code and one elected lane issues: what an instruction needs (descriptors,
+    // addresses) is then uniform over the warp. The descriptors are made once and only their address
+    // fields (units of 16 bytes) advance. An instruction is accepted only as fast as the tensor cores
+    // run, so whatever else this warp does between two of them leaves the tensor cores idle.
+    constexpr unsigned idesc_s = umma_idesc_bf16(BM, BN, false);
+    constexpr unsigned idesc_o = umma_idesc_bf16(BM, HS, true);
+    constexpr unsigned U_TILE = TILE * 2 / 16, U_QTILE = BM * HS * 2 / 16, U_HALF = BN * 64 * 2 / 16;
+    const int nq = two ? 2 : 1;
+    const unsigned long long qd0 = umma_desc_sw128(Qs, 16, 1024);
+    const unsigned long long kd0 = umma_desc_sw128(Ks, 16, 1024);
+    const unsigned long long vd0 = umma_desc_sw128(Vs, BN * 128, 1024);
+    auto issue_s = [&](int q, int t) {  // S_q[128, 128] = Q_q[128, HS] K_t[128 keys, HS]^T: 4 steps per 64-column half
+      const unsigned long long qd = qd0 + (unsigned)q * U_QTILE;
+      const unsigned long long kd = kd0 + (unsigned)(t % STAGES) * U_TILE;
+      const unsigned sd = tmem + TM_S + q * BN;
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < HS / 16; ++kk) {
-          const unsigned long long qd = umma_desc_sw128(Qs + (size_t)q * BM * HS + (size_t)(kk >> 2) * (BM * 64), 16, 1024) + 2 * (kk & 3);
-          const unsigned long long kd = umma_desc_sw128(Ks + (size_t)stage * TILE + (size_t)(kk >> 2) * (BN * 64), 16, 1024) + 2 * (kk & 3);
-          tc05_mma_bf16(tmem + TM_S + q * BN, qd, kd, idesc_s, kk != 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < HS / 16; ++kk)
+          tc05_mma_bf16(sd, qd + ((kk >> 2) * U_HALF + 2 * (kk & 3)), kd + ((kk >> 2) * U_HALF + 2 * (kk & 3)), idesc_s, kk != 0 ? 1u : 0u);
         tc05_commit(&s_full[q]);
-      };
-      bool ok = ntiles > 0 && mbar_wait(&k_full[0], 0);
-      if (ok) {
-        tc05_fence_after_sync();
-        for (int q = 0; q < nq; ++q) issue_s(q, 0);
-        tc05_commit(&k_empty[0]);
+        if (q == nq - 1) tc05_commit(&k_empty[t % STAGES]);      // the keys of this tile are not needed again
       }
-      for (int t = 0; t < ntiles && ok; ++t) {
-        const int stage = t % STAGES;
-        const bool more = t + 1 < ntiles;
-        ok = mbar_wait(&v_full[stage], (unsigned)((t / STAGES) & 1));
-        for (int q = 0; q < nq && ok; ++q) {
-          ok = mbar_wait(&p_full[q], (unsigned)(t & 1));
+      __syncwarp();
+    };
+    bool ok = ntiles > 0 && mbar_wait_warp(&k_full[0], 0);
+    if (ok) {
+      tc05_fence_after_sync();
+      for (int q = 0; q < nq; ++q) issue_s(q, 0);
+    }
+    for (int t = 0; t < ntiles && ok; ++t) {
+      const int stage = t % STAGES;
+      const bool more = t + 1 < ntiles;
+      ok = mbar_wait_warp(&v_full[stage], (unsigned)((t / STAGES) & 1));
+      for (int q = 0; q < nq && ok; ++q) {
+        ok = mbar_wait_warp(&p_full[q], (unsigned)(t & 1));
+        if (!ok) break;
+        tc05_fence_after_sync();
+        // O_q[128, HS] (+)= P_q[128, 128 keys] V_t[128 keys, HS]: 8 steps of 16 keys; P lies packed in the first
+        // 64 columns of S_q, V rows are keys (MN-major B)
+        const unsigned long long vd = vd0 + (unsigned)stage * U_TILE;
+        const unsigned sd = tmem + TM_S + q * BN, od = tmem + TM_O + q * HS;
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            tc05_mma_bf16_tmem_a(od, sd + 8 * kk, vd + 128 * kk, idesc_o, (t | kk) != 0 ? 1u : 0u);
+          if (!more) tc05_commit(&o_full[q]);
+          if (q == nq - 1) tc05_commit(&v_empty[stage]);
+        }
+        __syncwarp();
+        if (more) {                        // behind P V in the order of issue: S overwrites P only after it was read
+          if (q == 0) ok = mbar_wait_warp(&k_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1));
           if (!ok) break;
           tc05_fence_after_sync();
-          // O_q[128, HS] (+)= P_q[128, 128 keys] V_t[128 keys, HS]: 8 steps of 16 keys; P lies packed in the first
-          // 64 columns of S_q, V rows are keys (MN-major B)
-#pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            const unsigned long long vd = umma_desc_sw128(Vs + (size_t)stage * TILE, BN * 128, 1024) + 128 * kk;
-            tc05_mma_bf16_tmem_a(tmem + TM_O + q * HS, tmem + TM_S + q * BN + 8 * kk, vd, idesc_o, (t | kk) != 0 ? 1u : 0u);
-          }
-          if (!more) tc05_commit(&o_full[q]);
-          if (more) {                      // behind P V in the order of issue: S overwrites P only after it was read
-            if (q == 0) ok = mbar_wait(&k_full[(t + 1) % STAGES], (unsigned)(((t + 1) / STAGES) & 1));
-            if (!ok) break;
-            tc05_fence_after_sync();
-            issue_s(q, t + 1);
-          }
+          issue_s(q, t + 1);
         }
-        if (!ok) break;
-        tc05_commit(&v_empty[stage]);
-        if (more) tc05_commit(&k_empty[(t + 1) % STAGES]);
       }
-      if (!ok && ntiles > 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
     }
+    if (!ok && ntiles > 0 && lane == 0) { set_status(p.status, SI_WAIT_LIMIT); s_abort = 1; }
   } else if (warp < 4 || two) {
     // ---- one thread per row of query tile q
     const int q = warp >> 2;
@@ -245,27 +271,23 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       alive = mbar_wait_warp(&s_full[q], (unsigned)(t & 1));
       if (!alive) break;
       tc05_fence_after_sync();
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32_issue(ts + 32 * c, s + 32 * c);
+      tmem_ld_wait();
       // most tiles lie wholly inside every row's visible range: then nothing is masked
-      const bool masked = __any_sync(0xffffffffu, !(j0 >= lo && j0 + BN - 1 <= pos));
-      float s[64];
+      if (__any_sync(0xffffffffu, !(j0 >= lo && j0 + BN - 1 <= pos))) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int j = j0 + i;
+          if (j < lo || j > pos) s[i] = -INFINITY;
+        }
+      }
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        tmem_ld_32x32_issue(ts + 64 * b, s);
-        tmem_ld_32x32_issue(ts + 64 * b + 32, s + 32);
-        tmem_ld_wait();
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int j = j0 + 64 * b + i;
-            if (j < lo || j > pos) s[i] = -INFINITY;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          m4[0] = fmaxf(m4[0], s[i]); m4[1] = fmaxf(m4[1], s[i + 1]);
-          m4[2] = fmaxf(m4[2], s[i + 2]); m4[3] = fmaxf(m4[3], s[i + 3]);
-        }
+      for (int i = 0; i < BN; i += 4) {
+        m4[0] = fmaxf(m4[0], s[i]); m4[1] = fmaxf(m4[1], s[i + 1]);
+        m4[2] = fmaxf(m4[2], s[i + 2]); m4[3] = fmaxf(m4[3], s[i + 3]);
       }
       // the scale is positive, so the maximum may be taken before it
       const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
@@ -273,7 +295,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       // complete, so is every earlier product into O.
       float factor = 1.f;
       const bool raise = mx > m + 8.f;
-      if (raise) { factor = exp2f(m - mx); m = mx; }
+      if (raise) { factor = fast_exp2(m - mx); m = mx; }   // exp2(-inf) = 0 on the first keys
       if (t > 0 && __any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
         for (int c = 0; c < HS / 32; ++c) {
@@ -287,29 +309,20 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       const float base = m == -INFINITY ? 0.f : m;
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        tmem_ld_32x32_issue(ts + 64 * b, s);
-        tmem_ld_32x32_issue(ts + 64 * b + 32, s + 32);
-        tmem_ld_wait();
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int j = j0 + 64 * b + i;
-            if (j < lo || j > pos) s[i] = -INFINITY;
-          }
-        }
+      for (int b = 0; b < BN / 64; ++b) {
         unsigned pk[32];
 #pragma unroll
         for (int i = 0; i < 64; i += 4) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            s[i + u] = fast_exp2(fmaf(s[i + u], p.scale_log2, -base));    // exp2(-inf) = 0 for masked keys
-            s4[u] += s[i + u];
+          for (int w = 0; w < 4; ++w) {
+            const float e = fast_exp2(fmaf(s[64 * b + i + w], p.scale_log2, -base));    // exp2(-inf) = 0 for masked keys
+            s[64 * b + i + w] = e;
+            s4[w] += e;
           }
-          pk[i / 2] = pack_bf16(s[i], s[i + 1]);
-          pk[i / 2 + 1] = pack_bf16(s[i + 2], s[i + 3]);
+          pk[i / 2] = pack_bf16(s[64 * b + i], s[64 * b + i + 1]);
+          pk[i / 2 + 1] = pack_bf16(s[64 * b + i + 2], s[64 * b + i + 3]);
         }
-        // the probabilities of keys 64b .. 64b+63 go over columns 32b .. 32b+31 of S, which have been read
+        // the probabilities of keys 64b .. 64b+63 go over columns 32b .. 32b+31 of S, which is in registers
         tmem_st_32x32_issue(ts + 32 * b, pk);
       }
       l = l * factor + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
@@ -324,19 +337,21 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       tc05_fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs;
-#pragma unroll 1
-      for (int c = 0; c < HS / 32; ++c) {
-        float v[32];
-        tmem_ld_32x32(to + c * 32, v);
+#pragma unroll
+      for (int c = 0; c < HS / 64; ++c) {
+        float v[64];
+        tmem_ld_32x32_issue(to + c * 64, v);
+        tmem_ld_32x32_issue(to + c * 64 + 32, v + 32);
+        tmem_ld_wait();
         if (valid) {
 #pragma unroll
-          for (int q8 = 0; q8 < 4; ++q8) {
+          for (int q8 = 0; q8 < 8; ++q8) {
             uint4 raw;
             raw.x = pack_bf16(v[8 * q8] * inv, v[8 * q8 + 1] * inv);
             raw.y = pack_bf16(v[8 * q8 + 2] * inv, v[8 * q8 + 3] * inv);
             raw.z = pack_bf16(v[8 * q8 + 4] * inv, v[8 * q8 + 5] * inv);
             raw.w = pack_bf16(v[8 * q8 + 6] * inv, v[8 * q8 + 7] * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + q8 * 8) = raw;
+            *reinterpret_cast<uint4*>(dst + c * 64 + q8 * 8) = raw;
           }
         }
       }

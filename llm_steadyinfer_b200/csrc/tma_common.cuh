@@ -24,13 +24,15 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 // Bounded wait: false when the phase did not complete within the limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  if (mbar_try_wait(bar, parity)) return true;       // the common case costs one probe, not a loop
   for (int it = 0; it < (1 << 20); ++it)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
-// The same wait for a whole warp: one lane polls (32 lanes polling one barrier take turns at it and
-// cost hundreds of cycles even when the phase is long complete), the others get its answer.
+// The same wait for a whole warp: after one probe by all lanes, one lane polls and the others get
+// its answer.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, unsigned parity) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;   // already complete: one probe by all
   int ok = 1;
   if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
@@ -53,6 +55,15 @@ __device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
 }
 __device__ __forceinline__ void tc05_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc05_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// True in exactly one lane of a converged warp. The tensor-core instructions take their operands from
+// warp-uniform values: code that the whole warp runs, with only the instruction itself under this
+// predicate, lets the compiler keep descriptors and addresses in uniform registers, which a branch
+// on the lane number does not.
+__device__ __forceinline__ bool elect_one() {
+  unsigned pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
 // D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues.
 __device__ __forceinline__ void tc05_mma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
                                               unsigned idesc, unsigned accumulate) {
