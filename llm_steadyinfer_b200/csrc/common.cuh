@@ -5,6 +5,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -61,6 +62,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   __syncthreads();
   return scratch[32];
 }
+
+// The feed-forward's gated activation: silu(g) * u in fp32.
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.f + expf(-g))) * u; }
 
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status) atomicMax(status, code);

@@ -11,6 +11,11 @@
 //   the same mapping for A and B.
 // A block owns 16 output columns; its warps take the 32-wide k chunks in turn (adjacent warps
 // read adjacent 64 bytes of a row) and their partial sums are added in a fixed order.
+//
+// With SWIGLU the product is the stacked gate/up projection with gates and ups interleaved in
+// groups of 8 rows of W, so that a block's 16 columns are 8 gates and the 8 ups that belong to
+// them: the block stores out[m, f] = silu(gate) * up (both rounded to bf16 first, as when the
+// projection is stored and a second kernel applies the activation) and no second kernel runs.
 #include "common.cuh"
 
 typedef __nv_bfloat16 bf16;
@@ -40,7 +45,7 @@ __device__ __forceinline__ uint4 ld_cached(const bf16* p) {      // x: small, sh
 
 // Rows of W or x beyond N or M are replaced by row 0: their products land in output elements
 // that are never stored, so the loads need no predicate.
-template <int MT, int WARPS, int UNROLL, typename TO>
+template <int MT, int WARPS, int UNROLL, typename TO, bool SWIGLU = false>
 __global__ void __launch_bounds__(WARPS * 32, 512 / (WARPS * 32))
 gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W, long long ldw,
                    TO* __restrict__ out, long long ldo, int M, int N, int K) {
@@ -104,15 +109,29 @@ gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __rest
 #pragma unroll
     for (int e = 0; e < 4; ++e) red[warp][mt][lane][e] = acc[mt][e];
   __syncthreads();
-  // threads (mt, lane, e) add the warps' partial sums in warp order and store
-  for (int idx = threadIdx.x; idx < MT * 32 * 4; idx += WARPS * 32) {
-    const int mt = idx / 128, ln = (idx >> 2) & 31, e = idx & 3;
-    float s = 0.f;
+  if constexpr (SWIGLU) {
+    // threads (mt, lane, e) add the partial sums of gate (element e) and up (element e + 2) of one output
+    for (int idx = threadIdx.x; idx < MT * 32 * 2; idx += WARPS * 32) {
+      const int mt = idx / 64, ln = (idx >> 1) & 31, e = idx & 1;
+      float gs = 0.f, us = 0.f;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) s += red[w][mt][ln][e];
-    const int n = n0 + (ln >> 2) + ((e >> 1) ? 8 : 0);
-    const int m = mt * 8 + (ln & 3) * 2 + (e & 1);
-    if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, s);
+      for (int w = 0; w < WARPS; ++w) { gs += red[w][mt][ln][e]; us += red[w][mt][ln][e + 2]; }
+      const int f = blockIdx.x * 8 + (ln >> 2);
+      const int m = mt * 8 + (ln & 3) * 2 + e;
+      if (2 * f < N && m < M)
+        store_out<TO>(out + (size_t)m * ldo + f, silu_mul(__bfloat162float(__float2bfloat16_rn(gs)), __bfloat162float(__float2bfloat16_rn(us))));
+    }
+  } else {
+    // threads (mt, lane, e) add the warps' partial sums in warp order and store
+    for (int idx = threadIdx.x; idx < MT * 32 * 4; idx += WARPS * 32) {
+      const int mt = idx / 128, ln = (idx >> 2) & 31, e = idx & 3;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) s += red[w][mt][ln][e];
+      const int n = n0 + (ln >> 2) + ((e >> 1) ? 8 : 0);
+      const int m = mt * 8 + (ln & 3) * 2 + (e & 1);
+      if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, s);
+    }
   }
 }
 
@@ -136,5 +155,21 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
     if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
     else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
   }
+  return si_last_error();
+}
+
+// out[M, F] = silu(gate) * up of the stacked projection x[M, K] W[2F, K]^T whose rows are interleaved in
+// groups of 8 (8 gates, their 8 ups, ...); F a multiple of 8, bf16 output.
+SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
+                                    int M, int F, int K, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (F % 8)) return -2;
+  if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
+  constexpr int WARPS = 8, UNROLL = 8;
+  const unsigned blocks = (unsigned)(F / 8);
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K);
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K);
   return si_last_error();
 }

@@ -182,14 +182,17 @@ def paged_attention_ref(q, k_cache, v_cache, block_table, row_seq, positions, ou
              _ptr(status), _stream()), f"paged_attention_ref(head_dim={hs})")
 
 
-def swiglu(gu, out) -> None:
-    """out[t,f] = silu(gu[t,f]) * gu[t,F+f]."""
+def swiglu(gu, out, group=None) -> None:
+    """out[t,f] = silu(gate[t,f]) * up[t,f] from the stacked projection gu[t, 0..2F): gates and ups
+    interleaved in groups of ``group`` columns (default F: all gates, then all ups)."""
     _cuda(gu, out)
     T, F = out.shape
+    group = F if group is None else int(group)
     _need(gu.shape == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous()
           and gu.dtype == out.dtype, "swiglu: gu must be [T, 2F] like out [T, F]")
-    f = _fn("swiglu", "si_swiglu", [_c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
-    _check(f(_ptr(gu), _ptr(out), _dt(out), T, F, _stream()), "swiglu")
+    _need(group > 0 and F % group == 0, "swiglu: the group must divide F")
+    f = _fn("swiglu", "si_swiglu", [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(gu), _ptr(out), _dt(out), T, F, group, _stream()), "swiglu")
 
 
 def gemm_f32(a, w, out) -> None:
@@ -382,6 +385,20 @@ def gemm_skinny(a, w, out) -> None:
             [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _dt(out), M, N, K, _stream()),
            f"gemm_skinny(M={M}, N={N}, K={K})")
+
+
+def gemm_skinny_swiglu(a, w, out) -> None:
+    """out[M,F] = silu(gate) * up of a[M,K] @ w[2F,K]^T for M <= 16, the rows of w interleaved in groups of 8
+    (8 gates, their 8 ups, ...): the activation runs in the product's epilogue."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    F = out.shape[1]
+    _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
+          "gemm_skinny_swiglu: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
+    _need(gemm_skinny_ok(a, w, out), "gemm_skinny_swiglu: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_skinny", "si_gemm_skinny_swiglu", [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, F, K, _stream()),
+           f"gemm_skinny_swiglu(M={M}, F={F}, K={K})")
 
 
 # ---- tcgen05 matrix product (many rows) -------------------------------------------------------

@@ -1,6 +1,9 @@
 """Gated feed-forward part: ``down(silu(gate(x)) * up(x))`` without biases, as the reference's
 block computes it (src/source/model/llama3.cpp:1149-1180). gate and up are stacked into one
-[2F, d] matrix at load so one product feeds the activation kernel.
+[2F, d] matrix at load so one product feeds the activation: when F is a multiple of 8 the rows
+are interleaved in groups of 8 (8 rows of gate, the 8 rows of up that belong to them, ...), so
+that the few-row product holds a gate and its up in one block and applies the activation in
+its epilogue; the activation kernel of the many-row path reads the same interleaved columns.
 """
 from __future__ import annotations
 
@@ -8,7 +11,10 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, register_feed_forward
+from . import linear as linear_mod
 from .linear import linear
+
+INTERLEAVE = 8         # rows of gate, then rows of up, in the stacked weight
 
 
 class GatedMLP(FeedForward):
@@ -18,6 +24,7 @@ class GatedMLP(FeedForward):
         self.inter = int(params["intermediate_size"])
         if params.get("activation", "silu") != "silu":
             raise ValueError(f"gated_mlp: activation {params['activation']!r} is not supported")
+        self.group = INTERLEAVE if self.inter % INTERLEAVE == 0 else self.inter
         self.gate_up = None
         self.down = None
 
@@ -27,15 +34,22 @@ class GatedMLP(FeedForward):
                 "down_proj.weight": (self.hidden, self.inter)}
 
     def load_weights(self, tensors):
-        self.gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], 0).contiguous()
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        n = self.inter // self.group
+        self.gate_up = torch.stack([gate.view(n, self.group, self.hidden), up.view(n, self.group, self.hidden)], 1) \
+            .reshape(2 * self.inter, self.hidden).contiguous()
         self.down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x, ctx):
         T = x.shape[0]
-        gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
-        linear(x, self.gate_up, gu)
         act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
-        ops.swiglu(gu, act)
+        if (self.group == INTERLEAVE and linear_mod.USE_SKINNY and act.dtype == torch.bfloat16
+                and ops.gemm_skinny_ok(x, self.gate_up, act)):
+            ops.gemm_skinny_swiglu(x, self.gate_up, act)
+        else:
+            gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
+            linear(x, self.gate_up, gu)
+            ops.swiglu(gu, act, self.group)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(act, self.down, out)
         return out

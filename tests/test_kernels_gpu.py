@@ -75,6 +75,46 @@ def test_swiglu(dtype, T, F):
     assert (out.double().cpu() - want).abs().max().item() <= tol
 
 
+def _interleave(gate, up, group):
+    """Columns of gate and up interleaved in groups of `group`, as the stacked projection lays them out."""
+    T, F = gate.shape
+    return torch.stack([gate.view(T, F // group, group), up.view(T, F // group, group)], 2).reshape(T, 2 * F)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,F,group", [(3, 320, 8), (5, 1336, 8), (4, 36, 4), (2, 30, 3)])
+def test_swiglu_interleaved(dtype, T, F, group):
+    g = torch.Generator().manual_seed(22)
+    gate = (3 * torch.randn(T, F, generator=g)).to(dtype)
+    up = (3 * torch.randn(T, F, generator=g)).to(dtype)
+    gu = _interleave(gate, up, group).contiguous().to(DEV)
+    out = torch.empty(T, F, dtype=dtype, device=DEV)
+    ops().swiglu(gu, out, group)
+    want = plain_llama.swiglu(gate.double(), up.double())
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -8 * want.abs().max().item()
+    assert (out.double().cpu() - want).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 64, 96), (8, 1336, 320), (11, 40, 1000), (16, 256, 72)])
+def test_gemm_skinny_swiglu(M, F, K):
+    """The few-row gate/up product with the activation in its epilogue equals the product stored in bf16
+    followed by the activation kernel."""
+    g = torch.Generator().manual_seed(23)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    wg = (torch.randn(F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    wu = (torch.randn(F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    w = _interleave(wg.t().contiguous(), wu.t().contiguous(), 8).t().contiguous().to(DEV)     # rows interleaved
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops().gemm_skinny_swiglu(a, w, out)
+    gu = torch.empty(M, 2 * F, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_skinny(a, w, gu)
+    two = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    ops().swiglu(gu, two, 8)
+    assert torch.equal(out, two)
+    want = plain_llama.swiglu(a.double().cpu() @ wg.double().T, a.double().cpu() @ wu.double().T)
+    assert (out.double().cpu() - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (7, 513, 320), (130, 200, 1336), (64, 64, 16), (3, 5, 7)])
 def test_gemm_f32(M, N, K):
     g = torch.Generator().manual_seed(3)
