@@ -226,6 +226,26 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, seed=None, cou
              _ptr(seed), _ptr(counter), _ptr(out), _stream()), "sample")
 
 
+def argmax_scratch_words(rows: int) -> int:
+    lib = build.load("sampling")
+    lib.si_argmax_scratch_words.restype = _c_ll
+    return int(lib.si_argmax_scratch_words(_c_int(rows)))
+
+
+def argmax(logits, out, scratch) -> None:
+    """Greedy pick per row of fp32 logits (ties to the lowest index) with the vocabulary of a row split over
+    many blocks; ``scratch``: int32, ``argmax_scratch_words(capacity)`` long for some capacity >= rows,
+    zeroed once by the caller and then left to this function."""
+    _cuda(logits, out, scratch)
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "argmax: logits must be fp32 rows")
+    _i32(out, "out"); _i32(scratch, "scratch")
+    R, V = logits.shape
+    capacity = scratch.numel() // argmax_scratch_words(1)
+    _need(capacity >= R and scratch.is_contiguous(), "argmax: scratch too small")
+    f = _fn("sampling", "si_argmax", [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_p, _c_p])
+    _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(scratch), capacity, _ptr(out), _stream()), "argmax")
+
+
 # ---- tensor-core attention (bf16) ---------------------------------------------------------
 
 _c_llr = ctypes.c_longlong

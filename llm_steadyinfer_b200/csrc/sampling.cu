@@ -156,6 +156,73 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   }
 }
 
+// Greedy rows only: the vocabulary of a row is split over ARGMAX_SPLITS blocks, each leaves its
+// (maximum, lowest index) in `scratch`, and the block that comes last (a ticket per row) merges them;
+// it also puts the ticket back to zero for the next launch. One block per row, as in sample_kernel,
+// leaves most of the SMs idle while a few of them read the whole row.
+#define ARGMAX_SPLITS 32
+#define ARGMAX_THREADS 256
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_split_kernel(const float* __restrict__ logits, long long row_stride, int vocab, float* __restrict__ part_max,
+                    int* __restrict__ part_idx, int* __restrict__ tickets, int* __restrict__ out) {
+  __shared__ float sh[33];
+  __shared__ int s_idx, s_last;
+  pdl_prologue();
+  const int r = blockIdx.y, sp = blockIdx.x;
+  const float* x = logits + (size_t)r * row_stride;
+  const int per = (vocab + ARGMAX_SPLITS - 1) / ARGMAX_SPLITS;
+  const int b = sp * per, e = min(vocab, b + per);
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = b + threadIdx.x; i < e; i += ARGMAX_THREADS) {
+    const float v = x[i];
+    if (v > best) { best = v; best_i = i; }
+  }
+  const float mx = block_reduce_max_f(best, sh);
+  if (threadIdx.x == 0) s_idx = 0x7fffffff;
+  __syncthreads();
+  if (best == mx && best_i != 0x7fffffff) atomicMin(&s_idx, best_i);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    part_max[r * ARGMAX_SPLITS + sp] = mx;
+    part_idx[r * ARGMAX_SPLITS + sp] = s_idx;
+    __threadfence();
+    s_last = atomicAdd(&tickets[r], 1) == ARGMAX_SPLITS - 1;
+  }
+  __syncthreads();
+  if (!s_last || threadIdx.x >= 32) return;
+  __threadfence();
+  float m = __ldcg(part_max + r * ARGMAX_SPLITS + threadIdx.x);     // ARGMAX_SPLITS == 32: one per lane
+  int idx = __ldcg(part_idx + r * ARGMAX_SPLITS + threadIdx.x);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (m2 > m || (m2 == m && i2 < idx)) { m = m2; idx = i2; }
+  }
+  if (threadIdx.x == 0) {
+    out[r] = idx == 0x7fffffff ? 0 : idx;
+    tickets[r] = 0;
+  }
+}
+
+// Words of scratch (4 bytes each) that si_argmax needs for up to `capacity` rows; the caller zeroes them
+// once. The tickets stand first, so that they lie in the same place for every number of rows.
+SI_EXPORT long long si_argmax_scratch_words(int capacity) { return (long long)capacity * (2 * ARGMAX_SPLITS + 1); }
+
+SI_EXPORT int si_argmax(const float* logits, long long row_stride, int num_rows, int vocab, void* scratch, int capacity,
+                        int* out, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (!scratch || num_rows > capacity || num_rows > 65535) return -2;
+  int* tickets = (int*)scratch;
+  float* part_max = (float*)scratch + capacity;
+  int* part_idx = (int*)scratch + capacity + (size_t)capacity * ARGMAX_SPLITS;
+  si_launch(argmax_split_kernel, dim3(ARGMAX_SPLITS, num_rows), dim3(ARGMAX_THREADS), 0, stream, logits, row_stride,
+            vocab, part_max, part_idx, tickets, out);
+  return si_last_error();
+}
+
 SI_EXPORT int si_sample(const float* logits, long long row_stride, int num_rows, int vocab,
                         const float* temperature, const int* top_k, const float* top_p,
                         const unsigned long long* seed, const unsigned long long* counter,

@@ -22,6 +22,7 @@ class Sampler:
         self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
         self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._argmax_scratch = torch.zeros(ops.argmax_scratch_words(max_rows), dtype=torch.int32, device=self.device)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, int, int]]) -> torch.Tensor:
         """``rows[r] = (params, seed, index of the output token)``; returns int32 [R] on the device."""
@@ -30,7 +31,7 @@ class Sampler:
             raise ValueError(f"sampler got {R} logits rows for {len(rows)} requests (limit {self.max_rows})")
         out = self._out[:R]
         if all(p.greedy for p, _, _ in rows):
-            ops.sample(logits, out)
+            ops.argmax(logits, out, self._argmax_scratch)
             return out
         h = self._host.numpy()
         n = self.max_rows

@@ -218,6 +218,27 @@ def test_rope_kv_write(dtype, H, KV, hs, rot, page_size):
         assert torch.equal(vc[page, :, off], v3[t])
 
 
+@pytest.mark.parametrize("R,V", [(1, 31), (5, 1000), (24, 50257), (3, 128256)])
+def test_argmax_split(R, V):
+    """The greedy pick with a row split over many blocks: ties to the lowest index, also across blocks;
+    repeated calls with different numbers of rows share one scratch buffer."""
+    g = torch.Generator().manual_seed(60 + R)
+    o = ops()
+    scratch = torch.zeros(o.argmax_scratch_words(32), dtype=torch.int32, device=DEV)
+    for rows in (R, max(1, R // 2), R):
+        logits = (2.5 * torch.randn(rows, V, generator=g)).float()
+        top = logits.max().item() + 1
+        logits[0, V // 3] = logits[0, V - 1] = top                 # a tie in different blocks
+        dl = logits.to(DEV)
+        out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        o.argmax(dl, out, scratch)
+        assert out.tolist() == [plain_llama.sample(logits[r]) for r in range(rows)]
+        assert out[0].item() == V // 3
+        one = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        o.sample(dl, one)
+        assert torch.equal(one, out)
+
+
 def test_sampling_kernel_matches_plain():
     g = torch.Generator().manual_seed(6)
     V, R = 1000, 24
