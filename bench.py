@@ -131,7 +131,7 @@ def main() -> int:
     init_random(model, seed=0)
     B, CTX, PAGE = args.batch, args.context, 16
     big = 1 if (args.no_points or args.section != "all") else max(B, 64)
-    llm = LLM(model, dtype="bfloat16", max_batch=max(B, big), max_seq_len=CTX, max_gen_len=K + W + 8,
+    llm = LLM(model, dtype="bfloat16", max_batch=max(B, big), max_seq_len=CTX, max_gen_len=K + W + 16 + args.batch * (-(-args.context // 2048)),
               block_size=PAGE, max_num_batched_tokens=2048, enable_prefix_cache=False)
     runner, mgr = llm.runner, llm.runner.manager
     gen = torch.Generator().manual_seed(1)
@@ -237,9 +237,12 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b * min(K, 32) / pm * 1e3, 1)
 
     # ---- end to end through the Python entry point -------------------------------------------
-    plen = CTX - (K + W) - 2
+    # The prompts are prefilled in portions, so the first requests decode while the last ones are still in
+    # their prompts: every request gets room for those extra tokens, so that none ends inside the timed steps.
+    ahead = B * (-(-CTX // 2048)) + 8
+    plen = CTX - (K + W) - 2 - ahead
     for _ in range(B):
-        llm.add_request(rand_tokens(plen), SamplingParams(max_tokens=K + W + 1, ignore_eos=True))
+        llm.add_request(rand_tokens(plen), SamplingParams(max_tokens=K + W + 1 + ahead, ignore_eos=True))
     while any(not s.prefill_done for s in llm.get_running()) or llm.scheduler.waiting:
         llm.step()
     for _ in range(W):
@@ -250,6 +253,8 @@ def main() -> int:
         llm.step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    if len(llm.get_running()) != B:
+        raise RuntimeError("a request ended inside the timed end-to-end steps")
     e2e = {"value": round(B * K / e2e_s, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": runner.h2d_bytes_last_step,      # step inputs + attention work list
            "d2h_bytes_per_step": 4 * B + 4}                        # sampled ids + status word
