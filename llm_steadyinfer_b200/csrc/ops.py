@@ -426,6 +426,19 @@ def gemm_skinny_swiglu(a, w, out) -> None:
 _weight_maps = {}
 
 
+_tc05_available = None
+
+
+def gemm_tc05_available() -> bool:
+    """True when the driver hands out the tensor-map encoder that the TMA-fed kernels need."""
+    global _tc05_available
+    if _tc05_available is None:
+        lib = build.load("gemm_tc05")
+        lib.si_gemm_tc05_ok.restype = _c_int
+        _tc05_available = bool(lib.si_gemm_tc05_ok())
+    return _tc05_available
+
+
 def gemm_tc05_ok(a, w, out) -> bool:
     """True when the tcgen05 kernel takes these tensors (bf16, K a multiple of 8, aligned rows)."""
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
@@ -459,6 +472,20 @@ def gemm_tc05(a, w, out, status=None) -> None:
             [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(a), a.stride(0), _weight_map(w), _ptr(out), out.stride(0), _dt(out), M, N, K, _ptr(status),
              _stream()), f"gemm_tc05(M={M}, N={N}, K={K})")
+
+
+def gemm_tc05_swiglu(a, w, out, status=None) -> None:
+    """out[M,F] = silu(gate) * up of a[M,K] @ w[2F,K]^T on the tcgen05 tensor cores, the rows of w interleaved
+    in groups of 8 (8 gates, their 8 ups, ...): the activation runs in the product's epilogue."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    F = out.shape[1]
+    _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
+          "gemm_tc05_swiglu: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
+    _need(gemm_tc05_ok(a, w, out), "gemm_tc05_swiglu: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_tc05", "si_gemm_tc05_swiglu", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), _ptr(out), out.stride(0), M, F, K, _ptr(status), _stream()),
+           f"gemm_tc05_swiglu(M={M}, F={F}, K={K})")
 
 
 # ---- prompt-portion attention on tcgen05 ---------------------------------------------------------

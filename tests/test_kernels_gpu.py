@@ -548,6 +548,27 @@ def test_gemm_tc05(M, N, K, out_dtype):
     assert (out.double() - want).abs().max().item() <= tol
 
 
+@pytest.mark.parametrize("M,F,K", [(128, 128, 64), (200, 1336, 320), (2048, 512, 4096), (77, 40, 72)])
+def test_gemm_tc05_swiglu(M, F, K):
+    """The many-row gate/up product with the activation in its epilogue equals the product stored in bf16
+    followed by the activation kernel."""
+    g = torch.Generator().manual_seed(24)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * F, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops().gemm_tc05_swiglu(a, w, out, status)
+    gu = torch.empty(M, 2 * F, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_tc05(a, w, gu, status)
+    two = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    ops().swiglu(gu, two, 8)
+    assert status.item() == 0
+    assert torch.equal(out, two)
+    ref = (a.double() @ w.double().T).view(M, F // 8, 2, 8)
+    want = plain_llama.swiglu(ref[:, :, 0].reshape(M, F).cpu(), ref[:, :, 1].reshape(M, F).cpu())
+    assert (out.double().cpu() - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
+
+
 def test_gemm_tc05_at_prefill_size():
     """The projections of the Llama-3.1-8B block at 2,048 rows: achieved TFLOP/s (printed) beside the library."""
     g = torch.Generator(device=DEV).manual_seed(15)
