@@ -19,6 +19,13 @@
 #include "attention_common.cuh"
 #include "tma_common.cuh"
 
+// 2^x in fp32 by the hardware approximation (2 ulp); exp2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Tile of NROWS rows stored as 64-column halves; inside a half, row r holds its eight 16-byte
 // chunks at positions chunk ^ (r % 8): the layout the 128-byte TMA swizzle writes.
 template <int NROWS>
@@ -96,15 +103,21 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     // ---- producer warp: lane l fetches box (page l / (2 NH), half (l / 2) % NH, K or V) of each tile
     const int boxes = pages_per_tile * NH * 2;
     const int pg = lane / (2 * NH), h = (lane >> 1) % NH, is_v = lane & 1;
+    // The page numbers are read three tiles ahead: a lookup in the loop would put the latency of a load
+    // from global memory into every tile's turn.
+    constexpr int NOT_NEEDED = -2;
+    auto lookup = [&](int t) {
+      const int j = kv_begin + t * BLOCK_N;
+      if (t >= ntiles || lane >= boxes || j + pg * page_rows >= kv_end) return NOT_NEEDED;   // pages past the last key are not fetched
+      const int slot = (j >> log2_page) + pg;
+      return slot < p.table_width ? __ldg(table + slot) : -1;
+    };
+    int ahead0 = lookup(0), ahead1 = lookup(1), ahead2 = lookup(2);
     for (int t = 0; t < ntiles; ++t) {
       const int stage = t % STAGES;
-      const int j = kv_begin + t * BLOCK_N;
-      int page = -1;
-      if (lane < boxes && j + pg * page_rows < kv_end) {       // pages past the last key are not fetched
-        const int slot = (j >> log2_page) + pg;
-        page = slot < p.table_width ? table[slot] : -1;
-        if (page < 0 || page >= p.num_pages) { set_status(p.status, SI_BAD_PAGE); page = -1; }
-      }
+      int page = ahead0;
+      ahead0 = ahead1; ahead1 = ahead2; ahead2 = lookup(t + 3);
+      if (page != NOT_NEEDED && (page < 0 || page >= p.num_pages)) { set_status(p.status, SI_BAD_PAGE); page = -1; }
       const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
       bool ok = true;
       if (t >= STAGES) ok = mbar_wait(&empty_bar[stage], (unsigned)(((t / STAGES) - 1) & 1));
@@ -140,6 +153,23 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
       pos_of[mt][h2] = tok < item.ntok ? item.pos0 + tok : -1;
     }
 
+  // The query fragments do not change from tile to tile: they are read from shared memory once.
+  unsigned qf[MT][KT][4];
+  int pos_min = 0x7fffffff, pos_max = -1;            // over the rows of this lane's fragments
+  if (warp < NWARPS) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int kk = 0; kk < KT; ++kk)
+        ldsm_x4(qf[mt][kk][0], qf[mt][kk][1], qf[mt][kk][2], qf[mt][kk][3],
+                half_tile_ptr<ROWS>(Qs, mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2)
+        if (pos_of[mt][h2] >= 0) { pos_min = min(pos_min, pos_of[mt][h2]); pos_max = max(pos_max, pos_of[mt][h2]); }   // rows without a token decide nothing
+  }
+
   for (int t = 0; warp < NWARPS && t < ntiles; ++t) {
     const int j0 = kv_begin + t * BLOCK_N;
     const int stage = t % STAGES;
@@ -152,6 +182,8 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     }
     const int jw = j0 + warp * 16;          // this warp's 16 keys
     if (jw < kv_end) {
+      // most tiles lie wholly inside every row's visible range: then nothing is masked
+      const bool masked = __any_sync(0xffffffffu, jw + 15 > pos_min || (p.window > 0 && jw <= pos_max - p.window));
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         float s[2][4];
@@ -159,23 +191,29 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
         s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < KT; ++kk) {
-          unsigned a0, a1, a2, a3, b0, b1, b2, b3;
-          ldsm_x4(a0, a1, a2, a3, half_tile_ptr<ROWS>(Qs, mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+          unsigned b0, b1, b2, b3;
           ldsm_x4(b0, b1, b2, b3, half_tile_ptr<BLOCK_N>(Kt, warp * 16 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
-          mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
-          mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+          mma_bf16(s[0], qf[mt][kk][0], qf[mt][kk][1], qf[mt][kk][2], qf[mt][kk][3], b0, b1);
+          mma_bf16(s[1], qf[mt][kk][0], qf[mt][kk][1], qf[mt][kk][2], qf[mt][kk][3], b2, b3);
         }
         float mx[2] = {m[mt][0], m[mt][1]};
+        if (masked) {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = jw + nt * 8 + (lane & 3) * 2 + (e & 1);
+              const int pos = pos_of[mt][e >> 1];
+              const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
+              if (!vis) s[nt][e] = -INFINITY;
+            }
+        }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int j = jw + nt * 8 + (lane & 3) * 2 + (e & 1);
-            const int pos = pos_of[mt][e >> 1];
-            const bool vis = j <= pos && (p.window <= 0 || j > pos - p.window);
-            const float v = vis ? s[nt][e] * p.scale_log2 : -INFINITY;
-            s[nt][e] = v;
-            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            s[nt][e] *= p.scale_log2;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
           }
         float corr[2], base[2];
 #pragma unroll
@@ -183,7 +221,7 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
           mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
           mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
           base[h2] = mx[h2] == -INFINITY ? 0.f : mx[h2];
-          corr[h2] = exp2f(m[mt][h2] - base[h2]);
+          corr[h2] = fast_exp2(m[mt][h2] - base[h2]);
           m[mt][h2] = mx[h2];
         }
         float sum[2] = {0.f, 0.f};
@@ -191,17 +229,21 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            s[nt][e] = exp2f(s[nt][e] - base[e >> 1]);
+            s[nt][e] = fast_exp2(s[nt][e] - base[e >> 1]);
             sum[e >> 1] += s[nt][e];
           }
         l[mt][0] = l[mt][0] * corr[0] + sum[0];
         l[mt][1] = l[mt][1] * corr[1] + sum[1];
         const unsigned a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
         const unsigned a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
+        {
+#pragma unroll
+          for (int dt = 0; dt < DT; ++dt) {
+            o[mt][dt][0] *= corr[0]; o[mt][dt][1] *= corr[0]; o[mt][dt][2] *= corr[1]; o[mt][dt][3] *= corr[1];
+          }
+        }
 #pragma unroll
         for (int dt = 0; dt < DT; dt += 2) {
-          o[mt][dt][0] *= corr[0]; o[mt][dt][1] *= corr[0]; o[mt][dt][2] *= corr[1]; o[mt][dt][3] *= corr[1];
-          o[mt][dt + 1][0] *= corr[0]; o[mt][dt + 1][1] *= corr[0]; o[mt][dt + 1][2] *= corr[1]; o[mt][dt + 1][3] *= corr[1];
           unsigned b0, b1, b2, b3;
           ldsm_x4_t(b0, b1, b2, b3, half_tile_ptr<BLOCK_N>(Vt, warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dt + (lane >> 4)));
           mma_bf16(o[mt][dt], a0, a1, a2, a3, b0, b1);
