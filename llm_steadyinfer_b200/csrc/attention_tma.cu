@@ -317,18 +317,54 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   if (!s_last) return;
   __threadfence();
+  // The merge reads nsplit partial results per output. Loads that follow one another in a loop would each
+  // cost a trip to L2, so (1) the maxima and sums of all splits come into shared memory in one pass,
+  // (2) one thread per row turns them into the weights of the splits and the row's sum, and (3) the
+  // outputs are summed over the splits eight loads at a time. (The warps' merge buffers are free by now.)
+  float* w_s = reinterpret_cast<float*>(smem_raw);              // [rows_used][nsplit] maxima, then weights
+  float* l_s = w_s + rows_used * p.nsplit;                        // [rows_used][nsplit] sums
+  float* L_s = l_s + rows_used * p.nsplit;                        // [rows_used]
+  for (int i = threadIdx.x; i < rows_used * p.nsplit; i += THREADS) {
+    const int r = i / p.nsplit, sp = i - r * p.nsplit;
+    const size_t slab = slab0 + (size_t)sp * ROWS + r;
+    w_s[i] = __ldcg(p.part_ml + slab * 2);
+    l_s[i] = __ldcg(p.part_ml + slab * 2 + 1);
+  }
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
+  for (int r = threadIdx.x; r < rows_used; r += THREADS) {
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.nsplit; ++sp) M = fmaxf(M, w_s[r * p.nsplit + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < p.nsplit; ++sp) {
+      const float ms = w_s[r * p.nsplit + sp];
+      const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      L += l_s[r * p.nsplit + sp] * wgt;
+      w_s[r * p.nsplit + sp] = wgt;
+    }
+    L_s[r] = L;
+  }
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
     const int r = idx / p.hs, d = idx - r * p.hs;
-    float M = -INFINITY;
-    for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slab0 + (size_t)s * ROWS + r) * 2));
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < p.nsplit; ++s) {
-      const size_t slab = slab0 + (size_t)s * ROWS + r;
-      const float ms = __ldcg(p.part_ml + slab * 2);
-      const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += __ldcg(p.part_ml + slab * 2 + 1) * wgt;
-      acc += __ldcg(p.part_o + slab * p.hs + d) * wgt;
+    const float* src = p.part_o + (slab0 + r) * p.hs + d;       // split sp lies sp * ROWS * hs further
+    const size_t step = (size_t)ROWS * p.hs;
+    float acc = 0.f;
+    int sp = 0;
+    for (; sp + 8 <= p.nsplit; sp += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + (size_t)(sp + u) * step);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc += v[u] * w_s[r * p.nsplit + sp + u];    // in the order of the splits
     }
+    {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = sp + u < p.nsplit ? __ldcg(src + (size_t)(sp + u) * step) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) if (sp + u < p.nsplit) acc += v[u] * w_s[r * p.nsplit + sp + u];
+    }
+    const float L = L_s[r];
     const int tok = r / p.G, hh = r - tok * p.G;
     p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
         __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
@@ -393,7 +429,7 @@ SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* 
                                  int nsplit, float* scratch, int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_decode_tma_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
-  if ((q_stride % 8) || nsplit < 1 || nsplit > 65535) return -2;
+  if ((q_stride % 8) || nsplit < 1 || nsplit > 128) return -2;     // the merge stages 2 * rows * nsplit floats in shared memory
   AttnParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
