@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 # rounded to 8 bits of mantissa at each stored tensor; the plain implementation with the same
 # roundings differs from the exact one by 3e-3 on these models.
 ATOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2}
-LENGTHS = {"A": [1, 7, 33, 64, 150], "B": [3, 17, 50, 100, 129, 200]}
+LENGTHS = {"A": [1, 7, 33, 64, 150], "B": [3, 17, 50, 100, 129, 200], "C": [2, 40, 129, 200, 330]}
 
 
 @pytest.fixture(scope="module")
@@ -44,7 +44,7 @@ def replayer(folder, name, dtype, max_tokens):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_replay_modes(folders, plains, name, dtype, mode):
     reqs = requests_of(name)

@@ -1,4 +1,5 @@
-"""Two tiny Llama 3 configurations that differ in every size and option, and helpers that
+"""Tiny Llama 3 configurations that differ in every size and option (A and B; C sits at the layout
+that the TMA and tcgen05 kernels take), and helpers that
 write them as model folders with random weights into a temporary folder."""
 import os
 
@@ -27,7 +28,21 @@ TINY_B = {
     "tie_word_embeddings": False, "hidden_act": "silu", "attention_bias": False,
     "mlp_bias": False, "torch_dtype": "bfloat16", "bos_token_id": 0, "eos_token_id": [7, 9],
 }
-CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8)}     # config, seed, cache page size
+# head size 64 with grouped heads, pages of 16, an intermediate size that is a multiple of 8: the layout at
+# which the TMA and tcgen05 kernels (decode attention, prompt attention, the gate/up product with the
+# activation in its epilogue) take over from the general ones in bfloat16
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 256, "intermediate_size": 520, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "vocab_size": 777, "max_position_embeddings": 1024, "rms_norm_eps": 2e-6,
+    "rope_theta": 100000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "tie_word_embeddings": False, "hidden_act": "silu", "attention_bias": False,
+    "mlp_bias": False, "torch_dtype": "bfloat16", "bos_token_id": 0, "eos_token_id": 5,
+}
+CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}     # config, seed, cache page size
 
 
 def make_model_folder(tmp_path, name: str) -> str:
