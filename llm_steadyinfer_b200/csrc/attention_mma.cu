@@ -432,8 +432,10 @@ attn_decode_kernel(const AttnParams p) {
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
     const int r = idx / p.hs, d = idx - r * p.hs;
     float M = -INFINITY;
+#pragma unroll 8                   // several loads in flight, not one trip to L2 after the other
     for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, __ldcg(p.part_ml + (slab0 + (size_t)s * ROWS + r) * 2));
     float L = 0.f, acc = 0.f;
+#pragma unroll 4
     for (int s = 0; s < p.nsplit; ++s) {
       const size_t slab = slab0 + (size_t)s * ROWS + r;
       const float ms = __ldcg(p.part_ml + slab * 2);

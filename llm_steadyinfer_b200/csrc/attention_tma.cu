@@ -33,7 +33,21 @@ __device__ __forceinline__ bf16* half_tile_ptr(bf16* base, int row, int chunk) {
   return base + (size_t)(chunk >> 3) * (NROWS * 64) + (size_t)row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
-template <int NH, int MT, int STAGES>
+// m8n8 transpose of 16-bit elements across the warp: lane (g, t) gives row g, columns 2t and 2t+1 and gets
+// row g, columns 2t and 2t+1 of the transposed matrix.
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
+  unsigned r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+  return r;
+}
+
+// SWAP (items of at most 8 rows, the usual decode step): the products are taken the other way round,
+// S^T = K Q^T and O^T = V^T P^T, so that the 16 rows of the tensor-core instruction are keys (or
+// head-dim elements) and its 8 columns the query rows. With the rows as the 16 of the instruction
+// three quarters of every product and of the softmax arithmetic are spent on rows that do not exist;
+// this way a tile costs half the instructions, and the consumer warps, one per scheduler, are bound
+// by their instruction stream.
+template <int NH, int MT, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(160)
 attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
                        const __grid_constant__ CUtensorMap vmap, int log2_page) {
@@ -156,7 +170,24 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   // The query fragments do not change from tile to tile: they are read from shared memory once.
   unsigned qf[MT][KT][4];
   int pos_min = 0x7fffffff, pos_max = -1;            // over the rows of this lane's fragments
-  if (warp < NWARPS) {
+  if constexpr (SWAP) {
+    // lane (g, t): B fragment of Q^T, row g, head-dim elements 16kk + 2t, +1 and 16kk + 8 + 2t, +1;
+    // the lane's elements of S^T belong to rows 2t and 2t + 1
+    static_assert(!SWAP || MT == 1, "the swapped products take one 8-row tile");
+    if (warp < NWARPS) {
+#pragma unroll
+      for (int kk = 0; kk < KT; ++kk) {
+        qf[0][kk][0] = *reinterpret_cast<const unsigned*>(half_tile_ptr<ROWS>(Qs, lane >> 2, kk * 2) + 2 * (lane & 3));
+        qf[0][kk][1] = *reinterpret_cast<const unsigned*>(half_tile_ptr<ROWS>(Qs, lane >> 2, kk * 2 + 1) + 2 * (lane & 3));
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int tok = (2 * (lane & 3) + i) / p.G;
+        pos_of[0][i] = tok < item.ntok ? item.pos0 + tok : -1;
+        if (pos_of[0][i] >= 0) { pos_min = min(pos_min, pos_of[0][i]); pos_max = max(pos_max, pos_of[0][i]); }
+      }
+    }
+  } else if (warp < NWARPS) {
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -184,6 +215,51 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     if (jw < kv_end) {
       // most tiles lie wholly inside every row's visible range: then nothing is masked
       const bool masked = __any_sync(0xffffffffu, jw + 15 > pos_min || (p.window > 0 && jw <= pos_max - p.window));
+      if constexpr (SWAP) {
+        // S^T[16 keys, 8 rows]: the lane holds keys g, g + 8 (elements 0-1, 2-3) of rows 2t, 2t + 1
+        float st[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int kk = 0; kk < KT; ++kk) {
+          unsigned a0, a1, a2, a3;
+          ldsm_x4(a0, a1, a2, a3, half_tile_ptr<BLOCK_N>(Kt, warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+          mma_bf16(st, a0, a1, a2, a3, qf[0][kk][0], qf[0][kk][1]);
+        }
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = jw + (lane >> 2) + 8 * (e >> 1);
+            const int pos = pos_of[0][e & 1];
+            if (!(j <= pos && (p.window <= 0 || j > pos - p.window))) st[e] = -INFINITY;
+          }
+        }
+        float mx[2] = {m[0][0], m[0][1]}, corr[2], base[2];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { st[e] *= p.scale_log2; mx[e & 1] = fmaxf(mx[e & 1], st[e]); }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {                 // over the eight lanes that hold the other keys of the row
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
+          base[i] = mx[i] == -INFINITY ? 0.f : mx[i];
+          corr[i] = fast_exp2(m[0][i] - base[i]);
+          m[0][i] = mx[i];
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { st[e] = fast_exp2(st[e] - base[e & 1]); sum[e & 1] += st[e]; }
+        l[0][0] = l[0][0] * corr[0] + sum[0];          // this lane's keys only; the lanes are added at the end
+        l[0][1] = l[0][1] * corr[1] + sum[1];
+        // P^T as the B operand: transposing the 8x8 blocks turns (key g, rows 2t, 2t+1) into (row g, keys 2t, 2t+1)
+        const unsigned b0 = movmatrix_trans(pack_bf16(st[0], st[1])), b1 = movmatrix_trans(pack_bf16(st[2], st[3]));
+        // O^T[head dim, 8 rows] += V^T[head dim, 16 keys] P^T[16 keys, 8 rows], 16 head-dim elements a step
+#pragma unroll
+        for (int dm = 0; dm < HS_PAD / 16; ++dm) {
+          o[0][dm][0] *= corr[0]; o[0][dm][1] *= corr[1]; o[0][dm][2] *= corr[0]; o[0][dm][3] *= corr[1];
+          unsigned a0, a1, a2, a3;
+          ldsm_x4_t(a0, a1, a2, a3, half_tile_ptr<BLOCK_N>(Vt, warp * 16 + (lane & 7) + 8 * (lane >> 4), dm * 2 + ((lane >> 3) & 1)));
+          mma_bf16(o[0][dm], a0, a1, a2, a3, b0, b1);
+        }
+      } else
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         float s[2][4];
@@ -263,6 +339,23 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   float* fl = fm + NWARPS * ROWS;
   float* fo = fl + NWARPS * ROWS;
   constexpr int OS = HS_PAD + 4;
+  if constexpr (SWAP) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float lv = l[0][i];
+      lv += __shfl_xor_sync(0xffffffffu, lv, 4);
+      lv += __shfl_xor_sync(0xffffffffu, lv, 8);
+      lv += __shfl_xor_sync(0xffffffffu, lv, 16);
+      const int r = 2 * (lane & 3) + i;
+      if ((lane >> 2) == 0) { fm[warp * ROWS + r] = m[0][i]; fl[warp * ROWS + r] = lv; }
+#pragma unroll
+      for (int dm = 0; dm < HS_PAD / 16; ++dm) {
+        const int d = dm * 16 + (lane >> 2);
+        fo[((size_t)warp * ROWS + r) * OS + d] = o[0][dm][i];
+        fo[((size_t)warp * ROWS + r) * OS + d + 8] = o[0][dm][2 + i];
+      }
+    }
+  } else
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -404,7 +497,7 @@ SI_EXPORT long long si_attn_decode_tma_scratch_floats(int num_items, int H, int 
   return (long long)num_items * KV * nsplit * rows * (hs + 2) + (long long)num_items * KV;
 }
 
-template <int NH, int MT>
+template <int NH, int MT, bool SWAP = false>
 static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap& vm, int num_items, int log2_page,
                   cudaStream_t stream) {
   constexpr int STAGES = 3, ROWS = 16 * MT, HS_PAD = NH * 64;
@@ -412,7 +505,7 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
   const size_t merge = (size_t)4 * ROWS * (2 + HS_PAD + 4) * sizeof(float);
   if (merge > smem) smem = merge;
   smem += 1024;                                   // room to align the tiles to 1024 bytes
-  auto k = attn_decode_tma_kernel<NH, MT, STAGES>;
+  auto k = attn_decode_tma_kernel<NH, MT, STAGES, SWAP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -421,12 +514,14 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
   return si_last_error();
 }
 
-// Same contract as si_attn_decode, with the tensor maps of this layer's K and V cache.
+// Same contract as si_attn_decode, with the tensor maps of this layer's K and V cache. `max_rows`: the most
+// rows (tokens x query heads of a KV head) that any item has, when the caller knows it, else 0; items of at
+// most 8 rows take the kernel with the swapped products.
 SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                  const void* kmap, const void* vmap, const int* block_table, int table_width,
                                  const void* items, int num_items, void* out, long long out_stride, int num_pages,
                                  int page_size, int num_seqs, int H, int KV, int hs, float scale, int window,
-                                 int nsplit, float* scratch, int* status, cudaStream_t stream) {
+                                 int nsplit, float* scratch, int max_rows, int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_decode_tma_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
   if ((q_stride % 8) || nsplit < 1 || nsplit > 128) return -2;     // the merge stages 2 * rows * nsplit floats in shared memory
@@ -452,6 +547,9 @@ SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* 
   while ((1 << log2_page) < page_size) ++log2_page;
   const CUtensorMap& km = *(const CUtensorMap*)kmap;
   const CUtensorMap& vm = *(const CUtensorMap*)vmap;
+  if (rows == 16 && max_rows >= 1 && max_rows <= 8)
+    return hs == 64 ? launch<1, 1, true>(p, km, vm, num_items, log2_page, stream)
+                    : launch<2, 1, true>(p, km, vm, num_items, log2_page, stream);
   if (hs == 64) return rows == 16 ? launch<1, 1>(p, km, vm, num_items, log2_page, stream)
                                   : launch<1, 2>(p, km, vm, num_items, log2_page, stream);
   return rows == 16 ? launch<2, 1>(p, km, vm, num_items, log2_page, stream)

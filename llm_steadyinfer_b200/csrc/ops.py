@@ -362,9 +362,12 @@ def _cache_map(cache: torch.Tensor):
 
 
 def attn_decode_tma(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int,
-                    hs: int, scale: float, window: int = 0, nsplit: int = 1, scratch=None, status=None) -> None:
+                    hs: int, scale: float, window: int = 0, nsplit: int = 1, scratch=None, status=None,
+                    max_rows: int = 0) -> None:
     """``attn_decode`` with the K/V tiles fetched by TMA (head_dim 64 or 128, page sizes 8 to 64);
-    items hold at most ``attn_decode_tma_rows // (H // KV)`` tokens."""
+    items hold at most ``attn_decode_tma_rows // (H // KV)`` tokens. ``max_rows``: the most rows
+    (tokens x query heads of a KV head) of any item when the caller knows it (0: unknown); at most 8
+    rows run the variant with the products taken the other way round."""
     _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_decode_tma")
     if nsplit > 1:
         _cuda(scratch)
@@ -373,11 +376,11 @@ def attn_decode_tma(q, k_cache, v_cache, block_table, items, out, page_size: int
               f"attn_decode_tma: scratch must hold {need} floats")
     f = _fn("attention_tma", "si_attn_decode_tma",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_int, _c_p, _c_p])
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _cache_map(k_cache), _cache_map(v_cache),
              _ptr(block_table), block_table.shape[1], _ptr(items), items.shape[0], _ptr(out), out.stride(0),
              k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), int(nsplit),
-             _ptr(scratch), _ptr(status), _stream()),
+             _ptr(scratch), int(max_rows), _ptr(status), _stream()),
            f"attn_decode_tma(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")
 
 

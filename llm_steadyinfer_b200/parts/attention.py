@@ -108,6 +108,7 @@ class Attention(Mixer):
                 for b in range(0, n, por_tokens):
                     por.append((s, row0 + b, min(por_tokens, n - b), pos0 + b))
         plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma,
+                "dec_rows": max((d[2] for d in dec), default=0) * G,
                 "tc05": tc05}
         n_dec = len(dec)
         if ctx.seq_cap is not None:                   # fixed shapes: pad with empty items
@@ -139,9 +140,12 @@ class Attention(Mixer):
         plan = ctx.plans[("attention", self.H, self.KV, self.hs)]
         args = (cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs, self.scale, self.window or 0)
         if plan["dec"] is not None:
-            decode = ops.attn_decode_tma if plan["tma"] else ops.attn_decode
-            decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,
-                            nsplit=plan["nsplit"], scratch=plan["scratch"], status=ctx.status)
+            if plan["tma"]:
+                ops.attn_decode_tma(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args, nsplit=plan["nsplit"],
+                                    scratch=plan["scratch"], status=ctx.status, max_rows=plan["dec_rows"])
+            else:
+                ops.attn_decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,
+                                nsplit=plan["nsplit"], scratch=plan["scratch"], status=ctx.status)
         if plan["por"] is not None:
             portion = ops.attn_portion_tc05 if plan["tc05"] else ops.attn_portion
             portion(q, cache.k, cache.v, cache.block_table, plan["por"], out, *args, status=ctx.status)

@@ -324,9 +324,10 @@ def _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size,
         floats = o.attn_decode_tma_scratch_floats if tma else o.attn_decode_scratch_floats
         if nsplit > 1:
             scratch = torch.zeros(floats(len(dec), H, KV, hs, nsplit), device=DEV)
+        more = {"max_rows": max(d[2] for d in dec) * G} if tma else {}      # few rows: the swapped products
         (o.attn_decode_tma if tma else o.attn_decode)(
             q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, window or 0,
-            nsplit=nsplit, scratch=scratch, status=status)
+            nsplit=nsplit, scratch=scratch, status=status, **more)
     if por:
         items = torch.tensor(por, dtype=torch.int32, device=DEV)
         (o.attn_portion_tc05 if tc05 else o.attn_portion)(
@@ -456,8 +457,9 @@ def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
     floats = o.attn_decode_tma_scratch_floats if tma else o.attn_decode_scratch_floats
     scratch = torch.zeros(max(1, floats(batch, H, KV, hs, nsplit)), device=DEV)
     decode = o.attn_decode_tma if tma else o.attn_decode
+    more = {"max_rows": H // KV} if tma else {}
     run = lambda: decode(q, kc, vc, table, items, out, page_size, batch, H, KV, hs, scale, 0,
-                         nsplit=nsplit, scratch=scratch if nsplit > 1 else None, status=status)
+                         nsplit=nsplit, scratch=scratch if nsplit > 1 else None, status=status, **more)
     run()
     assert status.item() == 0
     assert (out.float() - want.float()).abs().max().item() <= 2 ** -8 * 4       # outputs of size up to ~4 in bf16
