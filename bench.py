@@ -175,12 +175,22 @@ def main() -> int:
             prefill_once(i)
         runner.check_status()
         pre_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
+        # the same step with every many-row product on this package's tcgen05 kernel (none in the library)
+        from llm_steadyinfer_b200.parts import linear as linear_mod
+        was = linear_mod.USE_OWN_GEMM
+        linear_mod.USE_OWN_GEMM = True
+        for i in range(2):
+            prefill_once(i)
+        runner.check_status()
+        own_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
+        linear_mod.USE_OWN_GEMM = was
     if args.section == "prefill":
-        print(json.dumps({"section": "prefill", "tokens": PT, "ms": round(pre_ms, 3)}))
+        print(json.dumps({"section": "prefill", "tokens": PT, "ms": round(pre_ms, 3), "own_gemm_ms": round(own_ms, 3)}))
         return 0
     pre_flops = 2 * PT * block_params + L * 4 * H * hs * PT * (PT + 1) / 2 + 2 * V * d
     prefill = {"value": round(PT / pre_ms * 1e3, 1), "tokens": PT, "ms": round(pre_ms, 3),
-               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "own_gemm_ms": round(own_ms, 3)}          # with no product in the library (SI_OWN_GEMM=1)
 
     # ---- decode on the device: contexts filled synthetically, fixed next tokens ----------------
     for t in runner.storage.keys + runner.storage.values:

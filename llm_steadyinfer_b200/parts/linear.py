@@ -4,9 +4,12 @@ fp32 tensors go through this package's own FFMA kernel (true 32-bit, no reduced-
 mode). bf16 products of at most 16 rows (decode) go through the package's weight-streaming
 kernel (``gemm_skinny.cu``). Other bf16 products go to the cuBLAS GEMM behind ``torch.mm`` with
 fp32 accumulation, as the reference sends every projection and the LM head to ``cublasGemmEx``
-(src/source/op/kernels/cuda/matmul_kernel.cu:128-150).
+(src/source/op/kernels/cuda/matmul_kernel.cu:128-150), or, with ``USE_OWN_GEMM``, to the package's
+tcgen05 kernel (``gemm_tc05.cu``).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -14,6 +17,12 @@ from ..csrc import ops
 
 
 USE_SKINNY = True      # few-row products (decode) through this package's weight-streaming kernel
+# Many-row bf16 products (at least OWN_GEMM_MIN_ROWS rows) through this package's tcgen05 kernel instead of
+# the library. Off by default: on the plain projections the library's 2-CTA kernels are 8 to 19 % faster
+# (the gate/up projection, where the fused activation makes up for it, does not come through here).
+# SI_OWN_GEMM=1 in the environment turns it on.
+USE_OWN_GEMM = os.environ.get("SI_OWN_GEMM", "0") == "1"
+OWN_GEMM_MIN_ROWS = 128
 
 
 def configure_library_gemm() -> None:
@@ -29,6 +38,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         ops.gemm_f32(x, w, out)
     elif USE_SKINNY and ops.gemm_skinny_ok(x, w, out):
         ops.gemm_skinny(x, w, out)
+    elif (USE_OWN_GEMM and x.shape[0] >= OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available()
+          and ops.gemm_tc05_ok(x, w, out)):
+        ops.gemm_tc05(x, w, out)
     elif x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

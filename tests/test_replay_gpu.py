@@ -66,6 +66,47 @@ def test_replay_modes(folders, plains, name, dtype, mode):
     print(f"{name} {mode} {dtype}: worst difference {worst:.2e}")
 
 
+# One block of the Llama-3.1-8B shape (widths, head layout, frequency scaling) with a small vocabulary: the sizes
+# at which serving runs its kernels (TMA and tcgen05 attention, the few-row and the tcgen05 matrix products).
+LAYER_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 1,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "vocab_size": 2000, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False, "hidden_act": "silu", "attention_bias": False,
+    "mlp_bias": False, "torch_dtype": "bfloat16", "bos_token_id": 0, "eos_token_id": 1,
+}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_replay_at_8b_layer_shape(tmp_path_factory, dtype):
+    """Mixed replay (portions beside decoded tokens, pages used again) of one block at the Llama-3.1-8B shape.
+    Allowed difference: fp32 sums run over up to 14,336 terms here, so 5e-5; bf16 three times the error that
+    the plain implementation predicts when it rounds activations to bf16 where serving stores them."""
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    from llm_steadyinfer_b200.weights import write_random_model
+    import plain_llama
+    folder = str(tmp_path_factory.mktemp("layer8b") / "m")
+    write_random_model(folder, LAYER_8B, 5, torch.bfloat16)
+    plain = ru.PlainLogits(folder)
+    reqs = {f"q{i}": ru.random_tokens(LAYER_8B["vocab_size"], n, 900 + i) for i, n in enumerate([5, 70, 190])}
+    if dtype == torch.float32:
+        atol = 5e-5
+    else:
+        toks = reqs["q2"]
+        predicted = (plain_llama.forward(plain.cfg, plain.w, toks, round_to=torch.bfloat16) - plain.of(toks)).abs().max().item()
+        atol = 3 * predicted
+    max_tokens = 256 + 128
+    steps = ru.trace_mixed(reqs, max_tokens, seed=11)
+    rp = Replayer(folder, dtype, max_tokens, page_size=16)
+    worst = ru.compare(rp, steps, reqs, plain, atol, f"8B layer shape/{dtype}")
+    rp.runner.manager.check_invariant()
+    print(f"8B layer shape {dtype}: worst difference {worst:.2e} (allowed {atol:.2e})")
+
+
 def test_trace_run_program(folders, plains, tmp_path):
     """The program itself, as a user runs it: JSON lines in, .f32 files and 'done' lines out."""
     name = "B"
