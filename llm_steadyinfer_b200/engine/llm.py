@@ -43,13 +43,15 @@ class LLM:
     def __init__(self, model, dtype="bfloat16", max_batch: int = 32, max_seq_len: Optional[int] = None,
                  max_gen_len: int = 256, block_size: int = 16, num_blocks: Optional[int] = None,
                  max_num_batched_tokens: Union[int, str] = "adaptive", enable_prefix_cache: bool = True,
-                 use_cuda_graph: bool = True, device: str = "cuda:0"):
+                 use_cuda_graph: bool = True, async_decode: bool = True, device: str = "cuda:0"):
         """``model``: a model folder or a built ``Model``. ``max_batch``: most requests running at
         once. ``max_seq_len``: most tokens (prompt + generated) of one request, by default the
         model's ``max_position``. ``num_blocks``: pages of the cache pool, by default
         ``max_batch * ceil(max_seq_len / block_size)`` as in the reference
         (src/source/scheduler/kv_manager.cpp:23-25). ``max_num_batched_tokens``: prompt tokens per
-        step, or "adaptive" for the reference's 512/1024/4096 rule."""
+        step, or "adaptive" for the reference's 512/1024/4096 rule. ``async_decode``: while a
+        decode step runs, the next one is already decided and launched (its tokens pass from step
+        to step on the device), so the host's work per step hides behind the GPU's."""
         self.dtype = _dtype_of(dtype)
         self.model = load_model(model, self.dtype, device) if isinstance(model, (str, bytes)) else model
         spec = self.model.spec
@@ -68,8 +70,11 @@ class LLM:
                                    token_budget=max_num_batched_tokens, eos_token_ids=eos)
         self.sampler = Sampler(self.model.device, self.max_batch)
         self.use_cuda_graph = bool(use_cuda_graph)
+        self.async_decode = bool(async_decode)
+        self._inflight = None             # a launched step whose tokens have not been read: (items, wanted, handle)
         self._returned = 0
-        self.stats = {"steps": 0, "decode_steps": 0, "graph_steps": 0, "tokens_in": 0, "tokens_out": 0}
+        self.stats = {"steps": 0, "decode_steps": 0, "graph_steps": 0, "ahead_steps": 0, "tokens_in": 0,
+                      "tokens_out": 0}
 
     # ---- the reference's driver-facing calls ----------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -77,7 +82,7 @@ class LLM:
         return self.scheduler.add_request(prompt_token_ids, params, request_id)
 
     def all_finished(self) -> bool:
-        return not self.scheduler.has_unfinished()
+        return self._inflight is None and not self.scheduler.has_unfinished()
 
     def get_running(self) -> List[Sequence_]:
         return list(self.scheduler.running)
@@ -89,35 +94,64 @@ class LLM:
         return out
 
     def step(self) -> List[Sequence_]:
-        """One scheduler step: decide, run the model, sample, book the tokens."""
-        items = self.scheduler.schedule()
-        if not items:
-            return []
+        """One scheduler step: decide, run the model, sample, book the tokens. With ``async_decode`` a
+        decode step is launched one call before its tokens are booked: the call launches the step after
+        it as well, when that can be decided without the tokens (``Scheduler.schedule_ahead``), and only
+        then waits for the tokens of the earlier one."""
         try:
-            sampled = self._execute(items)
+            pending = self._inflight
+            self._inflight = None
+            if pending is None:
+                items = self.scheduler.schedule()
+                if not items:
+                    return []
+                pending = self._launch(items)
+            items, wanted, handle, graph_step = pending
+            if self.async_decode and graph_step:
+                ahead = self.scheduler.schedule_ahead(items)
+                if ahead is not None:
+                    rows = {id(it.seq): r for r, it in enumerate(wanted)}
+                    self._inflight = self._launch(ahead, feed_rows=[rows[id(it.seq)] for it in ahead])
+                    self.stats["ahead_steps"] += 1
+            sampled = self._resolve(wanted, handle)
         except Exception:
+            self._inflight = None
             self.scheduler.abort_all()
             raise
         self.stats["steps"] += 1
         return self.scheduler.update(items, sampled)
 
-    def _execute(self, items: List[ScheduledItem]) -> Dict[Hashable, int]:
-        entries = [StepEntry(it.seq.id, it.tokens, [it.count - 1] if it.want_logits else []) for it in items]
+    def _launch(self, items: List[ScheduledItem], feed_rows: Optional[List[int]] = None):
+        """Queue one step on the GPU (model, sampling, copy of the ids to the host) without waiting for it.
+        ``feed_rows``: the step's tokens are the ids that the step before it sampled (row numbers among its
+        wanted rows), still on the device."""
+        ahead = feed_rows is not None
+        entries = [StepEntry(it.seq.id, [0] if ahead else it.tokens, [it.count - 1] if it.want_logits else [])
+                   for it in items]
         pure_decode = all(it.count == 1 and it.want_logits for it in items)
         if pure_decode:
             self.stats["decode_steps"] += 1
-        if pure_decode and self.use_cuda_graph and self.runner.graphs_available():
-            logits = self.runner.step_decode_graph(entries)
+        graph_step = pure_decode and self.use_cuda_graph and self.runner.graphs_available()
+        if graph_step:
+            feed = (self.sampler.last_ids(), feed_rows) if ahead else None
+            logits = self.runner.step_decode_graph(entries, feed=feed)
             self.stats["graph_steps"] += 1
         else:
             logits = self.runner.step(entries)
         self.stats["tokens_in"] += sum(it.count for it in items)
         wanted = [it for it in items if it.want_logits]
         if not wanted:
+            return items, wanted, None, False
+        # the index of the output token keys the draw; a step launched ahead draws the one after the unread token
+        rows = [(it.seq.params, it.seq.seed, len(it.seq.outputs) + (1 if ahead else 0)) for it in wanted]
+        handle = self.sampler.fetch(self.sampler.sample(logits, rows), status=self.runner.status)
+        return items, wanted, handle, graph_step
+
+    def _resolve(self, wanted: List[ScheduledItem], handle) -> Dict[Hashable, int]:
+        if handle is None:
             self.runner.check_status()
             return {}
-        rows = [(it.seq.params, it.seq.seed, len(it.seq.outputs)) for it in wanted]
-        tokens, code = self.sampler.to_host(self.sampler.sample(logits, rows), status=self.runner.status)
+        tokens, code = self.sampler.wait(handle)
         self.runner.raise_status(code)
         self.stats["tokens_out"] += len(tokens)
         return {it.seq.id: t for it, t in zip(wanted, tokens)}

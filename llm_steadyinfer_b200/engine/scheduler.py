@@ -181,6 +181,32 @@ class Scheduler:
                 taken += take
         return items
 
+    def schedule_ahead(self, inflight: Sequence[ScheduledItem]) -> Optional[List[ScheduledItem]]:
+        """The decode step that follows ``inflight`` (a step of decode rows only, launched but not read
+        yet), decided before its tokens are known: every request of it that will not have reached its
+        length takes one more token. None when that cannot be decided blind: a request waits for
+        admission, a row is no decode row, or a page is missing (making room is left to ``schedule``,
+        after the tokens have arrived). A request that the unread token ends (end of sequence) gets a row
+        too; ``update`` drops it."""
+        if self.waiting:
+            return None
+        items: List[ScheduledItem] = []
+        for it in inflight:
+            seq = it.seq
+            if it.count != 1 or not it.want_logits or seq.state is not SeqState.RUNNING:
+                return None
+            if len(seq.outputs) + 1 >= seq.max_gen:
+                continue                                  # ends by length with the unread token
+            if not self.cache.can_grow(seq.id, it.start + 2):
+                return None
+            items.append(ScheduledItem(seq, it.start + 1, 1, True))
+        if not items:
+            return None
+        for it in items:
+            self.cache.grow(it.seq.id, it.start + 1)
+        self.num_steps += 1
+        return items
+
     def _move_budget(self, decode_backlog: int) -> None:
         if not self.adaptive:
             return

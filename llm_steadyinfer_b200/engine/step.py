@@ -16,6 +16,8 @@ once, and later steps only refresh the integer inputs and the parts' work lists 
 """
 from __future__ import annotations
 
+import gc
+
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -201,10 +203,11 @@ class ModelRunner:
     def graphs_available(self) -> bool:
         return True
 
-    def step_decode_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step_decode_graph(self, entries: Sequence[StepEntry], feed=None) -> torch.Tensor:
         """A pure decode step (one token and one wanted row per entry) through a CUDA graph.
         The first step of a shape runs directly and is then captured; later ones are replays.
-        Returns logits [len(entries), vocab]."""
+        Returns logits [len(entries), vocab]. ``feed = (ids, rows)``: the token of entry i is not
+        known on the host yet and is taken on the device from ``ids[rows[i]]`` (int32 tensor, list)."""
         S = len(entries)
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             raise StepError("a graph step takes one token and one wanted row per entry")
@@ -214,6 +217,10 @@ class ModelRunner:
         if S > cap:
             raise StepError(f"{S} sequences exceed the limit of {self.max_requests}")
         ctx = self._prepare(entries, seq_cap=cap, width_cap=self.max_width)
+        if feed is not None:
+            ids, rows = feed
+            idx = self.upload_ints("token_feed", np.asarray(rows, dtype=np.int32), capacity=self.max_requests)
+            torch.index_select(ids, 0, idx, out=ctx.tokens[:S])
         self.storage.zero_new_slots()
         caches = self.storage.layer_views(self._tables)
         self.model.prepare(ctx, caches)
@@ -226,8 +233,17 @@ class ModelRunner:
             gen = self._generation
             graph = torch.cuda.CUDAGraph()
             torch.cuda.current_stream().synchronize()
-            with torch.cuda.graph(graph):
-                captured = self.model.forward(ctx, caches)      # recorded, not run
+            # No garbage collection while the stream records: collecting an engine that is no longer
+            # used destroys its graphs, a call that is not allowed during capture and spoils it.
+            collecting = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    captured = self.model.forward(ctx, caches)      # recorded, not run
+            finally:
+                if collecting:
+                    gc.enable()
             ops.add_launches(-launches)                          # recording launched nothing
             if gen == self._generation:                           # no buffer moved while capturing
                 self._graphs[key] = {"graph": graph, "logits": captured, "launches": launches}

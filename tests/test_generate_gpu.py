@@ -132,3 +132,34 @@ def test_graph_decode_equals_direct_decode(folders, dtype):
     if dtype == "float32":
         assert outs[True] == plain_generate(folders["B"], prompts, 40)[:0] + [
             o[:p.max_tokens] for o, p in zip(plain_generate(folders["B"], prompts, 40), params)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
+    """With ``async_decode`` a decode step is launched before the tokens of the step before it have been
+    read (they pass on the device): the tokens are those of the one-step-at-a-time engine, with requests of
+    different lengths, seeded sampling, a stop token in the middle and so few pages that requests are preempted."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("B", [5, 30, 12, 70, 3, 41])
+    free = LLM(folders["B"], dtype=dtype, max_batch=6, max_seq_len=160, max_gen_len=40, block_size=8, async_decode=False)
+    stop_at = free.generate([prompts[2]], SamplingParams(ignore_eos=True, max_tokens=12))[0].token_ids[7]
+    params = [SamplingParams(ignore_eos=True, max_tokens=40), SamplingParams(ignore_eos=True, max_tokens=9, temperature=0.8, top_p=0.9, seed=5),
+              SamplingParams(ignore_eos=True, max_tokens=30, stop_token_ids=(stop_at,)), SamplingParams(ignore_eos=True, max_tokens=17),
+              SamplingParams(ignore_eos=True, max_tokens=33, temperature=1.1, top_k=20, seed=9), SamplingParams(ignore_eos=True, max_tokens=1)]
+    outs = {}
+    for ahead in (False, True):
+        for blocks in (None, 18):                  # 18 pages of 8 tokens do not hold what the requests grow to
+            llm = LLM(folders["B"], dtype=dtype, max_batch=6, max_seq_len=160, max_gen_len=40, block_size=8,
+                      num_blocks=blocks, enable_prefix_cache=False, async_decode=ahead)
+            res = llm.generate(prompts, params)
+            outs[ahead, blocks] = [(g.token_ids, g.finish_reason) for g in res]
+            assert (llm.stats["ahead_steps"] > 10) == ahead
+            if blocks:
+                assert llm.scheduler.num_preemptions > 0
+            llm.runner.manager.check_invariant()
+            assert not llm.runner.manager.requests
+    assert outs[True, None] == outs[False, None]
+    assert outs[True, 18] == outs[False, 18]
+    if dtype == "float32":
+        assert outs[True, 18] == outs[True, None]
+    assert outs[True, None][2][1] == "eos" and outs[True, None][5][0].__len__() == 1

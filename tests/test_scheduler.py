@@ -183,3 +183,50 @@ def test_prefix_hits_skip_computed_pages():
     while s.has_unfinished():
         run_step(s, cache)
     cache.check_invariant()
+
+
+def test_decode_step_decided_ahead_of_its_tokens():
+    """``schedule_ahead``: the step after a decode step, decided before that step's tokens are known. It
+    holds the same requests one position further, leaves out a request that ends by length with the
+    unread token, and declines (None) while a request waits or when a page is missing."""
+    s, cache = make(num_pages=8, page_size=4, max_seqs=3, budget=64, max_gen=6)
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=6))
+    b = s.add_request([4, 5, 6, 7, 8], SamplingParams(max_tokens=2))
+    run_step(s, cache)                                  # prompts, first tokens
+    items = s.schedule()                                # a decode step, "launched": lengths committed, not read
+    assert [(it.seq.id, it.start, it.count) for it in items] == [(a, 3, 1), (b, 5, 1)]
+    for it in items:
+        cache.commit(it.seq.id, it.start + 1)
+    ahead = s.schedule_ahead(items)
+    # b has one output and may have two: the unread token ends it, so only a goes on
+    assert [(it.seq.id, it.start, it.count, it.want_logits) for it in ahead] == [(a, 4, 1, True)]
+    assert cache.blocks_for(6) <= len(cache.table(0, a))
+    s.update(items, {a: 50, b: 51})
+    for it in ahead:
+        cache.commit(it.seq.id, it.start + 1)
+    s.update(ahead, {a: 52})
+    seq_a = next(q for q in s.running if q.id == a)
+    assert seq_a.outputs[-2:] == [50, 52] and seq_a.num_computed == 5
+    assert [q.id for q in s.finished] == [b]
+    cache.check_invariant()
+    # a waiting request: the next step may admit it, which is not decided blind
+    items = s.schedule()
+    for it in items:
+        cache.commit(it.seq.id, it.start + 1)
+    s.add_request([9] * 3)
+    assert s.schedule_ahead(items) is None
+    s.update(items, {a: 53})
+
+
+def test_no_step_ahead_without_a_page():
+    s, cache = make(num_pages=2, page_size=4, max_seqs=2, budget=64, max_gen=8)
+    a = s.add_request([1, 2, 3, 4, 5, 6], SamplingParams(max_tokens=8))
+    run_step(s, cache)                                  # 6 tokens: both pages taken
+    items = s.schedule()                                # position 6 fits the second page
+    cache.commit(a, 7)
+    ahead = s.schedule_ahead(items)                     # position 7 still fits
+    assert ahead is not None and ahead[0].start == 7
+    s.update(items, {a: 70})
+    cache.commit(a, 8)
+    assert s.schedule_ahead(ahead) is None              # position 8 needs a third page: left to schedule()
+    s.update(ahead, {a: 71})
