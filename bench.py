@@ -169,7 +169,7 @@ def main() -> int:
         runner.finish("prefill")
 
     if args.section == "decode":
-        pre_ms = float("nan")
+        pre_ms = own_ms = float("nan")
     else:
         for i in range(3):
             prefill_once(i)
