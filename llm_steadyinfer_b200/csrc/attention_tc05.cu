@@ -30,13 +30,6 @@
 #include "tma_common.cuh"
 #include <limits.h>
 
-// 2^x in fp32 by the hardware approximation (2 ulp); exp2(-inf) = 0.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 template <int NROWS>
 __device__ __forceinline__ bf16* half_ptr(bf16* base, int row, int chunk) {
   return base + (size_t)(chunk >> 3) * (NROWS * 64) + (size_t)row * 64 + (((chunk & 7) ^ (row & 7)) << 3);

@@ -19,13 +19,6 @@
 #include "attention_common.cuh"
 #include "tma_common.cuh"
 
-// 2^x in fp32 by the hardware approximation (2 ulp); exp2(-inf) = 0.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 // Tile of NROWS rows stored as 64-column halves; inside a half, row r holds its eight 16-byte
 // chunks at positions chunk ^ (r % 8): the layout the 128-byte TMA swizzle writes.
 template <int NROWS>
