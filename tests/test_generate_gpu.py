@@ -163,3 +163,42 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
     if dtype == "float32":
         assert outs[True, 18] == outs[True, None]
     assert outs[True, None][2][1] == "eos" and outs[True, None][5][0].__len__() == 1
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_workloads_ahead_and_not(folders, seed):
+    """Random workloads (more requests than run at once, shared prefixes, stop tokens, sampling with seeds,
+    pools that force preemption): the engine that launches steps ahead and the one that does not give the
+    same tokens and finish reasons, and no page or slot is left behind."""
+    import random
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    rng = random.Random(seed)
+    cfg = CONFIGS["B"][0]
+    V = cfg["vocab_size"]
+    shared = ru.random_tokens(V, 24, 4000 + seed)
+    prompts, params = [], []
+    for i in range(14):
+        n = rng.choice([1, 2, 5, 9, 17, 33, 60])
+        toks = ru.random_tokens(V, n, 5000 + 100 * seed + i)
+        if rng.random() < 0.3:
+            toks = shared + toks
+        prompts.append(toks)
+        kw = {"max_tokens": rng.choice([1, 2, 7, 16, 29]), "ignore_eos": rng.random() < 0.5}
+        if rng.random() < 0.5:
+            kw.update(temperature=rng.choice([0.6, 1.0]), top_p=rng.choice([1.0, 0.8]), top_k=rng.choice([0, 10]),
+                      seed=rng.randrange(1000))
+        if rng.random() < 0.3:
+            kw["stop_token_ids"] = tuple(rng.randrange(V) for _ in range(40))     # likely to end a request early
+        params.append(SamplingParams(**kw))
+    blocks = rng.choice([20, 26])
+    outs = []
+    for ahead in (False, True):
+        llm = LLM(folders["B"], dtype="float32", max_batch=5, max_seq_len=128, max_gen_len=32, block_size=8,
+                  num_blocks=blocks, async_decode=ahead)
+        res = llm.generate(prompts, params)
+        outs.append([(g.token_ids, g.finish_reason) for g in res])
+        llm.runner.manager.check_invariant()
+        assert not llm.runner.manager.requests
+        if ahead:
+            assert llm.stats["ahead_steps"] > 0
+    assert outs[0] == outs[1]
