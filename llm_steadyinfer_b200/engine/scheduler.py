@@ -198,12 +198,11 @@ class Scheduler:
             if len(seq.outputs) + 1 >= seq.max_gen:
                 continue                                  # ends by length with the unread token
             if not self.cache.can_grow(seq.id, it.start + 2):
-                return None
+                return None                               # pages taken for earlier rows stay with their requests
+            self.cache.grow(seq.id, it.start + 2)
             items.append(ScheduledItem(seq, it.start + 1, 1, True))
         if not items:
             return None
-        for it in items:
-            self.cache.grow(it.seq.id, it.start + 1)
         self.num_steps += 1
         return items
 

@@ -230,3 +230,22 @@ def test_no_step_ahead_without_a_page():
     cache.commit(a, 8)
     assert s.schedule_ahead(ahead) is None              # position 8 needs a third page: left to schedule()
     s.update(ahead, {a: 71})
+
+
+def test_step_ahead_counts_pages_row_by_row():
+    """Two requests that each need a new page for the step ahead and one free page: the step ahead is
+    declined (the page that the first took stays with it), nothing is raised."""
+    s, cache = make(num_pages=5, page_size=4, max_seqs=2, budget=64, max_gen=8)
+    a = s.add_request([1, 2, 3], SamplingParams(max_tokens=8))
+    b = s.add_request([4, 5, 6], SamplingParams(max_tokens=8))
+    run_step(s, cache)                                  # prompts: one page each, lengths 3
+    items = s.schedule()                                # position 3 of both: still the first page
+    for it in items:
+        cache.commit(it.seq.id, 4)
+    assert cache.free_pages(0) == 3
+    taken = cache.groups[0].pool.allocate(2)              # someone else takes two pages: one is left
+    assert s.schedule_ahead(items) is None              # position 4 needs a second page for both
+    s.update(items, {a: 7, b: 8})
+    assert cache.free_pages(0) == 0
+    cache.groups[0].pool.release(taken[0]); cache.groups[0].pool.release(taken[1])
+    cache.check_invariant()
