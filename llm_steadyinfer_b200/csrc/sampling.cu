@@ -1,4 +1,5 @@
-// Token selection from fp32 logits, one block per row.
+// Token selection from fp32 logits: one block per row (sample_kernel), or, for batches that are greedy
+// throughout, the vocabulary of a row split over 32 blocks (argmax_split_kernel).
 //  * greedy: argmax, ties to the lowest index, as the reference's batch argmax
 //    (src/source/op/kernels/cuda/argmax_kernel.cu:14-19, 93-117).
 //  * temperature / top-k / top-p: p_i = exp((x_i - max) / T); keep the k largest logits
