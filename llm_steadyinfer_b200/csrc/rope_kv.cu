@@ -122,11 +122,17 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, long l
   const int lanes_h = blockDim.x / cpr;           // head lanes
   const int c = threadIdx.x % cpr, hl = threadIdx.x / cpr;
   const int rot_end = min(head_end, H + KV);
+  // the sines and cosines of the token's angles, once for the block (every head lane needs the same ones)
+  __shared__ float s_sin[128], s_cos[128];
+  if (head_begin < rot_end) {
+    const float fpos = (float)pos;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(fpos * inv_freq[i], &s_sin[i], &s_cos[i]);
+  }
+  __syncthreads();
   if (hl < lanes_h && head_begin + hl < rot_end) {
     float sn[8], cs[8];
-    const float fpos = (float)pos;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sincosf(fpos * inv_freq[c * 8 + i], &sn[i], &cs[i]);
+    for (int i = 0; i < 8; ++i) { sn[i] = s_sin[c * 8 + i]; cs[i] = s_cos[c * 8 + i]; }
     for (int head = head_begin + hl; head < rot_end; head += lanes_h) {
       T* x = row + (size_t)head * hs;
       uint4 lo = *reinterpret_cast<const uint4*>(x + c * 8);
@@ -183,7 +189,7 @@ SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const
   const int work = hpb * hs / 2;
   const int threads = work >= 2048 ? 256 : (work >= 128 ? 128 : 64);
   dim3 grid(num_tokens, blocks_y);
-  const bool vec = dtype == SI_BF16 && inv_freq && rot_dim >= 16 && rot_dim % 16 == 0 && hs % 8 == 0 &&
+  const bool vec = dtype == SI_BF16 && inv_freq && rot_dim >= 16 && rot_dim <= 256 && rot_dim % 16 == 0 && hs % 8 == 0 &&
                    row_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) &&
                    ((uintptr_t)v_cache % 16 == 0);
   if (vec) {
