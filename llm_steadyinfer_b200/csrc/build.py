@@ -161,10 +161,17 @@ def load(name: str, verbose: bool = True) -> ctypes.CDLL:
         return lib
 
 
-def build_all(verbose: bool = True, jobs: Optional[int] = None) -> List[str]:
-    """Compile every source that has no up-to-date library; returns the library paths."""
-    names = kernel_sources()
-    todo = [n for n in names if not os.path.isfile(library_path(n))]
+def prebuild(names, verbose: bool = True) -> None:
+    """Compile those of ``names`` that have no up-to-date library, several at a time: what a model needs
+    is known when it is built, and its first step need not wait for one compiler run after the other."""
+    build_all(verbose, names=sorted(set(names)))
+
+
+def build_all(verbose: bool = True, jobs: Optional[int] = None, names: Optional[List[str]] = None) -> List[str]:
+    """Compile every source (or every one of ``names``) that has no up-to-date library; returns the
+    library paths."""
+    names = kernel_sources() if names is None else list(names)
+    todo = [n for n in names if n not in _libs and not os.path.isfile(library_path(n))]
     errors: List[str] = []
 
     _build_dir()

@@ -25,7 +25,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheLayout, CacheManager, CacheStorage, OutOfPages
-from ..csrc import ops
+from ..csrc import build, ops
 from ..csrc.ops import KernelError
 
 STATUS_TEXT = {
@@ -110,6 +110,7 @@ class ModelRunner:
             raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
         self.model = model
         self.device = model.device
+        build.prebuild(model.kernel_files(page_size))       # together now, not one by one inside the first step
         spec = model.spec
         # Caches and state belong to the places of the run order: a layer that runs twice keeps a
         # cache per run; "cache_from = j" reads the cache of the latest earlier run of layer j.

@@ -82,6 +82,13 @@ class Model:
         for prefix, part in self._named_parts():
             part.load_weights({n: tensors[prefix + n] for n in part.weight_shapes()})
 
+    def kernel_files(self, page_size: int) -> List[str]:
+        """CUDA sources of the model's own kernels and of its parts (see ``Part.kernel_files``)."""
+        names = {"embedding", "sampling", "gemm_f32" if self.dtype == torch.float32 else "gemm_skinny"}
+        for _, part in self._named_parts():
+            names.update(part.kernel_files(page_size))
+        return sorted(names)
+
     # ---- forward -------------------------------------------------------------------
     def prepare(self, ctx, caches) -> None:
         """Host-side planning of the parts for this step (work lists, uploads); runs before

@@ -54,6 +54,15 @@ class Attention(Mixer):
     def cache_need(self):
         return CacheNeed(self.KV, self.hs, self.window)
 
+    def kernel_files(self, page_size):
+        names = ["rope_kv", "gemm_f32" if self.dtype == torch.float32 else "gemm_skinny"]
+        if not self.uses_tensor_cores():
+            return tuple(names + ["attention_ref"])
+        names.append("attention_mma")
+        if self.hs in (64, 128) and page_size in (8, 16, 32, 64):        # the layouts the TMA-fed kernels take
+            names += ["attention_tma"] * bool(USE_TMA) + ["attention_tc05"] * bool(USE_TC05)
+        return tuple(names)
+
     def forward(self, x, ctx, cache):
         T = x.shape[0]
         H, KV, hs = self.H, self.KV, self.hs

@@ -68,6 +68,11 @@ class Part:
         weights); matrices are converted to the compute dtype."""
         return False
 
+    def kernel_files(self, page_size: int) -> Tuple[str, ...]:
+        """Names of the CUDA sources (``csrc/<name>.cu``) this part launches, so that they can be compiled
+        together before the first step; a part that names none has its kernels compiled when first used."""
+        return ()
+
 
 class Norm(Part):
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,

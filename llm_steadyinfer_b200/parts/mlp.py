@@ -44,6 +44,11 @@ class GatedMLP(FeedForward):
             .reshape(2 * self.inter, self.hidden).contiguous()
         self.down = tensors["down_proj.weight"].contiguous()
 
+    def kernel_files(self, page_size):
+        if self.dtype == torch.float32:
+            return ("gemm_f32", "swiglu")
+        return ("gemm_skinny", "swiglu") + (("gemm_tc05",) if self.group == INTERLEAVE and USE_TC05_GEMM else ())
+
     def forward(self, x, ctx):
         T = x.shape[0]
         act = ctx.buf("ffn_act", (T, self.inter), self.dtype)

@@ -29,6 +29,9 @@ class RMSNorm(Norm):
     def load_weights(self, tensors):
         self.weight = tensors["weight"].contiguous()
 
+    def kernel_files(self, page_size):
+        return ("norm",)
+
     def forward(self, resid, delta, out, rows=None):
         ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows)
 
