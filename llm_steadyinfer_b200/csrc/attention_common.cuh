@@ -8,6 +8,12 @@ typedef __nv_bfloat16 bf16;
 
 struct AttnItem { int seq, row0, ntok, pos0; };
 
+// The split decode kernels keep one ticket per (item, kv head) at the START of their scratch, in a
+// region of this fixed size that never holds anything else: the scratch is shared by launches with
+// different numbers of items and splits, and a ticket that lay behind the partial results would
+// fall, after such a change, on a word that an earlier launch has left a partial result in.
+#define SI_ATTN_TICKETS 65536
+
 struct AttnParams {
   const bf16* q; long long q_stride;
   const bf16* k_cache; const bf16* v_cache;

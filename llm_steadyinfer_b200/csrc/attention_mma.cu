@@ -522,13 +522,13 @@ SI_EXPORT int si_attn_decode_rows(int H, int KV, int hs) {
   return (G <= 64 && need <= cap) ? need : 0;
 }
 
-// Scratch of the split decode kernel in 4-byte words: partial outputs, (max, sum) pairs and
-// one ticket counter per (item, kv head). It must be zero before its first use; the kernel
-// leaves the counters at zero.
+// Scratch of the split decode kernel in 4-byte words: SI_ATTN_TICKETS ticket counters (one per (item,
+// kv head) is used), then partial outputs and (max, sum) pairs. The tickets must be zero before
+// their first use; the kernel leaves them at zero.
 SI_EXPORT long long si_attn_decode_scratch_floats(int num_items, int H, int KV, int hs, int nsplit) {
   if (nsplit <= 1) return 0;
   const long long rows = si_attn_decode_rows(H, KV, hs);
-  return (long long)num_items * KV * nsplit * rows * (hs + 2) + (long long)num_items * KV;
+  return SI_ATTN_TICKETS + (long long)num_items * KV * nsplit * rows * (hs + 2);
 }
 
 template <int HS_PAD, int MT>
@@ -560,10 +560,10 @@ SI_EXPORT int si_attn_decode(const void* q, long long q_stride, const void* k_ca
   if (rows <= 0 || nsplit < 1 || nsplit > 65535) return -2;
   p.nsplit = nsplit;
   if (nsplit > 1) {
-    if (!scratch) return -2;
-    p.part_o = scratch;
-    p.part_ml = scratch + (size_t)num_items * KV * nsplit * rows * hs;
-    p.counters = reinterpret_cast<int*>(p.part_ml + (size_t)num_items * KV * nsplit * rows * 2);
+    if (!scratch || (long long)num_items * KV > SI_ATTN_TICKETS) return -2;
+    p.counters = reinterpret_cast<int*>(scratch);
+    p.part_o = scratch + SI_ATTN_TICKETS;
+    p.part_ml = p.part_o + (size_t)num_items * KV * nsplit * rows * hs;
   }
   if (hs <= 64) {
     if (rows == 16) return launch_decode<64, 1>(p, num_items, stream);

@@ -487,7 +487,7 @@ SI_EXPORT int si_attn_encode_cache_map(void* map_out, const void* cache, long lo
 SI_EXPORT long long si_attn_decode_tma_scratch_floats(int num_items, int H, int KV, int hs, int nsplit) {
   if (nsplit <= 1) return 0;
   const long long rows = rows_for(H, KV);
-  return (long long)num_items * KV * nsplit * rows * (hs + 2) + (long long)num_items * KV;
+  return SI_ATTN_TICKETS + (long long)num_items * KV * nsplit * rows * (hs + 2);
 }
 
 template <int NH, int MT, bool SWAP = false>
@@ -531,10 +531,10 @@ SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* 
   p.window = window; p.nsplit = nsplit; p.status = status;
   const int rows = rows_for(H, KV);
   if (nsplit > 1) {
-    if (!scratch) return -2;
-    p.part_o = scratch;
-    p.part_ml = scratch + (size_t)num_items * KV * nsplit * rows * hs;
-    p.counters = reinterpret_cast<int*>(p.part_ml + (size_t)num_items * KV * nsplit * rows * 2);
+    if (!scratch || (long long)num_items * KV > SI_ATTN_TICKETS) return -2;
+    p.counters = reinterpret_cast<int*>(scratch);
+    p.part_o = scratch + SI_ATTN_TICKETS;
+    p.part_ml = p.part_o + (size_t)num_items * KV * nsplit * rows * hs;
   }
   int log2_page = 0;
   while ((1 << log2_page) < page_size) ++log2_page;

@@ -431,6 +431,35 @@ def test_attention_window_edge():
             assert hit == visible, (target, tails)
 
 
+@pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
+def test_split_decode_shares_its_scratch_between_shapes(tma):
+    """One scratch buffer serves launches with different numbers of items and splits, as the engine's does
+    from step to step: a launch with many items and splits fills it with partial results, a launch with few
+    follows and must find its tickets at zero all the same (they have a region of their own)."""
+    o = ops()
+    H, KV, hs, page_size = 16, 1, 64, 16                # 16 query heads per KV head: every row of a partial tile is written
+    lengths = [300, 290, 280, 270, 260, 250]
+    seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page_size, seed=31)
+    kcd, vcd, tb = kc.to(DEV), vc.to(DEV), table.to(DEV)
+    floats = o.attn_decode_tma_scratch_floats if tma else o.attn_decode_scratch_floats
+    decode = o.attn_decode_tma if tma else o.attn_decode
+    scratch = torch.zeros(floats(len(lengths), H, KV, hs, 4), device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    full = [plain_llama.attention(q.double(), k.double(), v.double(), scale, None) for q, k, v in seqs]
+    vmax = max(v.abs().max().item() for _, _, v in seqs)
+    for which, nsplit in (([0, 1, 2, 3, 4, 5], 4), ([1], 2), ([0, 2, 4], 3), ([5], 4), ([0, 1, 2, 3, 4, 5], 2)):
+        items = torch.tensor([(s, i, 1, lengths[s] - 1) for i, s in enumerate(which)], dtype=torch.int32, device=DEV)
+        q = torch.stack([seqs[s][0][lengths[s] - 1].reshape(-1) for s in which]).to(torch.bfloat16).to(DEV)
+        out = torch.full_like(q, float("nan"))
+        decode(q, kcd, vcd, tb, items, out, page_size, len(lengths), H, KV, hs, scale, 0, nsplit=nsplit,
+               scratch=scratch, status=status)
+        want = torch.stack([full[s][lengths[s] - 1].reshape(-1) for s in which])
+        assert status.item() == 0
+        assert not torch.isnan(out).any(), (which, nsplit)
+        assert (out.double().cpu() - want).abs().max().item() <= 2 ** -8 * vmax, (which, nsplit)
+
+
 @pytest.mark.parametrize("batch,ctx,nsplit", [(8, 8192, 4), (64, 2048, 1)])
 @pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
 def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):

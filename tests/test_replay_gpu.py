@@ -107,6 +107,21 @@ def test_replay_at_8b_layer_shape(tmp_path_factory, dtype):
     print(f"8B layer shape {dtype}: worst difference {worst:.2e} (allowed {atol:.2e})")
 
 
+@pytest.mark.parametrize("seed", [101, 102, 103])
+def test_mixed_replay_more_orders(folders, plains, seed):
+    """More random orders of the mixed replay at the layout of the TMA and tcgen05 kernels, bf16: steps with
+    one request follow steps with several, so that scratch shared between steps changes its layout."""
+    name = "C"
+    cfg, cseed, _ = CONFIGS[name]
+    reqs = {f"r{i}": ru.random_tokens(cfg["vocab_size"], n, 1000 * cseed + i)
+            for i, n in enumerate([2, 40, 129, 200, 330, 65, 64, 128])}
+    max_tokens = 384 + 64 * (seed % 3)
+    steps = ru.trace_mixed(reqs, max_tokens, seed=seed)
+    rp = replayer(folders[name], name, torch.bfloat16, max_tokens)
+    ru.compare(rp, steps, reqs, plains[name], ATOL[torch.bfloat16], f"{name}/mixed/seed {seed}")
+    rp.runner.manager.check_invariant()
+
+
 def test_trace_run_program(folders, plains, tmp_path):
     """The program itself, as a user runs it: JSON lines in, .f32 files and 'done' lines out."""
     name = "B"
