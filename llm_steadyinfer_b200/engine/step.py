@@ -54,7 +54,11 @@ class StepContext:
     def __init__(self, runner: "ModelRunner"):
         self._runner = runner
         self.num_tokens = 0               # rows of the step (with padding rows in a fixed-shape step)
-        self.num_seqs = 0
+        self.num_seqs = 0                 # sequences of this step (host-side planning loops over them)
+        # Rows of the block tables and of ctx_len, q_start, slots: what kernels check a row's sequence number
+        # against. In a fixed-shape step it is the shape's capacity, not this step's count: kernel arguments
+        # are recorded with the graph, and a later step of the same shape may hold more sequences.
+        self.seq_slots = 0
         self.num_logit_rows = 0
         self.status = runner.status
         self.plans: Dict = {}             # per-step host-side plans of parts, cleared each step
@@ -358,6 +362,7 @@ class ModelRunner:
         ctx.plans.clear()
         ctx.seq_cap = seq_cap
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T_cap, S, R_cap
+        ctx.seq_slots = S_cap
         ctx.tokens = dev[b_tok:b_tok + T_cap]
         ctx.positions = dev[b_pos:b_pos + T_cap]
         ctx.row_seq = dev[b_seq:b_seq + T_cap]

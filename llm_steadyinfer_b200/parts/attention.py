@@ -76,7 +76,7 @@ class Attention(Mixer):
         inv_freq, rot_dim = rot if rot is not None else (None, 0)
         ops.rope_kv_write(qkv, ctx.positions, ctx.row_seq, inv_freq, rot_dim, cache.block_table,
                           cache.k if cache.writes else None, cache.v if cache.writes else None,
-                          cache.page_size, ctx.num_seqs, H, KV, hs, status=ctx.status)
+                          cache.page_size, ctx.seq_slots, H, KV, hs, status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * hs), self.dtype)
         self.attend(qkv[:, :H * hs], cache, ctx, attn)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
@@ -143,11 +143,11 @@ class Attention(Mixer):
     def attend(self, q, cache, ctx, out):
         if not self.uses_tensor_cores():
             ops.paged_attention_ref(q, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions,
-                                    out, cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs,
+                                    out, cache.page_size, ctx.seq_slots, self.H, self.KV, self.hs,
                                     self.scale, self.window or 0, status=ctx.status)
             return
         plan = ctx.plans[("attention", self.H, self.KV, self.hs)]
-        args = (cache.page_size, ctx.num_seqs, self.H, self.KV, self.hs, self.scale, self.window or 0)
+        args = (cache.page_size, ctx.seq_slots, self.H, self.KV, self.hs, self.scale, self.window or 0)
         if plan["dec"] is not None:
             if plan["tma"]:
                 ops.attn_decode_tma(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args, nsplit=plan["nsplit"],

@@ -202,3 +202,24 @@ def test_random_workloads_ahead_and_not(folders, seed):
         if ahead:
             assert llm.stats["ahead_steps"] > 0
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_requests_join_a_captured_batch(folders, ahead):
+    """Five requests decode from CUDA graphs (the shape for up to eight is recorded with five), then three more
+    join: the recorded step must serve the larger batch too. Tokens equal the plain implementation's."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    prompts = prompts_of("B", [5, 30, 12, 70, 3, 41, 9, 22])
+    want = plain_generate(folders["B"], prompts, 30)
+    llm = LLM(folders["B"], dtype="float32", max_batch=8, max_seq_len=160, max_gen_len=30, block_size=8,
+              async_decode=ahead)
+    ids = [llm.add_request(p, SamplingParams(ignore_eos=True)) for p in prompts[:5]]
+    for _ in range(12):
+        llm.step()
+    assert llm.stats["graph_steps"] >= 5
+    ids += [llm.add_request(p, SamplingParams(ignore_eos=True)) for p in prompts[5:]]
+    while not llm.all_finished():
+        llm.step()
+    by_id = {s.id: s for s in llm.get_finished()}
+    assert [by_id[i].outputs for i in ids] == want
+    llm.runner.manager.check_invariant()

@@ -122,6 +122,45 @@ def test_mixed_replay_more_orders(folders, plains, seed):
     rp.runner.manager.check_invariant()
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_graph_decode_logits(folders, plains, name):
+    """The CUDA-graph decode step (fixed shapes, padding rows, splits chosen for the bucket) against the plain
+    implementation, row by row, while the set of decoding requests changes between steps, so that graphs of
+    different batch buckets follow each other on the same scratch; bf16."""
+    import random
+    from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
+    from llm_steadyinfer_b200.weights import load_model
+    cfg, cseed, page = CONFIGS[name]
+    lengths = [70, 33, 150, 5, 129, 90, 64, 17, 200]
+    reqs = {f"g{i}": ru.random_tokens(cfg["vocab_size"], n + 40, 7000 + 10 * cseed + i) for i, n in enumerate(lengths)}
+    model = load_model(folders[name], torch.bfloat16, "cuda:0")
+    rn = ModelRunner(model, page_size=page, num_pages=256, max_requests=16, max_step_tokens=512)
+    assert rn.graphs_available()
+    pos = {}
+    for (rid, toks), n in zip(reqs.items(), lengths):          # prompts, directly
+        rn.step([StepEntry(rid, toks[:n], [])])
+        pos[rid] = n
+    rng = random.Random(5)
+    worst, buckets = 0.0, set()
+    for step in range(60):
+        live = [r for r in reqs if pos[r] < len(reqs[r])]
+        if not live:
+            break
+        chosen = rng.sample(live, rng.choice([1, 1, 2, 3, 5, 8, 9][:max(1, min(7, len(live)))]) if len(live) > 1 else 1)
+        chosen = chosen[:len(live)]
+        logits = rn.step_decode_graph([StepEntry(r, [reqs[r][pos[r]]], [0]) for r in chosen])
+        buckets.add(len(chosen))
+        for i, r in enumerate(chosen):
+            ref = plains[name].of(reqs[r])[pos[r]]
+            d = (logits[i].double().cpu() - ref).abs().max().item()
+            assert d <= ATOL[torch.bfloat16], f"{name}: step {step}, request {r} at position {pos[r]} beside {chosen}: {d:.3e}"
+            worst = max(worst, d)
+            pos[r] += 1
+    rn.check_status()
+    assert len(rn._graphs) >= 3, "several batch buckets were captured"
+    print(f"{name} graph decode: worst difference {worst:.2e}, batch sizes {sorted(buckets)}")
+
+
 def test_trace_run_program(folders, plains, tmp_path):
     """The program itself, as a user runs it: JSON lines in, .f32 files and 'done' lines out."""
     name = "B"
