@@ -165,15 +165,16 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, dtype):
     assert outs[True, None][2][1] == "eos" and outs[True, None][5][0].__len__() == 1
 
 
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("C", "bfloat16")])
 @pytest.mark.parametrize("seed", [1, 2, 3])
-def test_random_workloads_ahead_and_not(folders, seed):
+def test_random_workloads_ahead_and_not(folders, seed, name, dtype):
     """Random workloads (more requests than run at once, shared prefixes, stop tokens, sampling with seeds,
     pools that force preemption): the engine that launches steps ahead and the one that does not give the
     same tokens and finish reasons, and no page or slot is left behind."""
     import random
     from llm_steadyinfer_b200 import LLM, SamplingParams
     rng = random.Random(seed)
-    cfg = CONFIGS["B"][0]
+    cfg, _, page = CONFIGS[name]
     V = cfg["vocab_size"]
     shared = ru.random_tokens(V, 24, 4000 + seed)
     prompts, params = [], []
@@ -190,10 +191,10 @@ def test_random_workloads_ahead_and_not(folders, seed):
         if rng.random() < 0.3:
             kw["stop_token_ids"] = tuple(rng.randrange(V) for _ in range(40))     # likely to end a request early
         params.append(SamplingParams(**kw))
-    blocks = rng.choice([20, 26])
+    blocks = rng.choice([20, 26]) * 8 // page
     outs = []
     for ahead in (False, True):
-        llm = LLM(folders["B"], dtype="float32", max_batch=5, max_seq_len=128, max_gen_len=32, block_size=8,
+        llm = LLM(folders[name], dtype=dtype, max_batch=5, max_seq_len=128, max_gen_len=32, block_size=page,
                   num_blocks=blocks, async_decode=ahead)
         res = llm.generate(prompts, params)
         outs.append([(g.token_ids, g.finish_reason) for g in res])
