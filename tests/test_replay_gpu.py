@@ -161,6 +161,69 @@ def test_graph_decode_logits(folders, plains, name):
     print(f"{name} graph decode: worst difference {worst:.2e}, batch sizes {sorted(buckets)}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name,seed", [("B", 1), ("C", 2), ("C", 3)])
+def test_random_serving_through_the_runner(folders, plains, name, seed, dtype):
+    """The step function driven as the entry point drives it, with given tokens: steps that mix prompt
+    portions with decode rows run directly, steps of decode rows alone run from CUDA graphs, in random turn;
+    requests join while others decode and leave when done, in a pool that makes them wait for pages. Every
+    wanted row against the plain implementation."""
+    import random
+    from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
+    from llm_steadyinfer_b200.weights import load_model
+    cfg, _, page = CONFIGS[name]
+    rng = random.Random(seed)
+    num_pages = 640 // page
+    rn = ModelRunner(load_model(folders[name], dtype, "cuda:0"), page_size=page, num_pages=num_pages, max_requests=8,
+                     max_step_tokens=256)
+    pool = [ru.random_tokens(cfg["vocab_size"], rng.choice([3, 17, 40, 64, 65, 100, 129, 180]) + rng.choice([5, 20, 33]),
+                             seed * 100 + i) for i in range(12)]
+    waiting, live = list(range(len(pool))), {}                 # live: request -> [tokens done, tokens of its "prompt"]
+    steps = graph_steps = 0
+    worst = 0.0
+    while waiting or live:
+        while waiting and len(live) < 6 and rng.random() < 0.5:
+            i = waiting[0]
+            if sum(-(-len(pool[j]) // page) for j in list(live) + [i]) > num_pages:
+                break
+            waiting.pop(0)
+            live[i] = [0, len(pool[i]) - rng.choice([5, 20])]
+        entries, meta = [], []
+        prompts = [i for i in live if live[i][0] < live[i][1]]
+        for i in live:
+            if live[i][0] >= live[i][1] and rng.random() < 0.85:
+                entries.append(StepEntry(f"q{i}", [pool[i][live[i][0]]], [0]))
+                meta.append((i, live[i][0], 1))
+        from_graph = not prompts or rng.random() < 0.3
+        budget = rng.choice([16, 48, 100])
+        for i in ([] if from_graph else prompts):
+            n = min(budget, live[i][1] - live[i][0], rng.choice([2, 7, 30, 64, 100]))
+            if n <= 0:
+                break
+            budget -= n
+            p = live[i][0]
+            entries.append(StepEntry(f"q{i}", pool[i][p:p + n], [n - 1]))
+            meta.append((i, p + n - 1, n))
+        if not entries:
+            continue
+        logits = rn.step_decode_graph(entries) if from_graph else rn.step(entries)
+        steps += 1
+        graph_steps += from_graph
+        for r, (i, p, n) in enumerate(meta):
+            d = (logits[r].double().cpu() - plains[name].of(pool[i])[p]).abs().max().item()
+            assert d <= ATOL[dtype], (f"{name} {dtype}: step {steps}, request q{i} position {p} ({n} tokens, "
+                                      f"from a graph: {from_graph}, batch {[(m[0], m[2]) for m in meta]}): {d:.3e}")
+            worst = max(worst, d)
+            live[i][0] += n
+        for i in [i for i in live if live[i][0] >= len(pool[i])]:
+            rn.finish(f"q{i}")
+            del live[i]
+    rn.check_status()
+    rn.manager.check_invariant()
+    assert graph_steps >= 10 and steps - graph_steps >= 10
+    print(f"{name} {dtype}: {steps} steps, {graph_steps} from graphs, worst difference {worst:.2e}")
+
+
 def test_trace_run_program(folders, plains, tmp_path):
     """The program itself, as a user runs it: JSON lines in, .f32 files and 'done' lines out."""
     name = "B"
