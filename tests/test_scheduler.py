@@ -249,3 +249,58 @@ def test_step_ahead_counts_pages_row_by_row():
     assert cache.free_pages(0) == 0
     cache.groups[0].pool.release(taken[0]); cache.groups[0].pool.release(taken[1])
     cache.check_invariant()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_serving_with_and_without_steps_ahead(seed):
+    """A stand-in model (the token of request r at output index i is a fixed function of both) under random
+    arrivals, small pools, stop tokens and shared prefixes: with steps decided ahead where the scheduler allows
+    it and without, every request ends with the same tokens and reason, and the cache keeps its books."""
+    import random
+
+    def token(seq, index):
+        return (hash((seq.id, index)) % 97) + 3
+
+    def serve(ahead):
+        rng = random.Random(seed)
+        s, cache = make(num_pages=rng.choice([12, 20, 40]), page_size=4, max_seqs=4, budget=rng.choice([8, 32]),
+                        max_len=64, max_gen=12, prefix=True, eos=(5, 6, 7))
+        shared = [11, 12, 13, 14, 15, 16, 17, 18]
+        todo = []
+        for i in range(16):
+            prompt = [20 + rng.randrange(50) for _ in range(rng.choice([1, 3, 6, 10, 17]))]
+            if rng.random() < 0.3:
+                prompt = shared + prompt
+            todo.append((rng.randrange(0, 30), prompt, SamplingParams(max_tokens=rng.choice([1, 2, 5, 12])), i))
+        inflight, step, aheads = None, 0, 0
+        while todo or s.has_unfinished() or inflight:
+            for t in [t for t in todo if t[0] <= step]:
+                todo.remove(t)
+                s.add_request(t[1], t[2], req_id=f"r{t[3]}")
+            step += 1
+            items = inflight if inflight is not None else s.schedule()
+            if inflight is None:
+                for it in items:
+                    cache.commit(it.seq.id, it.start + it.count)
+            inflight = None
+            if ahead and items and all(it.count == 1 and it.want_logits for it in items):
+                nxt = s.schedule_ahead(items)
+                if nxt is not None:
+                    for it in nxt:
+                        cache.commit(it.seq.id, it.start + it.count)
+                    inflight = nxt
+                    aheads += 1
+            # the index of the token a row draws: outputs so far, plus one when the row was decided ahead
+            sampled = {it.seq.id: token(it.seq, it.start + it.count - len(it.seq.prompt)) for it in items if it.want_logits}
+            s.update(items, sampled)
+            cache.check_invariant()
+            assert step < 5000
+        assert not cache.requests
+        return {q.id: (q.outputs, q.finish_reason) for q in s.finished}, aheads
+
+    plain, _ = serve(False)
+    piped, aheads = serve(True)
+    assert plain == piped
+    assert aheads > 0
+    for outs, reason in plain.values():
+        assert reason in ("eos", "length") and len(outs) >= 1
