@@ -16,6 +16,8 @@ This module is host bookkeeping only; the tensors live in ``CacheStorage``.
 """
 from __future__ import annotations
 
+import itertools
+
 import hashlib
 import struct
 from dataclasses import dataclass, field
@@ -118,7 +120,11 @@ class CacheManager:
         if self.prefix_reuse:
             self.groups[0].pool.on_evict = self._forget_page
         self.new_slots: List[int] = []     # slots admitted since the storage last zeroed state
-        self.versions: Dict[Hashable, int] = {}     # bumped whenever a request's tables change
+        # A number per live request that changes whenever its tables change. The numbers are never used
+        # twice, also not by a later request under the same name, so that whoever caches something
+        # derived from a table under (name, number) cannot mistake one request's table for another's.
+        self.versions: Dict[Hashable, int] = {}
+        self._version = itertools.count(1)
 
     # ---- queries -------------------------------------------------------------------
     def has(self, req) -> bool:
@@ -158,7 +164,7 @@ class CacheManager:
             raise OutOfSlots(f"all {self.slots.num_slots} state slots are in use")
         rc = RequestCache(slot=slot)
         self.requests[req] = rc
-        self.versions[req] = 0
+        self.versions[req] = next(self._version)
         self.new_slots.append(slot)
         for g in self.groups:
             g.tables[req] = []
@@ -183,7 +189,7 @@ class CacheManager:
             assert got is not None
             if got:
                 g.tables[req].extend(got)
-                self.versions[req] += 1
+                self.versions[req] = next(self._version)
 
     def commit(self, req, new_length: int) -> None:
         """The request now holds ``new_length`` tokens; windowed groups give back the pages
@@ -200,7 +206,7 @@ class CacheManager:
                 if t[b] >= 0:
                     g.pool.release(t[b])
                     t[b] = -1
-                    self.versions[req] += 1
+                    self.versions[req] = next(self._version)
 
     def can_truncate_to(self, keep_length: int) -> int:
         """Preemption keeps a whole number of pages; with windows or fixed-size state nothing
@@ -222,7 +228,7 @@ class CacheManager:
                     self._release(g, p)
             del t[nb:]
         rc.length = keep
-        self.versions[req] += 1
+        self.versions[req] = next(self._version)
         rc.shared_pages = min(rc.shared_pages, nb)
         if keep == 0:
             self.new_slots.append(rc.slot)           # state starts over

@@ -310,3 +310,28 @@ def test_step_rejects_what_it_cannot_hold(folders):
     rp.run_step([], ["a", "b"])
     rp.runner.manager.check_invariant()
     assert rp.runner.manager.free_pages(0) == 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_a_name_used_again(folders, plains, dtype):
+    """A request ends and a new one comes under the same name, with other tokens, after its pages have gone
+    to someone else, and with a table that has changed as often as the first one's: nothing kept from the first
+    (its block table) may serve the second, or it writes into the other request's pages."""
+    name = "B"
+    cfg, _, page = CONFIGS[name]
+    rp = replayer(folders[name], name, dtype, 256)
+    first = ru.random_tokens(cfg["vocab_size"], 20, 31)
+    other = ru.random_tokens(cfg["vocab_size"], 12, 32)
+    second = ru.random_tokens(cfg["vocab_size"], 20, 33)
+    steps = [
+        ("x", first, 0, 20, ["x"]),          # whole, in one step, and gone
+        ("z", other, 0, 9, []),              # takes the pages that x gave back
+        ("x", second, 0, 20, []),            # the name again, again in one step
+        ("z", other, 9, 3, ["x", "z"]),      # z goes on: its first pages must still hold its keys
+    ]
+    for rid, toks, start, n, end in steps:
+        out = rp.run_step([{"id": rid, "tokens": toks[start:start + n], "want": list(range(n))}], end)
+        for w in range(n):
+            ref = plains[name].of(toks)[start + w]
+            assert (out[w].double().cpu() - ref).abs().max().item() <= ATOL[dtype], (rid, start + w)
+    rp.runner.manager.check_invariant()
