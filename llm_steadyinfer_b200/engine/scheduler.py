@@ -145,11 +145,18 @@ class Scheduler:
         want = params.max_tokens if params.max_tokens is not None else self.max_gen_len
         max_gen = max(1, min(want, self.max_model_len - len(prompt)))      # scheduler.cpp:107-109
         rid = req_id if req_id is not None else next(self._ids)
+        while req_id is None and self._is_live(rid):          # a counter value that a caller's own id has taken
+            rid = next(self._ids)
+        if self._is_live(rid):
+            raise RequestRejected(f"a request with the id {rid!r} is waiting or running")
         seed = params.seed if params.seed is not None else (hash(rid) & 0x7FFFFFFF)
         seq = Sequence_(id=rid, prompt=prompt, params=params, max_gen=max_gen, seed=seed,
                         arrival_time=self.clock())
         self.waiting.append(seq)
         return rid
+
+    def _is_live(self, rid) -> bool:
+        return any(q.id == rid for q in self.running) or any(q.id == rid for q in self.waiting)
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)

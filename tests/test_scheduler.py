@@ -304,3 +304,17 @@ def test_random_serving_with_and_without_steps_ahead(seed):
     assert aheads > 0
     for outs, reason in plain.values():
         assert reason in ("eos", "length") and len(outs) >= 1
+
+
+def test_an_id_cannot_be_live_twice():
+    s, cache = make()
+    s.add_request([1, 2, 3], req_id="a")
+    with pytest.raises(RequestRejected):
+        s.add_request([4, 5], req_id="a")
+    run_step(s, cache)
+    with pytest.raises(RequestRejected):
+        s.add_request([4, 5], req_id="a")                # running now
+    while s.has_unfinished():
+        run_step(s, cache)
+    s.add_request([4, 5], req_id="a")                    # ended: the id is free again
+    assert s.add_request([6], req_id=None) != "a"
