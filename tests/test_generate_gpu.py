@@ -224,3 +224,24 @@ def test_requests_join_a_captured_batch(folders, ahead):
     by_id = {s.id: s for s in llm.get_finished()}
     assert [by_id[i].outputs for i in ids] == want
     llm.runner.manager.check_invariant()
+
+
+def test_shared_prefix_under_load_matches_plain(folders):
+    """Requests with a common prefix run beside each other and beside others in a pool so small that some are
+    preempted: pages of the prefix are shared while requests that use them come, are cut and go. Greedy tokens
+    equal the plain implementation's; the hits are counted."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    cfg = CONFIGS["B"][0]
+    V = cfg["vocab_size"]
+    shared = ru.random_tokens(V, 24, 800)                      # three pages of 8
+    prompts = ([shared + ru.random_tokens(V, n, 810 + n) for n in (3, 11, 20, 6)]
+               + [ru.random_tokens(V, n, 830 + n) for n in (30, 9)])
+    order = [0, 4, 1, 5, 2, 3]
+    prompts = [prompts[i] for i in order]
+    want = plain_generate(folders["B"], prompts, 14)
+    llm = LLM(folders["B"], dtype="float32", max_batch=3, max_seq_len=128, max_gen_len=14, block_size=8, num_blocks=16)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [g.token_ids for g in got] == want
+    assert sum(g.prefix_hit_tokens for g in got) >= 24, "later requests found the shared pages"
+    llm.runner.manager.check_invariant()
+    assert not llm.runner.manager.requests
