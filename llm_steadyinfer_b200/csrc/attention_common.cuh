@@ -14,6 +14,13 @@ struct AttnItem { int seq, row0, ntok, pos0; };
 // fall, after such a change, on a word that an earlier launch has left a partial result in.
 #define SI_ATTN_TICKETS 65536
 
+// The first key that any row of an item can see: with a window of w keys the item's first token, at
+// position pos0, reads keys pos0 - w + 1 onwards. Keys before it are never fetched and their pages
+// never looked up: the cache manager has given those pages back, and their table entries say so.
+__device__ __forceinline__ int window_first_key(int pos0, int window) {
+  return window > 0 && pos0 - window + 1 > 0 ? pos0 - window + 1 : 0;
+}
+
 struct AttnParams {
   const bf16* q; long long q_stride;
   const bf16* k_cache; const bf16* v_cache;

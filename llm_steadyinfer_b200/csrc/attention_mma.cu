@@ -28,8 +28,8 @@ __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
 // Fetch keys [j0, j0 + ROWS) of one KV head into Ks and Vs. Keys at or beyond kv_end, before 0,
 // or on a bad page are zero-filled.
 template <int HS_PAD, int ROWS, int THREADS>
-__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* table, int g, int j0, int kv_end,
-                                             bf16* Ks, bf16* Vs) {
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* table, int g, int j0, int kv_lo,
+                                             int kv_end, bf16* Ks, bf16* Vs) {
   constexpr int CH = HS_PAD / 8;
   constexpr int TOTAL = ROWS * CH;
   static_assert(TOTAL % THREADS == 0, "tile chunks must divide over the threads");
@@ -39,7 +39,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* tab
     const int id = threadIdx.x + it * THREADS;
     const int row = id / CH, c = id % CH;
     const int j = j0 + row;
-    bool valid = j >= 0 && j < kv_end && c < hs_chunks;
+    bool valid = j >= kv_lo && j < kv_end && c < hs_chunks;
     size_t off = 0;
     if (valid) {
       const int slot = j / p.page_size;
@@ -96,12 +96,12 @@ attn_portion_kernel(const AttnParams p) {
   }
   const int* table = p.block_table + (size_t)item.seq * p.table_width;
   const int kv_end = item.pos0 + item.ntok;
-  int kv_begin = 0;
-  if (p.window > 0) kv_begin = max(0, item.pos0 - p.window + 1) / BLOCK_N * BLOCK_N;
+  const int kv_lo = window_first_key(item.pos0, p.window);
+  const int kv_begin = kv_lo / BLOCK_N * BLOCK_N;
   const int ntiles = (kv_end - kv_begin + BLOCK_N - 1) / BLOCK_N;
 
   load_q_tile<HS_PAD, BLOCK_M, THREADS>(p, item, g, Qs);
-  load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin, kv_end, Ks, Vs);
+  load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin, kv_lo, kv_end, Ks, Vs);
   cp_async_commit();
 
   // the two rows this thread owns in the warp's 16-row slab
@@ -126,7 +126,7 @@ attn_portion_kernel(const AttnParams p) {
     bf16* Kt = Ks + (t & 1) * BLOCK_N * HS_PAD;
     bf16* Vt = Vs + (t & 1) * BLOCK_N * HS_PAD;
     if (t + 1 < ntiles) {
-      load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, j0 + BLOCK_N, kv_end,
+      load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, j0 + BLOCK_N, kv_lo, kv_end,
                                              Ks + ((t + 1) & 1) * BLOCK_N * HS_PAD,
                                              Vs + ((t + 1) & 1) * BLOCK_N * HS_PAD);
       cp_async_commit();
@@ -255,8 +255,8 @@ attn_decode_kernel(const AttnParams p) {
   }
   const int* table = p.block_table + (size_t)item.seq * p.table_width;
   const int kv_end_all = item.pos0 + item.ntok;
-  int kv_begin_all = 0;
-  if (p.window > 0) kv_begin_all = max(0, item.pos0 - p.window + 1) / BLOCK_N * BLOCK_N;
+  const int kv_lo = window_first_key(item.pos0, p.window);
+  const int kv_begin_all = kv_lo / BLOCK_N * BLOCK_N;
   // this block's share of the key range, in whole tiles
   const int tiles_all = (kv_end_all - kv_begin_all + BLOCK_N - 1) / BLOCK_N;
   const int tiles_per = (tiles_all + p.nsplit - 1) / p.nsplit;
@@ -288,7 +288,7 @@ attn_decode_kernel(const AttnParams p) {
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     if (st < ntiles)
-      load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin + st * BLOCK_N, kv_end,
+      load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin + st * BLOCK_N, kv_lo, kv_end,
                                              Ks + st * BLOCK_N * HS_PAD, Vs + st * BLOCK_N * HS_PAD);
     cp_async_commit();
   }
@@ -300,7 +300,7 @@ attn_decode_kernel(const AttnParams p) {
     {
       const int tn = t + STAGES - 1;            // refill the buffer that was read in iteration t - 1
       if (tn < ntiles)
-        load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin + tn * BLOCK_N, kv_end,
+        load_kv_tile<HS_PAD, BLOCK_N, THREADS>(p, table, g, kv_begin + tn * BLOCK_N, kv_lo, kv_end,
                                                Ks + (tn % STAGES) * BLOCK_N * HS_PAD,
                                                Vs + (tn % STAGES) * BLOCK_N * HS_PAD);
       cp_async_commit();

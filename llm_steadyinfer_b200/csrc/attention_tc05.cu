@@ -67,8 +67,8 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   const int tile_tokens = BM / p.G;                  // tokens of one query tile
   const bool two = item.ntok > tile_tokens;          // the second query tile has rows
   const int kv_end = item.pos0 + item.ntok;
-  int kv_begin = 0;
-  if (p.window > 0) kv_begin = max(0, item.pos0 - p.window + 1) / BN * BN;
+  const int kv_lo = window_first_key(item.pos0, p.window);
+  const int kv_begin = kv_lo / BN * BN;
   const int ntiles = (kv_end - kv_begin + BN - 1) / BN;
   const int page_rows = 1 << log2_page;
   const int pages_per_tile = BN >> log2_page;
@@ -88,13 +88,15 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 9) tmem_alloc(&tmem_slot, TM_COLS);
-  // rows of the last tile that no copy fills must hold finite numbers (they meet zero probabilities)
-  if ((kv_end - kv_begin) % BN != 0) {
-    const int stage = (ntiles - 1) % STAGES;
+  // rows that no copy fills must hold finite numbers (they meet zero probabilities): those behind the
+  // last key in the last tile, and pages wholly before the window in the first
+  auto clear_stage = [&](int stage) {
     uint4* kz = reinterpret_cast<uint4*>(Ks + (size_t)stage * TILE);
     uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
     for (int i = threadIdx.x; i < TILE / 8; i += blockDim.x) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
-  }
+  };
+  if ((kv_end - kv_begin) % BN != 0) clear_stage((ntiles - 1) % STAGES);
+  if (kv_begin + page_rows <= kv_lo) clear_stage(0);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   tc05_fence_before_sync();
   __syncthreads();                                   // barriers, tensor memory and the zeroed rows stand
@@ -142,7 +144,8 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
       for (int i = 0; i < 2; ++i) {
         const int b = lane + 32 * i;
         const int pg = b / (2 * NH);
-        if (b < boxes && j + pg * page_rows < kv_end) {           // pages past the last key are not fetched
+        // pages past the last key, or wholly before the window, are not fetched
+        if (b < boxes && j + pg * page_rows < kv_end && j + (pg + 1) * page_rows > kv_lo) {
           const int slot = (j >> log2_page) + pg;
           int page = slot < p.table_width ? table[slot] : -1;
           if (page < 0 || page >= p.num_pages) { set_status(p.status, SI_BAD_PAGE); page = -1; }

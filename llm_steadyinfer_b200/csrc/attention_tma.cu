@@ -68,8 +68,8 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   }
   const int* table = p.block_table + (size_t)item.seq * p.table_width;
   const int kv_end_all = item.pos0 + item.ntok;
-  int kv_begin_all = 0;
-  if (p.window > 0) kv_begin_all = max(0, item.pos0 - p.window + 1) / BLOCK_N * BLOCK_N;
+  const int kv_lo = window_first_key(item.pos0, p.window);
+  const int kv_begin_all = kv_lo / BLOCK_N * BLOCK_N;
   const int tiles_all = (kv_end_all - kv_begin_all + BLOCK_N - 1) / BLOCK_N;
   const int tiles_per = (tiles_all + p.nsplit - 1) / p.nsplit;
   const int t_begin = split * tiles_per;
@@ -86,14 +86,16 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  // Rows of the last tile that no copy fills must hold finite numbers (they meet zero
-  // probabilities): clear the stage the last tile lands in.
-  if (ntiles > 0 && (kv_end - kv_begin) % BLOCK_N != 0) {
-    const int stage = (ntiles - 1) % STAGES;
+  // Rows that no copy fills must hold finite numbers (they meet zero probabilities): clear the stage
+  // the last tile lands in if keys end inside it, and the first one if pages of it lie wholly before
+  // the window.
+  auto clear_stage = [&](int stage) {
     uint4* kz = reinterpret_cast<uint4*>(Ks + (size_t)stage * TILE);
     uint4* vz = reinterpret_cast<uint4*>(Vs + (size_t)stage * TILE);
     for (int i = threadIdx.x; i < TILE / 8; i += blockDim.x) { kz[i] = make_uint4(0, 0, 0, 0); vz[i] = make_uint4(0, 0, 0, 0); }
-  }
+  };
+  if (ntiles > 0 && (kv_end - kv_begin) % BLOCK_N != 0) clear_stage((ntiles - 1) % STAGES);
+  if (ntiles > 0 && kv_begin + page_rows <= kv_lo) clear_stage(0);
   // query rows: tile row r is token r / G, head g*G + r % G
   for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += blockDim.x) {
     const int row = id / (HS_PAD / 8), c = id % (HS_PAD / 8);
@@ -115,7 +117,8 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     constexpr int NOT_NEEDED = -2;
     auto lookup = [&](int t) {
       const int j = kv_begin + t * BLOCK_N;
-      if (t >= ntiles || lane >= boxes || j + pg * page_rows >= kv_end) return NOT_NEEDED;   // pages past the last key are not fetched
+      // pages past the last key, or wholly before the window, are not fetched
+      if (t >= ntiles || lane >= boxes || j + pg * page_rows >= kv_end || j + (pg + 1) * page_rows <= kv_lo) return NOT_NEEDED;
       const int slot = (j >> log2_page) + pg;
       return slot < p.table_width ? __ldg(table + slot) : -1;
     };

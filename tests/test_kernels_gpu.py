@@ -431,6 +431,42 @@ def test_attention_window_edge():
             assert hit == visible, (target, tails)
 
 
+@pytest.mark.parametrize("H,KV,hs,page_size,window", [
+    (4, 2, 64, 16, 40), (8, 2, 128, 16, 100), (2, 1, 64, 8, 11), (6, 3, 64, 16, 70), (5, 5, 80, 32, 7),
+    (16, 2, 128, 32, 200), (3, 1, 32, 4, 5), (2, 1, 256, 16, 129)])
+@pytest.mark.parametrize("nsplit", [1, 3])
+@pytest.mark.parametrize("tma", [False, True, "tc05"], ids=["cp_async", "tma", "tcgen05"])
+def test_attention_window_with_pages_given_back(H, KV, hs, page_size, window, nsplit, tma):
+    """Pages that lie wholly before the window of a step's first token have been given back: their table
+    entries are -1 and the pages hold someone else's data (NaN here). The kernels round the first key
+    down to a tile of 64, so such pages fall inside their first tile; they are neither looked up
+    nor read, and no status is raised."""
+    tc05 = tma == "tc05"
+    tma = bool(tma)
+    if tc05 and nsplit != 1:
+        pytest.skip("splits concern the decode kernel only")
+    lengths = [1, 37, 130, 700, 64, 129, 650, 333]
+    tails = [1, 1, 3, 45, 64, 2, 300, 1]
+    seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page_size, seed=12)
+    gone = 0
+    for s, (n, tl) in enumerate(zip(lengths, tails)):
+        first_needed = (n - min(tl, n)) - window + 1          # what the step's first token reads from
+        for b in range(max(0, first_needed) // page_size):
+            kc[table[s, b]] = float("nan"); vc[table[s, b]] = float("nan")
+            table[s, b] = -1
+            gone += 1
+    assert gone > 20
+    out, rows, used_dec, used_por = _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page_size, window,
+                                                      nsplit, tma, tc05)
+    assert used_dec and used_por
+    scale = 1.0 / math.sqrt(hs)
+    full = [plain_llama.attention(q.double(), k.double(), v.double(), scale, window) for q, k, v in seqs]
+    want = torch.stack([full[s][p].reshape(-1) for s, p in rows])
+    assert not torch.isnan(out).any(), "every row was written, and nothing of a page given back was read"
+    vmax = max(v.abs().max().item() for _, _, v in seqs)
+    assert (out - want).abs().max().item() <= 2 ** -8 * vmax
+
+
 @pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
 def test_split_decode_shares_its_scratch_between_shapes(tma):
     """One scratch buffer serves launches with different numbers of items and splits, as the engine's does

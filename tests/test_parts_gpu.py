@@ -352,3 +352,70 @@ def test_window_gives_pages_back_while_stepping(tmp_path):
     assert sum(1 for p in mgr.table(1 - win, "r") if p >= 0) == 13
     rp.run_step([], ["r"])
     mgr.check_invariant()
+
+
+def _windowed_llama_register():
+    """An architecture of this test: the Llama arrangement with a window on every attention layer."""
+    from dataclasses import replace
+    from llm_steadyinfer_b200.config.base import ModelConfig, register_architecture
+    from llm_steadyinfer_b200.models.llama import LlamaConfig
+
+    @dataclass(frozen=True)
+    class WindowedConfig(ModelConfig):
+        d: dict
+        architecture = "WindowedToyForCausalLM"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(dict(d))
+
+        def to_dict(self):
+            return dict(self.d)
+
+        def model_spec(self):
+            d = {k: v for k, v in self.d.items() if k != "window"}
+            base = LlamaConfig.from_dict({**d, "architectures": ["LlamaForCausalLM"]}).model_spec()
+            layers = [replace(l, mixer=replace(l.mixer, params={**l.mixer.params, "window": self.d["window"]}))
+                      for l in base.layers]
+            return replace(base, layers=layers)
+
+    register_architecture("WindowedToyForCausalLM", WindowedConfig)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("head_dim,heads,kv_heads,window,page_size", [(64, 4, 2, 40, 16), (128, 3, 1, 100, 16), (64, 6, 3, 11, 8),
+                                                                      (96, 2, 2, 70, 32)])
+def test_windowed_layers_with_pages_given_back(tmp_path, dtype, head_dim, heads, kv_heads, window, page_size):
+    """Windowed attention at head sizes that the tensor-core kernels take, cut every way. Those kernels
+    round the first key down to a tile of 64 keys, and pages inside that tile have been given back
+    (table entries of -1) once the window has passed them: they are neither looked up nor reported.
+    Compared with the plain implementation and its own window, within what the other replay tests allow."""
+    _windowed_llama_register()
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    from llm_steadyinfer_b200.weights import write_random_model
+    cfg = {
+        "architectures": ["WindowedToyForCausalLM"], "hidden_size": 136, "intermediate_size": 200,
+        "num_hidden_layers": 3, "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim,
+        "vocab_size": 411, "max_position_embeddings": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "rope_scaling": None, "tie_word_embeddings": False, "hidden_act": "silu", "window": window,
+    }
+    folder = os.path.join(str(tmp_path), "windowed")
+    write_random_model(folder, cfg, seed=6, store_dtype=torch.bfloat16)
+    _, w = pl.read_model_folder(folder)
+    reqs = {"x": ru.random_tokens(cfg["vocab_size"], 300, 41), "y": ru.random_tokens(cfg["vocab_size"], 133, 42),
+            "z": ru.random_tokens(cfg["vocab_size"], 190, 43)}
+    want = {r: pl.forward(cfg, w, t, window=window) for r, t in reqs.items()}
+    atol = 1e-5 if dtype == torch.float32 else 1e-2
+    for mode in ("whole", "tail", "portions", "mixed"):
+        rp = Replayer(folder, dtype, max_tokens=704, page_size=page_size)
+        steps = {"whole": ru.trace_whole, "tail": ru.trace_tail,
+                 "portions": ru.trace_portions}.get(mode, lambda r: ru.trace_mixed(r, 704, seed=1))(reqs)
+        worst = 0.0
+        for rid, p, row in ru.replay_in_process(rp, steps):
+            diff = (row.double() - want[rid][p]).abs().max().item()
+            assert diff <= atol, f"windowed layers, {mode}: request {rid} position {p} differs by {diff:.2e}"
+            worst = max(worst, diff)
+        mgr = rp.runner.manager
+        mgr.check_invariant()
+        assert not mgr.requests and mgr.free_pages(0) == mgr.groups[0].pool.num_pages
+        print(f"windowed head_dim {head_dim} window {window} {dtype} {mode}: worst {worst:.2e}")
