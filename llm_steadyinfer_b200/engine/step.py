@@ -206,7 +206,8 @@ class ModelRunner:
             self.manager.commit(e.req, new_len)
 
     def graphs_available(self) -> bool:
-        return True
+        """Decode steps may be captured only if every part of the model says that it can be."""
+        return self.model.capturable()
 
     def step_decode_graph(self, entries: Sequence[StepEntry], feed=None) -> torch.Tensor:
         """A pure decode step (one token and one wanted row per entry) through a CUDA graph.
@@ -214,6 +215,8 @@ class ModelRunner:
         Returns logits [len(entries), vocab]. ``feed = (ids, rows)``: the token of entry i is not
         known on the host yet and is taken on the device from ``ids[rows[i]]`` (int32 tensor, list)."""
         S = len(entries)
+        if not self.graphs_available():
+            raise StepError("a part of this model cannot be captured into a graph; run the step directly")
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             raise StepError("a graph step takes one token and one wanted row per entry")
         cap = next((b for b in GRAPH_BUCKETS if b >= S), None)

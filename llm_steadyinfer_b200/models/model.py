@@ -89,6 +89,10 @@ class Model:
             names.update(part.kernel_files(page_size))
         return sorted(names)
 
+    def capturable(self) -> bool:
+        """True if every part's ``forward`` may be captured into a CUDA graph (see ``Part.capturable``)."""
+        return all(part.capturable for _, part in self._named_parts())
+
     # ---- forward -------------------------------------------------------------------
     def prepare(self, ctx, caches) -> None:
         """Host-side planning of the parts for this step (work lists, uploads); runs before

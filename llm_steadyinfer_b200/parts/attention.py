@@ -54,6 +54,12 @@ class Attention(Mixer):
     def cache_need(self):
         return CacheNeed(self.KV, self.hs, self.window)
 
+    @property
+    def capturable(self):
+        """The step's work lists are made in ``prepare``; a position encoding applied through its
+        unfused hook decides for itself."""
+        return self.position is None or self.position.capturable
+
     def kernel_files(self, page_size):
         names = ["rope_kv", "gemm_f32" if self.dtype == torch.float32 else "gemm_skinny"]
         if not self.uses_tensor_cores():

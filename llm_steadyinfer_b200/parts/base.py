@@ -17,6 +17,8 @@ know which model or layer it sits in. Four kinds exist:
 Every part lists the checkpoint tensors it wants under its prefix (``weight_shapes()``) and
 takes them with ``load_weights()``; it may fuse or re-lay them out there.
 
+A part whose ``forward`` can be captured into a CUDA graph says so with ``capturable = True``.
+
 Another part is added by subclassing and ``register_mixer`` / ``register_feed_forward`` /
 ``register_norm`` / ``register_position`` under a new kind name; a configuration class then
 names that kind in its layer specs.
@@ -51,6 +53,12 @@ class StateNeed:
 
 
 class Part:
+    # True if ``forward`` reads nothing on the host that changes from step to step: whatever depends on
+    # the step comes from device tensors of ``ctx`` or is planned in ``prepare``, and nothing waits for
+    # the device. Only then may a decode step be captured into a CUDA graph and replayed; a model with a
+    # part that says False (the default, which is always right) runs every step directly.
+    capturable = False
+
     def __init__(self, params: Dict[str, Any], dtype: torch.dtype, device: torch.device):
         self.params = dict(params)
         self.dtype = dtype

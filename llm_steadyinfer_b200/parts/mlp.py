@@ -22,6 +22,8 @@ TC05_MIN_ROWS = 128    # below one 128-row tile the library product and the acti
 
 
 class GatedMLP(FeedForward):
+    capturable = True
+
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
         self.hidden = int(params["hidden_size"])

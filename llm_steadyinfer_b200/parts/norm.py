@@ -14,6 +14,8 @@ from .base import Norm, register_norm
 
 
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
         self.size = int(params["size"])

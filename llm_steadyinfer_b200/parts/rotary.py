@@ -35,6 +35,8 @@ def rotary_inverse_frequencies(rot_dim: int, theta: float, scaling) -> torch.Ten
 
 
 class Rotary(PositionEncoding):
+    capturable = True
+
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
         self.head_dim = int(params["head_dim"])

@@ -419,3 +419,64 @@ def test_windowed_layers_with_pages_given_back(tmp_path, dtype, head_dim, heads,
         mgr.check_invariant()
         assert not mgr.requests and mgr.free_pages(0) == mgr.groups[0].pool.num_pages
         print(f"windowed head_dim {head_dim} window {window} {dtype} {mode}: worst {worst:.2e}")
+
+
+def _greedy(logits_of, prompt, n_new):
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(torch.argmax(logits_of(toks)[-1]))
+        out.append(t)
+        toks.append(t)
+    return out
+
+
+def test_toy_architecture_generates_through_the_entry_point(tmp_path):
+    """The toy parts read host values in ``forward`` and leave ``capturable`` at its default, so no
+    decode step of theirs is captured into a graph; requests come and go with so few pages that
+    some are put back, and the state slots are zeroed for each admission."""
+    _toy_register()
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    from llm_steadyinfer_b200.weights import write_random_model
+    from safetensors.torch import load_file
+    folder = os.path.join(str(tmp_path), "toy")
+    write_random_model(folder, TOY, seed=5, store_dtype=torch.float32)
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    prompts = [ru.random_tokens(TOY["vocab_size"], n, 60 + i) for i, n in enumerate([3, 41, 18, 70, 9])]
+    want = [_greedy(lambda t: _toy_plain(TOY, w, t), p, 20) for p in prompts]
+    llm = LLM(folder, dtype="float32", max_batch=3, max_seq_len=96, max_gen_len=20, block_size=8,
+              max_num_batched_tokens=32, num_blocks=20)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [g.token_ids for g in got] == want
+    assert llm.stats["graph_steps"] == 0 and llm.stats["ahead_steps"] == 0
+    llm.runner.manager.check_invariant()
+    assert not llm.runner.manager.requests
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_windowed_layers_generate_through_the_entry_point(tmp_path, ahead):
+    """Windowed layers through the scheduler, captured decode steps and steps launched ahead: the
+    windowed group gives pages back while requests decode, and its pool is smaller than the
+    requests' lengths would need without a window."""
+    _windowed_llama_register()
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    from llm_steadyinfer_b200.weights import write_random_model
+    cfg = {
+        "architectures": ["WindowedToyForCausalLM"], "hidden_size": 72, "intermediate_size": 100,
+        "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 32,
+        "vocab_size": 211, "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "rope_scaling": None, "tie_word_embeddings": True, "hidden_act": "silu", "window": 24,
+    }
+    folder = os.path.join(str(tmp_path), "windowed")
+    write_random_model(folder, cfg, seed=8, store_dtype=torch.float32)
+    _, w = pl.read_model_folder(folder)
+    prompts = [ru.random_tokens(cfg["vocab_size"], n, 80 + i) for i, n in enumerate([5, 90, 33, 120])]
+    want = [_greedy(lambda t: pl.forward(cfg, w, t, window=24), p, 40) for p in prompts]
+    # 4 requests of up to 160 tokens would hold 80 pages of 8 without a window; with it, 4 + 1 + the step's growth each
+    llm = LLM(folder, dtype="float32", max_batch=4, max_seq_len=160, max_gen_len=40, block_size=8,
+              max_num_batched_tokens=32, num_blocks=40, async_decode=ahead)
+    got = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [g.token_ids for g in got] == want
+    assert llm.stats["graph_steps"] > 0
+    assert (llm.stats["ahead_steps"] > 0) == ahead
+    llm.runner.manager.check_invariant()
+    assert not llm.runner.manager.requests
