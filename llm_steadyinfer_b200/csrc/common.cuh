@@ -82,6 +82,19 @@ __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
+// A hint that [base, base + bytes) will be streamed soon: block `part` of `parts` asks the memory system
+// to bring its share into L2, one prefetch per 128-byte line. Kernels that wait on latency while HBM
+// idles (the norms of a decode step) call this for the first weights of the matrix product after them.
+__device__ __forceinline__ void l2_prefetch_share(const void* base, long long bytes, int part, int parts) {
+  constexpr long long LINE = 128;
+  const long long lines = bytes / LINE;
+  const long long per = (lines + parts - 1) / parts;
+  const long long c0 = (long long)part * per;
+  const long long c1 = c0 + per < lines ? c0 + per : lines;
+  for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x)
+    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(reinterpret_cast<const char*>(base) + c * LINE) : "memory");
+}
+
 static inline bool si_pdl_enabled() {
   static int on = -1;
   if (on < 0) {

@@ -48,8 +48,13 @@ template <> struct Vec8<__nv_bfloat16> {
 template <typename TX, typename TW, int CHUNKS>
 __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
                                        const int* __restrict__ rows, const TW* __restrict__ weight,
-                                       TX* __restrict__ out, int hidden, float eps) {
+                                       TX* __restrict__ out, int hidden, float eps, int num_rows,
+                                       const void* ahead, long long ahead_bytes) {
   __shared__ float scratch[33];
+  if ((int)blockIdx.x >= num_rows) {              // blocks behind the rows only fetch ahead
+    l2_prefetch_share(ahead, ahead_bytes, blockIdx.x - num_rows, gridDim.x - num_rows);
+    return;
+  }
   pdl_prologue();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -124,7 +129,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TX* __restri
 
 template <typename TX, typename TW>
 static int launch2(float* resid, const void* delta, const int* rows, const void* weight, void* out,
-                   int num_rows, int hidden, float eps, cudaStream_t stream) {
+                   int num_rows, int hidden, float eps, const void* ahead, long long ahead_bytes, cudaStream_t stream) {
   const TX* d = (const TX*)delta;
   const TW* w = (const TW*)weight;
   TX* o = (TX*)out;
@@ -136,9 +141,13 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
     int threads = nchunks > 256 ? 512 : (nchunks > 128 ? 256 : 128);
     if (num_rows >= 1024 && nchunks <= 1024) threads = min(threads, 256);   // many rows: more blocks per SM
     const int per = (nchunks + threads - 1) / threads;
-    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, dim3(num_rows), dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps);
-    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, dim3(num_rows), dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps);
-    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, dim3(num_rows), dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps);
+    // with something to fetch ahead: enough further blocks that every SM takes part
+    if (ahead && ahead_bytes < 4096) ahead = nullptr;
+    const int extra = ahead ? max(0, 148 - num_rows) + 148 : 0;
+    const dim3 grid(num_rows + extra);
+    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes);
+    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes);
+    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes);
     return si_last_error();
   }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -150,17 +159,19 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
   return si_last_error();
 }
 
-// x_dtype: dtype of delta and out. Returns 0, a CUDA error code, or -2 (size refused).
+// x_dtype: dtype of delta and out. `ahead` (may be null): `ahead_bytes` bytes that the kernel after this
+// one streams, fetched into L2 meanwhile (a hint: the vectorised kernel takes it, the other one ignores it).
+// Returns 0, a CUDA error code, or -2 (size refused).
 SI_EXPORT int si_add_rmsnorm(float* resid, const void* delta, const int* rows, const void* weight,
                              int weight_dtype, void* out, int x_dtype, int num_rows, int hidden,
-                             float eps, cudaStream_t stream) {
+                             float eps, const void* ahead, long long ahead_bytes, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (x_dtype == SI_BF16) {
     if (weight_dtype == SI_BF16)
-      return launch2<__nv_bfloat16, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
-    return launch2<__nv_bfloat16, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
+      return launch2<__nv_bfloat16, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
+    return launch2<__nv_bfloat16, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
   }
   if (weight_dtype == SI_BF16)
-    return launch2<float, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
-  return launch2<float, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, stream);
+    return launch2<float, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
+  return launch2<float, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
 }

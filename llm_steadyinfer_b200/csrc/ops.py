@@ -5,6 +5,7 @@ Nothing here computes on the CPU or through a library: a missing build fails lou
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -115,11 +116,17 @@ def embedding_gather(tokens, table, out, status=None) -> None:
              _ptr(status), _stream()), "embedding_gather")
 
 
-def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None) -> None:
+# Most bytes that one launch fetches ahead into L2. Measured on the 8B shape: 4 to 8 MB, what arrives while
+# the norm waits on its own loads, shorten a decode step by 0.5 to 1.3 %; 16 MB and more lengthen it.
+AHEAD_BYTES = int(os.environ.get("SI_AHEAD_MB", "8")) << 20
+
+
+def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None, ahead=None) -> None:
     """resid (fp32, in place) += delta; out = weight * resid * rsqrt(mean(resid^2) + eps).
 
     With ``rows`` (int32 [R]) output row r comes from stream row rows[r] and resid stays
-    as it is.
+    as it is. ``ahead``: a tensor that the kernel after this one streams from memory (weights of
+    the next matrix product); further blocks of this launch start fetching it into L2.
     """
     _cuda(resid, delta, weight, out, rows)
     _i32(rows, "rows")
@@ -133,9 +140,13 @@ def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None) -> None:
     R = out.shape[0]
     _need(R == (rows.numel() if rows is not None else resid.shape[0]), "add_rmsnorm: row count mismatch")
     f = _fn("norm", "si_add_rmsnorm",
-            [_c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+            [_c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_p])
+    ahead_bytes = 0
+    if ahead is not None:
+        _cuda(ahead)
+        ahead_bytes = min(ahead.numel() * ahead.element_size(), AHEAD_BYTES) if ahead.is_contiguous() else 0
     _check(f(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), _dt(weight), _ptr(out), _dt(out),
-             R, d, float(eps), _stream()), f"add_rmsnorm(hidden={d})")
+             R, d, float(eps), _ptr(ahead) if ahead_bytes else None, ahead_bytes, _stream()), f"add_rmsnorm(hidden={d})")
 
 
 def rope_kv_write(qkv, positions, row_seq, inv_freq, rot_dim: int, block_table, k_cache, v_cache,

@@ -60,6 +60,10 @@ class Attention(Mixer):
         unfused hook decides for itself."""
         return self.position is None or self.position.capturable
 
+    def streams_first(self, rows):
+        # few rows in bfloat16 go to the weight-streaming product, which reads every weight once
+        return self.qkv if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
+
     def kernel_files(self, page_size):
         names = ["rope_kv", "gemm_f32" if self.dtype == torch.float32 else "gemm_skinny"]
         if not self.uses_tensor_cores():

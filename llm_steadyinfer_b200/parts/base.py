@@ -76,6 +76,11 @@ class Part:
         weights); matrices are converted to the compute dtype."""
         return False
 
+    def streams_first(self, rows: int) -> Optional[torch.Tensor]:
+        """The weights that ``forward`` on ``rows`` rows reads first, if it streams them from memory once
+        (few rows); the launch before it may fetch them into L2 ahead. None: nothing to fetch ahead."""
+        return None
+
     def kernel_files(self, page_size: int) -> Tuple[str, ...]:
         """Names of the CUDA sources (``csrc/<name>.cu``) this part launches, so that they can be compiled
         together before the first step; a part that names none has its kernels compiled when first used."""
@@ -83,6 +88,10 @@ class Part:
 
 
 class Norm(Part):
+    # True if ``forward`` takes ``ahead=tensor``: what the part after the norm streams first, which the
+    # norm's launch may start fetching into L2 (only asked of norms that say so)
+    takes_ahead = False
+
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError

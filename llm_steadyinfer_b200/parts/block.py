@@ -30,7 +30,14 @@ class Block:
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx, cache) -> torch.Tensor:
         T, d = resid.shape
         x = ctx.buf("block_x", (T, d), self.mixer.dtype)
-        self.mixer_norm.forward(resid, delta, x)
+        self._norm(self.mixer_norm, resid, delta, x, self.mixer.streams_first(T))
         a = self.mixer.forward(x, ctx, cache)
-        self.feed_forward_norm.forward(resid, a, x)
+        self._norm(self.feed_forward_norm, resid, a, x, self.feed_forward.streams_first(T))
         return self.feed_forward.forward(x, ctx)
+
+    @staticmethod
+    def _norm(norm: Norm, resid, delta, out, ahead) -> None:
+        if ahead is not None and norm.takes_ahead:
+            norm.forward(resid, delta, out, ahead=ahead)
+        else:
+            norm.forward(resid, delta, out)

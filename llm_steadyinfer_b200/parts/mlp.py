@@ -46,6 +46,10 @@ class GatedMLP(FeedForward):
             .reshape(2 * self.inter, self.hidden).contiguous()
         self.down = tensors["down_proj.weight"].contiguous()
 
+    def streams_first(self, rows):
+        # few rows in bfloat16 go to the weight-streaming product, which reads every weight once
+        return self.gate_up if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
+
     def kernel_files(self, page_size):
         if self.dtype == torch.float32:
             return ("gemm_f32", "swiglu")

@@ -15,6 +15,7 @@ from .base import Norm, register_norm
 
 class RMSNorm(Norm):
     capturable = True
+    takes_ahead = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -34,8 +35,8 @@ class RMSNorm(Norm):
     def kernel_files(self, page_size):
         return ("norm",)
 
-    def forward(self, resid, delta, out, rows=None):
-        ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows)
+    def forward(self, resid, delta, out, rows=None, ahead=None):
+        ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, ahead=ahead)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -61,6 +61,14 @@ def test_add_rmsnorm(xdtype, wdtype, d, T, eps):
     ops().add_rmsnorm(r3, None, w, eps, out3)
     want3 = plain_llama.rmsnorm(resid.double().cpu(), w.double().cpu(), eps)
     assert (out3.double().cpu() - want3).abs().max().item() <= tol
+    # with something to fetch ahead into L2 (a hint for the launch after this one): the same numbers,
+    # for tensors below one chunk, of an odd size, and larger than the most that is fetched
+    for n in (100, 4096 * 3 + 72, 20 << 20):
+        nxt = torch.zeros(n, dtype=torch.uint8, device=DEV)
+        r4 = resid.clone()
+        out4 = torch.empty(T, d, dtype=xdtype, device=DEV)
+        ops().add_rmsnorm(r4, delta, w, eps, out4, ahead=nxt)
+        assert torch.equal(out4, out) and torch.equal(r4, r2)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
