@@ -43,7 +43,7 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
 template <int NH, int MT, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(160)
 attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
-                       const __grid_constant__ CUtensorMap vmap, int log2_page) {
+                       const __grid_constant__ CUtensorMap vmap, int log2_page, const int4* __restrict__ work) {
   constexpr int NWARPS = 4, THREADS = 128, BLOCK_N = 64, ROWS = 16 * MT, HS_PAD = NH * 64;   // consumer warps/threads
   constexpr int KT = HS_PAD / 16, DT = HS_PAD / 8;
   constexpr int TILE = NH * BLOCK_N * 64;             // elements of one K (or V) tile
@@ -58,9 +58,18 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   bf16* Qs = Vs + STAGES * TILE;                     // [NH][ROWS][64]
 
   pdl_prologue();
-  const AttnItem item = p.items[blockIdx.x];
+  // Which share of which item: with a work list, entry blockIdx.x = (item, split, splits of the item, first
+  // partial-result slot of the item), so that long sequences are cut into more shares than short ones;
+  // without one, item blockIdx.x and split blockIdx.z of p.nsplit.
+  int item_idx = blockIdx.x, split = blockIdx.z, nsplit = p.nsplit, slot0 = blockIdx.x * p.nsplit;
+  if (work) {
+    const int4 w = work[blockIdx.x];
+    if (w.x < 0) return;                           // entries behind the step's last one
+    item_idx = w.x; split = w.y; nsplit = w.z; slot0 = w.w;
+  }
+  const AttnItem item = p.items[item_idx];
   if (item.ntok <= 0) return;
-  const int g = blockIdx.y, split = blockIdx.z;
+  const int g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (item.seq < 0 || item.seq >= p.num_seqs) {
     if (threadIdx.x == 0) set_status(p.status, SI_BAD_SEQ);
@@ -71,7 +80,7 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   const int kv_lo = window_first_key(item.pos0, p.window);
   const int kv_begin_all = kv_lo / BLOCK_N * BLOCK_N;
   const int tiles_all = (kv_end_all - kv_begin_all + BLOCK_N - 1) / BLOCK_N;
-  const int tiles_per = (tiles_all + p.nsplit - 1) / p.nsplit;
+  const int tiles_per = (tiles_all + nsplit - 1) / nsplit;
   const int t_begin = split * tiles_per;
   const int t_end = min(tiles_all, t_begin + tiles_per);
   const int ntiles = max(0, t_end - t_begin);
@@ -370,7 +379,9 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
     }
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   const int rows_used = min(ROWS, item.ntok * p.G);
-  const size_t slab0 = ((size_t)blockIdx.x * p.KV + g) * p.nsplit * ROWS;
+  // partial results: [slot0 + split][kv head][row]
+  const size_t slab0 = ((size_t)slot0 * p.KV + g) * ROWS;
+  const size_t slab_step = (size_t)p.KV * ROWS;                       // from one split to the next
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
     const int r = idx / p.hs, d = idx - r * p.hs;
     float M = -INFINITY;
@@ -384,24 +395,24 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
       L += fl[w * ROWS + r] * wgt;
       acc += fo[((size_t)w * ROWS + r) * OS + d] * wgt;
     }
-    if (p.nsplit == 1) {
+    if (nsplit == 1) {
       const int tok = r / p.G, hh = r - tok * p.G;
       p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
           __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
-      const size_t slab = slab0 + (size_t)split * ROWS + r;
+      const size_t slab = slab0 + (size_t)split * slab_step + r;
       __stcg(p.part_o + slab * p.hs + d, acc);
       if (d == 0) { __stcg(p.part_ml + slab * 2, M); __stcg(p.part_ml + slab * 2 + 1, L); }
     }
   }
-  if (p.nsplit == 1) return;
+  if (nsplit == 1) return;
 
   // ticket: the last block of this (item, kv head) merges the splits
   __threadfence();
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   if (threadIdx.x == 0) {
-    const int ticket = atomicAdd(p.counters + blockIdx.x * p.KV + g, 1);
-    s_last = ticket == p.nsplit - 1;
+    const int ticket = atomicAdd(p.counters + item_idx * p.KV + g, 1);
+    s_last = ticket == nsplit - 1;
   }
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   if (!s_last) return;
@@ -411,54 +422,54 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   // (2) one thread per row turns them into the weights of the splits and the row's sum, and (3) the
   // outputs are summed over the splits eight loads at a time. (The warps' merge buffers are free by now.)
   float* w_s = reinterpret_cast<float*>(smem_raw);              // [rows_used][nsplit] maxima, then weights
-  float* l_s = w_s + rows_used * p.nsplit;                        // [rows_used][nsplit] sums
-  float* L_s = l_s + rows_used * p.nsplit;                        // [rows_used]
-  for (int i = threadIdx.x; i < rows_used * p.nsplit; i += THREADS) {
-    const int r = i / p.nsplit, sp = i - r * p.nsplit;
-    const size_t slab = slab0 + (size_t)sp * ROWS + r;
+  float* l_s = w_s + rows_used * nsplit;                        // [rows_used][nsplit] sums
+  float* L_s = l_s + rows_used * nsplit;                        // [rows_used]
+  for (int i = threadIdx.x; i < rows_used * nsplit; i += THREADS) {
+    const int r = i / nsplit, sp = i - r * nsplit;
+    const size_t slab = slab0 + (size_t)sp * slab_step + r;
     w_s[i] = __ldcg(p.part_ml + slab * 2);
     l_s[i] = __ldcg(p.part_ml + slab * 2 + 1);
   }
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   for (int r = threadIdx.x; r < rows_used; r += THREADS) {
     float M = -INFINITY;
-    for (int sp = 0; sp < p.nsplit; ++sp) M = fmaxf(M, w_s[r * p.nsplit + sp]);
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, w_s[r * nsplit + sp]);
     float L = 0.f;
-    for (int sp = 0; sp < p.nsplit; ++sp) {
-      const float ms = w_s[r * p.nsplit + sp];
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float ms = w_s[r * nsplit + sp];
       const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += l_s[r * p.nsplit + sp] * wgt;
-      w_s[r * p.nsplit + sp] = wgt;
+      L += l_s[r * nsplit + sp] * wgt;
+      w_s[r * nsplit + sp] = wgt;
     }
     L_s[r] = L;
   }
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   for (int idx = threadIdx.x; idx < rows_used * p.hs; idx += THREADS) {
     const int r = idx / p.hs, d = idx - r * p.hs;
-    const float* src = p.part_o + (slab0 + r) * p.hs + d;       // split sp lies sp * ROWS * hs further
-    const size_t step = (size_t)ROWS * p.hs;
+    const float* src = p.part_o + (slab0 + r) * p.hs + d;       // split sp lies sp * slab_step * hs further
+    const size_t step = slab_step * p.hs;
     float acc = 0.f;
     int sp = 0;
-    for (; sp + 8 <= p.nsplit; sp += 8) {
+    for (; sp + 8 <= nsplit; sp += 8) {
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + (size_t)(sp + u) * step);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) acc += v[u] * w_s[r * p.nsplit + sp + u];    // in the order of the splits
+      for (int u = 0; u < 8; ++u) acc += v[u] * w_s[r * nsplit + sp + u];    // in the order of the splits
     }
     {
       float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = sp + u < p.nsplit ? __ldcg(src + (size_t)(sp + u) * step) : 0.f;
+      for (int u = 0; u < 8; ++u) v[u] = sp + u < nsplit ? __ldcg(src + (size_t)(sp + u) * step) : 0.f;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) if (sp + u < p.nsplit) acc += v[u] * w_s[r * p.nsplit + sp + u];
+      for (int u = 0; u < 8; ++u) if (sp + u < nsplit) acc += v[u] * w_s[r * nsplit + sp + u];
     }
     const float L = L_s[r];
     const int tok = r / p.G, hh = r - tok * p.G;
     p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d] =
         __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
-  if (threadIdx.x == 0) p.counters[blockIdx.x * p.KV + g] = 0;      // ready for the next launch
+  if (threadIdx.x == 0) p.counters[item_idx * p.KV + g] = 0;      // ready for the next launch
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -493,9 +504,15 @@ SI_EXPORT long long si_attn_decode_tma_scratch_floats(int num_items, int H, int 
   return SI_ATTN_TICKETS + (long long)num_items * KV * nsplit * rows * (hs + 2);
 }
 
+// Scratch of the launch with a work list: the tickets, then `slots` partial results (one per work entry).
+SI_EXPORT long long si_attn_decode_tma_work_floats(int slots, int H, int KV, int hs) {
+  const long long rows = rows_for(H, KV);
+  return SI_ATTN_TICKETS + (long long)slots * KV * rows * (hs + 2);
+}
+
 template <int NH, int MT, bool SWAP = false>
 static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap& vm, int num_items, int log2_page,
-                  cudaStream_t stream) {
+                  const int4* work, int num_work, cudaStream_t stream) {
   constexpr int STAGES = 3, ROWS = 16 * MT, HS_PAD = NH * 64;
   size_t smem = (size_t)(2 * STAGES * 64 + ROWS) * HS_PAD * sizeof(bf16);
   const size_t merge = (size_t)4 * ROWS * (2 + HS_PAD + 4) * sizeof(float);
@@ -506,20 +523,31 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  si_launch(k, dim3(num_items, p.KV, p.nsplit), dim3(160), smem, stream, p, km, vm, log2_page);
+  const dim3 grid = work ? dim3(num_work, p.KV, 1) : dim3(num_items, p.KV, p.nsplit);
+  si_launch(k, grid, dim3(160), smem, stream, p, km, vm, log2_page, work);
   return si_last_error();
 }
 
 // Same contract as si_attn_decode, with the tensor maps of this layer's K and V cache. `max_rows`: the most
 // rows (tokens x query heads of a KV head) that any item has, when the caller knows it, else 0; items of at
 // most 8 rows take the kernel with the swapped products.
+// `work` (may be null): `num_work` entries (item, split, splits of that item, first slot of that item), one
+// block row each, so that every item is cut into its own number of shares; entries with item -1 do nothing.
+// The splits of an item take the slots first slot .. first slot + splits - 1, all below `work_slots`, and
+// every split of an item with more than one has an entry. `nsplit` is not used then; `scratch` holds
+// si_attn_decode_tma_work_floats(work_slots, ...) floats.
 SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                  const void* kmap, const void* vmap, const int* block_table, int table_width,
                                  const void* items, int num_items, void* out, long long out_stride, int num_pages,
                                  int page_size, int num_seqs, int H, int KV, int hs, float scale, int window,
-                                 int nsplit, float* scratch, int max_rows, int* status, cudaStream_t stream) {
+                                 int nsplit, const int* work, int num_work, int work_slots, float* scratch,
+                                 int max_rows, int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_decode_tma_ok(H, KV, hs, page_size) || !kmap || !vmap) return -2;
+  if (work) {
+    if (num_work <= 0 || work_slots <= 0 || !scratch || ((uintptr_t)work % 16)) return -2;
+    nsplit = 1;
+  }
   if ((q_stride % 8) || nsplit < 1 || nsplit > 128) return -2;     // the merge stages 2 * rows * nsplit floats in shared memory
   AttnParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride;
@@ -533,21 +561,23 @@ SI_EXPORT int si_attn_decode_tma(const void* q, long long q_stride, const void* 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.nsplit = nsplit; p.status = status;
   const int rows = rows_for(H, KV);
-  if (nsplit > 1) {
+  if (nsplit > 1 || work) {
     if (!scratch || (long long)num_items * KV > SI_ATTN_TICKETS) return -2;
+    const size_t slots = work ? (size_t)work_slots : (size_t)num_items * nsplit;
     p.counters = reinterpret_cast<int*>(scratch);
     p.part_o = scratch + SI_ATTN_TICKETS;
-    p.part_ml = p.part_o + (size_t)num_items * KV * nsplit * rows * hs;
+    p.part_ml = p.part_o + slots * KV * rows * hs;
   }
+  const int4* wl = reinterpret_cast<const int4*>(work);
   int log2_page = 0;
   while ((1 << log2_page) < page_size) ++log2_page;
   const CUtensorMap& km = *(const CUtensorMap*)kmap;
   const CUtensorMap& vm = *(const CUtensorMap*)vmap;
   if (rows == 16 && max_rows >= 1 && max_rows <= 8)
-    return hs == 64 ? launch<1, 1, true>(p, km, vm, num_items, log2_page, stream)
-                    : launch<2, 1, true>(p, km, vm, num_items, log2_page, stream);
-  if (hs == 64) return rows == 16 ? launch<1, 1>(p, km, vm, num_items, log2_page, stream)
-                                  : launch<1, 2>(p, km, vm, num_items, log2_page, stream);
-  return rows == 16 ? launch<2, 1>(p, km, vm, num_items, log2_page, stream)
-                    : launch<2, 2>(p, km, vm, num_items, log2_page, stream);
+    return hs == 64 ? launch<1, 1, true>(p, km, vm, num_items, log2_page, wl, num_work, stream)
+                    : launch<2, 1, true>(p, km, vm, num_items, log2_page, wl, num_work, stream);
+  if (hs == 64) return rows == 16 ? launch<1, 1>(p, km, vm, num_items, log2_page, wl, num_work, stream)
+                                  : launch<1, 2>(p, km, vm, num_items, log2_page, wl, num_work, stream);
+  return rows == 16 ? launch<2, 1>(p, km, vm, num_items, log2_page, wl, num_work, stream)
+                    : launch<2, 2>(p, km, vm, num_items, log2_page, wl, num_work, stream);
 }

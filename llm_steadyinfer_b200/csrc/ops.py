@@ -379,26 +379,102 @@ def _cache_map(cache: torch.Tensor):
     return _c_p(ent[1])
 
 
+def split_work(tiles, budget: int, entries: int, max_splits: int = 128, min_tiles: int = 1):
+    """Cut decode items into shares of about equal length. ``tiles[i]``: 64-key tiles that item i reads
+    (0: an empty item, which gets no entry). ``budget``: shares that run at the same time. With no more
+    items than that, the shares are as short as ``budget`` shares in all allow (the smallest length L with
+    sum(ceil(tiles / L)) <= budget): more would run in a second round, fewer would leave the longest item
+    to few blocks. With more items than that, L is the mean load of a share, so that a long item among
+    many short ones is still cut. No share is shorter than ``min_tiles``, no item has more than
+    ``max_splits``. Returns an int32 array [entries, 4] of (item, split, splits of the item, first slot
+    of the item), longest shares first, the rest filled with item -1: ``attn_decode_tma(work=...)``;
+    ``entries >= budget + len(tiles)`` always suffices."""
+    import numpy as np
+    key = (tuple(tiles), budget, entries, max_splits, min_tiles)
+    if _split_memo.get("key") == key:               # tile counts change once in 64 decode steps of a sequence
+        return _split_memo["work"]
+    _split_memo["key"], _split_memo["work"] = key, _split_work(np, tiles, budget, entries, max_splits, min_tiles)
+    return _split_memo["work"]
+
+
+_split_memo: dict = {}
+
+
+def _split_work(np, tiles, budget, entries, max_splits, min_tiles):
+    t = np.asarray(tiles, dtype=np.int64)
+    live = np.flatnonzero(t > 0)
+    out = np.full((entries, 4), -1, dtype=np.int32)
+    out[:, 1:] = 0
+    if live.size == 0:
+        return out
+    tl = t[live]
+
+    def splits_for(L):
+        return np.minimum(max_splits, -(-tl // max(L, min_tiles, 1)))
+
+    if live.size <= budget:
+        lo, hi = 1, int(tl.max())                    # smallest L whose shares fit the budget
+        while lo < hi:
+            mid = (lo + hi) // 2
+            if int(splits_for(mid).sum()) <= budget:
+                hi = mid
+            else:
+                lo = mid + 1
+        sp = splits_for(lo)
+    else:
+        sp = splits_for(-(-int(tl.sum()) // max(budget, 1)))
+    if int(sp.sum()) > entries:
+        raise ValueError(f"split_work: {int(sp.sum())} shares do not fit {entries} entries")
+    first = np.concatenate([[0], np.cumsum(sp)[:-1]])
+    order = np.argsort(-(-(-tl // sp)), kind="stable")          # longest shares first: they start first
+    row = 0
+    for j in order:
+        n = int(sp[j])
+        out[row:row + n, 0] = live[j]
+        out[row:row + n, 1] = np.arange(n)
+        out[row:row + n, 2] = n
+        out[row:row + n, 3] = first[j]
+        row += n
+    return out
+
+
+def attn_decode_tma_work_floats(slots: int, H: int, KV: int, hs: int) -> int:
+    lib = build.load("attention_tma")
+    lib.si_attn_decode_tma_work_floats.restype = _c_llr
+    return lib.si_attn_decode_tma_work_floats(_c_int(slots), _c_int(H), _c_int(KV), _c_int(hs))
+
+
 def attn_decode_tma(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int,
                     hs: int, scale: float, window: int = 0, nsplit: int = 1, scratch=None, status=None,
-                    max_rows: int = 0) -> None:
+                    max_rows: int = 0, work=None) -> None:
     """``attn_decode`` with the K/V tiles fetched by TMA (head_dim 64 or 128, page sizes 8 to 64);
     items hold at most ``attn_decode_tma_rows // (H // KV)`` tokens. ``max_rows``: the most rows
     (tokens x query heads of a KV head) of any item when the caller knows it (0: unknown); at most 8
-    rows run the variant with the products taken the other way round."""
+    rows run the variant with the products taken the other way round.
+    ``work`` (int32 [W, 4], rows of (item, split, splits of that item, first slot of that item); item -1:
+    nothing): every item is cut into its own number of shares, ``nsplit`` is not used, and ``scratch``
+    holds ``attn_decode_tma_work_floats(W, ...)`` floats. Made by ``split_work``."""
     _attn_common(q, k_cache, v_cache, block_table, items, out, page_size, H, KV, hs, "attn_decode_tma")
-    if nsplit > 1:
+    if work is not None:
+        _cuda(work, scratch)
+        _need(work.dtype == torch.int32 and work.dim() == 2 and work.shape[1] == 4 and work.is_contiguous(),
+              "attn_decode_tma: work must be int32 [W, 4]")
+        need = attn_decode_tma_work_floats(work.shape[0], H, KV, hs)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need,
+              f"attn_decode_tma: scratch must hold {need} floats")
+    elif nsplit > 1:
         _cuda(scratch)
         need = attn_decode_tma_scratch_floats(items.shape[0], H, KV, hs, nsplit)
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need,
               f"attn_decode_tma: scratch must hold {need} floats")
     f = _fn("attention_tma", "si_attn_decode_tma",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_p])
+    W = work.shape[0] if work is not None else 0
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _cache_map(k_cache), _cache_map(v_cache),
              _ptr(block_table), block_table.shape[1], _ptr(items), items.shape[0], _ptr(out), out.stride(0),
              k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), int(nsplit),
-             _ptr(scratch), int(max_rows), _ptr(status), _stream()),
+             _ptr(work), W, W, _ptr(scratch), int(max_rows), _ptr(status), _stream()),
            f"attn_decode_tma(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")
 
 

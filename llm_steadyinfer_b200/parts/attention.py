@@ -100,10 +100,10 @@ class Attention(Mixer):
     def prepare(self, ctx, cache):
         """Cut the step's sequences into work items for the tensor-core kernels: runs of few
         tokens (decode rows) for the decode kernel, longer portions in runs of the portion
-        kernel's item size. One plan serves every layer with the same head layout."""
+        kernel's item size. One plan serves every layer with the same head layout and window."""
         if not self.uses_tensor_cores():
             return
-        key = ("attention", self.H, self.KV, self.hs)
+        key = ("attention", self.H, self.KV, self.hs, self.window)
         if key in ctx.plans or cache.k is None:
             return
         G = self.H // self.KV
@@ -126,27 +126,41 @@ class Attention(Mixer):
             else:
                 for b in range(0, n, por_tokens):
                     por.append((s, row0 + b, min(por_tokens, n - b), pos0 + b))
-        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma,
+        plan = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "tma": tma, "work": None,
                 "dec_rows": max((d[2] for d in dec), default=0) * G,
                 "tc05": tc05}
         n_dec = len(dec)
         if ctx.seq_cap is not None:                   # fixed shapes: pad with empty items
             dec += [(0, 0, 0, 0)] * (ctx.seq_cap - n_dec)
-        if dec:
+        if dec and tma:
+            # Shares of about equal length for as many blocks as run at once (two per SM), so that a long
+            # sequence beside short ones is cut into more of them; a second wave of blocks would wait.
+            tiles = []
+            for (_, _, n, pos0) in dec:
+                first = max(0, pos0 - self.window + 1) // 64 * 64 if self.window else 0
+                tiles.append(-(-(pos0 + n - first) // 64) if n > 0 else 0)
+            entries = TARGET_BLOCKS // self.KV + len(dec)
+            work = ops.split_work(tiles, TARGET_BLOCKS // self.KV, entries, MAX_SPLITS, MIN_TILES_PER_SPLIT)
+            both = ctx.upload_ints(f"attn_dec_{self.H}_{self.KV}_{self.hs}_{self.window}",
+                                   np.concatenate([np.asarray(dec, dtype=np.int32).reshape(-1), work.reshape(-1)]))
+            plan["dec"] = both[:4 * len(dec)].view(-1, 4)
+            plan["work"] = both[4 * len(dec):].view(-1, 4)
+            plan["scratch"] = ctx.buf("attn_split", (ops.attn_decode_tma_work_floats(entries, self.H, self.KV, self.hs),),
+                                      torch.float32)
+        elif dec:
             # as many blocks as run at once (two per SM), not more: a second wave would wait
             nsplit = max(1, min(MAX_SPLITS, TARGET_BLOCKS // (len(dec) * self.KV)))
             if ctx.seq_cap is None:
                 longest = max(d[3] + d[2] for d in dec)
                 nsplit = min(nsplit, max(1, -(-longest // (64 * MIN_TILES_PER_SPLIT))))
             plan["nsplit"] = nsplit
-            plan["dec"] = ctx.upload_ints(f"attn_dec_{self.H}_{self.KV}_{self.hs}",
+            plan["dec"] = ctx.upload_ints(f"attn_dec_{self.H}_{self.KV}_{self.hs}_{self.window}",
                                           np.asarray(dec, dtype=np.int32)).view(-1, 4)
             if nsplit > 1:
-                floats = ops.attn_decode_tma_scratch_floats if tma else ops.attn_decode_scratch_floats
-                n = floats(len(dec), self.H, self.KV, self.hs, nsplit)
+                n = ops.attn_decode_scratch_floats(len(dec), self.H, self.KV, self.hs, nsplit)
                 plan["scratch"] = ctx.buf("attn_split", (n,), torch.float32)
         if por:
-            plan["por"] = ctx.upload_ints(f"attn_por_{self.H}_{self.KV}_{self.hs}",
+            plan["por"] = ctx.upload_ints(f"attn_por_{self.H}_{self.KV}_{self.hs}_{self.window}",
                                           np.asarray(por, dtype=np.int32)).view(-1, 4)
         ctx.plans[key] = plan
 
@@ -156,11 +170,11 @@ class Attention(Mixer):
                                     out, cache.page_size, ctx.seq_slots, self.H, self.KV, self.hs,
                                     self.scale, self.window or 0, status=ctx.status)
             return
-        plan = ctx.plans[("attention", self.H, self.KV, self.hs)]
+        plan = ctx.plans[("attention", self.H, self.KV, self.hs, self.window)]
         args = (cache.page_size, ctx.seq_slots, self.H, self.KV, self.hs, self.scale, self.window or 0)
         if plan["dec"] is not None:
             if plan["tma"]:
-                ops.attn_decode_tma(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args, nsplit=plan["nsplit"],
+                ops.attn_decode_tma(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args, work=plan["work"],
                                     scratch=plan["scratch"], status=ctx.status, max_rows=plan["dec_rows"])
             else:
                 ops.attn_decode(q, cache.k, cache.v, cache.block_table, plan["dec"], out, *args,

@@ -475,6 +475,53 @@ def test_attention_window_with_pages_given_back(H, KV, hs, page_size, window, ns
     assert (out - want).abs().max().item() <= 2 ** -8 * vmax
 
 
+@pytest.mark.parametrize("H,KV,hs,page_size,window", [(32, 8, 128, 16, None), (4, 2, 64, 8, None), (16, 2, 128, 32, 300),
+                                                     (8, 8, 64, 16, None), (40, 1, 128, 16, None)])
+@pytest.mark.parametrize("budget", [1, 7, 37, 200])
+def test_decode_with_shares_of_equal_length(H, KV, hs, page_size, window, budget):
+    """Decode items of very different lengths, each cut into its own number of shares by ``split_work``:
+    the same outputs as whole sequences give, whatever the budget of shares, with empty items and unused
+    work entries in between, twice over the same scratch."""
+    o = ops()
+    if not o.attn_decode_tma_ok(H, KV, hs, page_size):
+        pytest.skip("the TMA decode kernel does not take this layout")
+    G = H // KV
+    lengths = [2000, 3, 64, 700, 129, 1, 65, 1200]
+    seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page_size, seed=21)
+    dec = [(s, s, 1, n - 1) for s, n in enumerate(lengths)]
+    dec.insert(3, (0, 0, 0, 0))                                  # an empty item, as fixed shapes are padded with
+    tiles = []
+    for (_, _, n, pos0) in dec:
+        first = max(0, pos0 - window + 1) // 64 * 64 if window else 0
+        tiles.append(-(-(pos0 + n - first) // 64) if n else 0)
+    entries = budget + len(dec)
+    work_h = o.split_work(tiles, budget, entries, 32, 2)
+    live = work_h[work_h[:, 0] >= 0]
+    assert len(live) <= budget + len(lengths) and set(live[:, 0].tolist()) == {i for i, t in enumerate(tiles) if t}
+    for i in set(live[:, 0].tolist()):
+        mine = live[live[:, 0] == i]
+        assert sorted(mine[:, 1].tolist()) == list(range(mine[0, 2])) and len(set(mine[:, 3].tolist())) == 1
+    if budget >= 37 and not window:
+        shares = {i: (live[:, 0] == i).sum() for i in range(len(dec))}
+        assert shares[0] > 4 * shares[1 + 1], "the longest item is cut into the most shares"
+    q = torch.stack([seqs[s][0][n - 1].reshape(-1) for s, n in enumerate(lengths)]).to(torch.bfloat16).to(DEV)
+    items = torch.tensor(dec, dtype=torch.int32, device=DEV)
+    work = torch.tensor(work_h, dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(o.attn_decode_tma_work_floats(entries, H, KV, hs), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    full = [plain_llama.attention(qq.double(), k.double(), v.double(), scale, window) for qq, k, v in seqs]
+    want = torch.stack([full[s][n - 1].reshape(-1) for s, n in enumerate(lengths)])
+    vmax = max(v.abs().max().item() for _, _, v in seqs)
+    for turn in range(2):
+        out = torch.full_like(q, float("nan"))
+        o.attn_decode_tma(q, kc.to(DEV), vc.to(DEV), table.to(DEV), items, out, page_size, len(lengths), H, KV, hs, scale,
+                          window or 0, work=work, scratch=scratch, status=status, max_rows=G)
+        assert status.item() == 0
+        assert not torch.isnan(out).any(), "every row was written"
+        assert (out.double().cpu() - want).abs().max().item() <= 2 ** -8 * vmax, turn
+
+
 @pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
 def test_split_decode_shares_its_scratch_between_shapes(tma):
     """One scratch buffer serves launches with different numbers of items and splits, as the engine's does
