@@ -50,8 +50,8 @@ class LLM:
         ``max_batch * ceil(max_seq_len / block_size)`` as in the reference
         (src/source/scheduler/kv_manager.cpp:23-25). ``max_num_batched_tokens``: prompt tokens per
         step, or "adaptive" for the reference's 512/1024/4096 rule. ``async_decode``: while a
-        decode step runs, the next one is already decided and launched (its tokens pass from step
-        to step on the device), so the host's work per step hides behind the GPU's."""
+        step runs, the next one is already decided and launched (the tokens it draws pass to the
+        next step on the device), so the host's work per step hides behind the GPU's."""
         self.dtype = _dtype_of(dtype)
         self.model = load_model(model, self.dtype, device) if isinstance(model, (str, bytes)) else model
         spec = self.model.spec
@@ -71,6 +71,8 @@ class LLM:
         self.sampler = Sampler(self.model.device, self.max_batch)
         self.use_cuda_graph = bool(use_cuda_graph)
         self.async_decode = bool(async_decode)
+        # steps are launched ahead only for models whose parts read nothing of a step on the host
+        self._run_ahead = self.async_decode and self.runner.graphs_available()
         self._inflight = None             # a launched step whose tokens have not been read: (items, wanted, handle)
         self._returned = 0
         self.stats = {"steps": 0, "decode_steps": 0, "graph_steps": 0, "ahead_steps": 0, "tokens_in": 0,
@@ -95,9 +97,9 @@ class LLM:
 
     def step(self) -> List[Sequence_]:
         """One scheduler step: decide, run the model, sample, book the tokens. With ``async_decode`` a
-        decode step is launched one call before its tokens are booked: the call launches the step after
-        it as well, when that can be decided without the tokens (``Scheduler.schedule_ahead``), and only
-        then waits for the tokens of the earlier one."""
+        step is launched one call before its tokens are booked: the call launches the step after it as
+        well, when that can be decided without the tokens (``Scheduler.schedule_ahead``), and only then
+        waits for the tokens of the earlier one."""
         try:
             pending = self._inflight
             self._inflight = None
@@ -106,12 +108,12 @@ class LLM:
                 if not items:
                     return []
                 pending = self._launch(items)
-            items, wanted, handle, graph_step = pending
-            if self.async_decode and graph_step:
+            items, wanted, handle = pending
+            if self._run_ahead:
                 ahead = self.scheduler.schedule_ahead(items)
                 if ahead is not None:
                     rows = {id(it.seq): r for r, it in enumerate(wanted)}
-                    self._inflight = self._launch(ahead, feed_rows=[rows[id(it.seq)] for it in ahead])
+                    self._inflight = self._launch(ahead, src_rows=rows)
                     self.stats["ahead_steps"] += 1
             sampled = self._resolve(wanted, handle)
         except Exception:
@@ -121,31 +123,37 @@ class LLM:
         self.stats["steps"] += 1
         return self.scheduler.update(items, sampled)
 
-    def _launch(self, items: List[ScheduledItem], feed_rows: Optional[List[int]] = None):
+    def _launch(self, items: List[ScheduledItem], src_rows: Optional[Dict[int, int]] = None):
         """Queue one step on the GPU (model, sampling, copy of the ids to the host) without waiting for it.
-        ``feed_rows``: the step's tokens are the ids that the step before it sampled (row numbers among its
-        wanted rows), still on the device."""
-        ahead = feed_rows is not None
-        entries = [StepEntry(it.seq.id, [0] if ahead else it.tokens, [it.count - 1] if it.want_logits else [])
+        Rows with ``fed`` set take their token from the ids that the step before this one sampled, which
+        are still on the device: ``src_rows`` maps ``id(request)`` to its row among that step's wanted rows."""
+        entries = [StepEntry(it.seq.id, [0] if it.fed else it.tokens, [it.count - 1] if it.want_logits else [])
                    for it in items]
+        feed = None
+        if any(it.fed for it in items):
+            dst, src, row = [], [], 0
+            for it in items:
+                if it.fed:
+                    dst.append(row)
+                    src.append(src_rows[id(it.seq)])
+                row += it.count
+            feed = (self.sampler.last_ids(), dst, src)
         pure_decode = all(it.count == 1 and it.want_logits for it in items)
         if pure_decode:
             self.stats["decode_steps"] += 1
-        graph_step = pure_decode and self.use_cuda_graph and self.runner.graphs_available()
-        if graph_step:
-            feed = (self.sampler.last_ids(), feed_rows) if ahead else None
+        if pure_decode and self.use_cuda_graph and self.runner.graphs_available():
             logits = self.runner.step_decode_graph(entries, feed=feed)
             self.stats["graph_steps"] += 1
         else:
-            logits = self.runner.step(entries)
+            logits = self.runner.step(entries, feed=feed)
         self.stats["tokens_in"] += sum(it.count for it in items)
         wanted = [it for it in items if it.want_logits]
         if not wanted:
-            return items, wanted, None, False
-        # the index of the output token keys the draw; a step launched ahead draws the one after the unread token
-        rows = [(it.seq.params, it.seq.seed, len(it.seq.outputs) + (1 if ahead else 0)) for it in wanted]
+            return items, wanted, None
+        # the index of the output token keys the draw; a fed row draws the one after the unread token
+        rows = [(it.seq.params, it.seq.seed, len(it.seq.outputs) + (1 if it.fed else 0)) for it in wanted]
         handle = self.sampler.fetch(self.sampler.sample(logits, rows), status=self.runner.status)
-        return items, wanted, handle, graph_step
+        return items, wanted, handle
 
     def _resolve(self, wanted: List[ScheduledItem], handle) -> Dict[Hashable, int]:
         if handle is None:

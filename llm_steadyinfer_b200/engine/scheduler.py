@@ -88,6 +88,7 @@ class ScheduledItem:
     start: int                         # first token position of the portion
     count: int                         # tokens in the portion
     want_logits: bool                  # the portion reaches the end of what is known
+    fed: bool = False                  # a decode row whose token the step before it draws: not on the host yet
 
     @property
     def tokens(self) -> List[int]:
@@ -176,42 +177,62 @@ class Scheduler:
         decoding = {id(it.seq) for it in items}
         pending = [s for s in self.running if s.state is SeqState.RUNNING and id(s) not in decoding
                    and not s.prefill_done]
-        if pending:
-            self._move_budget(len(decoding))
-            taken = 0
-            for seq in pending:
-                if taken >= self.token_budget:
-                    break
-                remaining = seq.num_tokens - seq.num_computed
-                take = min(remaining, self.token_budget - taken)
-                items.append(ScheduledItem(seq, seq.num_computed, take, take == remaining))
-                taken += take
+        self._portions(items, pending, {})
         return items
 
     def schedule_ahead(self, inflight: Sequence[ScheduledItem]) -> Optional[List[ScheduledItem]]:
-        """The decode step that follows ``inflight`` (a step of decode rows only, launched but not read
-        yet), decided before its tokens are known: every request of it that will not have reached its
-        length takes one more token. None when that cannot be decided blind: a request waits for
-        admission, a row is no decode row, or a page is missing (making room is left to ``schedule``,
-        after the tokens have arrived). A request that the unread token ends (end of sequence) gets a row
-        too; ``update`` drops it."""
-        if self.waiting:
-            return None
+        """The step that follows ``inflight`` (launched, its tokens not read yet), decided before those
+        tokens are known. Every request whose logits the step in flight takes will have one more token,
+        unless that token is its last by length: it gets a decode row whose token is still on the device
+        (``ScheduledItem.fed``). Prompt portions go on where the step in flight leaves them, and waiting
+        requests are admitted, as ``schedule`` would do it. None when a decode row lacks a page: making
+        room is left to ``schedule``, after the tokens have arrived. A request that the unread token
+        ends (end of sequence) has a row all the same; ``update`` drops it."""
+        self._admit()
+        flying = {id(it.seq): it for it in inflight}
         items: List[ScheduledItem] = []
-        for it in inflight:
-            seq = it.seq
-            if it.count != 1 or not it.want_logits or seq.state is not SeqState.RUNNING:
-                return None
-            if len(seq.outputs) + 1 >= seq.max_gen:
-                continue                                  # ends by length with the unread token
-            if not self.cache.can_grow(seq.id, it.start + 2):
+        pending: List[Sequence_] = []
+        for seq in self.running:
+            if seq.state is not SeqState.RUNNING:
+                continue
+            it = flying.get(id(seq))
+            computed = it.start + it.count if it is not None else seq.num_computed
+            unread = it is not None and it.want_logits
+            if unread:
+                if len(seq.outputs) + 1 >= seq.max_gen:
+                    continue                              # ends by length with the unread token
+                row = ScheduledItem(seq, computed, 1, True, fed=True)
+            elif computed >= seq.num_tokens - 1 and seq.outputs:
+                row = ScheduledItem(seq, computed, 1, True)      # a decode row whose token is known
+            else:
+                pending.append(seq)
+                continue
+            if not self.cache.can_grow(seq.id, row.start + 1):
                 return None                               # pages taken for earlier rows stay with their requests
-            self.cache.grow(seq.id, it.start + 2)
-            items.append(ScheduledItem(seq, it.start + 1, 1, True))
+            self.cache.grow(seq.id, row.start + 1)
+            items.append(row)
+        self._portions(items, pending, {id(s): flying[id(s)].start + flying[id(s)].count
+                                        for s in pending if id(s) in flying})
         if not items:
             return None
         self.num_steps += 1
         return items
+
+    def _portions(self, items: List[ScheduledItem], pending: List[Sequence_], computed: Dict[int, int]) -> None:
+        """Prompt portions in admission order under the token budget, behind the decode rows in ``items``.
+        ``computed``: where a request's cache will stand when the step runs, if not at ``num_computed``."""
+        if not pending:
+            return
+        self._move_budget(len(items))
+        taken = 0
+        for seq in pending:
+            if taken >= self.token_budget:
+                break
+            start = computed.get(id(seq), seq.num_computed)
+            remaining = seq.num_tokens - start
+            take = min(remaining, self.token_budget - taken)
+            items.append(ScheduledItem(seq, start, take, take == remaining))
+            taken += take
 
     def _move_budget(self, decode_backlog: int) -> None:
         if not self.adaptive:

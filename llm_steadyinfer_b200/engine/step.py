@@ -188,10 +188,14 @@ class ModelRunner:
         self._generation += 1
 
     # ---- the step ----------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], feed=None) -> Optional[torch.Tensor]:
         """Run one batch; returns fp32 logits [wanted rows, vocab] (a view into scratch that the
-        next step overwrites) or None when nothing is wanted."""
+        next step overwrites) or None when nothing is wanted. ``feed = (ids, dst, src)``: token row
+        ``dst[i]`` of the batch is not known on the host yet (its entry holds a placeholder) and is
+        taken on the device from ``ids[src[i]]`` (int32 tensor, lists)."""
         ctx = self._prepare(entries)
+        if feed is not None:
+            self._feed_tokens(ctx, feed)
         self.storage.zero_new_slots()
         caches = self.storage.layer_views(self._tables)
         before = ops.launch_count()
@@ -200,6 +204,17 @@ class ModelRunner:
         self.launches_last_step = ops.launch_count() - before
         self._commit(entries)
         return logits
+
+    def _feed_tokens(self, ctx, feed) -> None:
+        ids, dst, src = feed
+        n = len(dst)
+        if list(dst) == list(range(n)):                                  # the first n rows: one gather into place
+            idx = self.upload_ints("token_feed", np.asarray(src, dtype=np.int32), capacity=self.max_requests)
+            torch.index_select(ids, 0, idx, out=ctx.tokens[:n])
+            return
+        both = self.upload_ints("token_feed_some", np.asarray(list(src) + list(dst), dtype=np.int32),
+                                capacity=2 * self.max_requests)
+        ctx.tokens.index_copy_(0, both[n:].to(torch.int64), torch.index_select(ids, 0, both[:n]))
 
     def _commit(self, entries) -> None:
         for e, new_len in zip(entries, self._new_lengths):
@@ -212,8 +227,7 @@ class ModelRunner:
     def step_decode_graph(self, entries: Sequence[StepEntry], feed=None) -> torch.Tensor:
         """A pure decode step (one token and one wanted row per entry) through a CUDA graph.
         The first step of a shape runs directly and is then captured; later ones are replays.
-        Returns logits [len(entries), vocab]. ``feed = (ids, rows)``: the token of entry i is not
-        known on the host yet and is taken on the device from ``ids[rows[i]]`` (int32 tensor, list)."""
+        Returns logits [len(entries), vocab]. ``feed = (ids, dst, src)`` as in ``step``."""
         S = len(entries)
         if not self.graphs_available():
             raise StepError("a part of this model cannot be captured into a graph; run the step directly")
@@ -226,9 +240,7 @@ class ModelRunner:
             raise StepError(f"{S} sequences exceed the limit of {self.max_requests}")
         ctx = self._prepare(entries, seq_cap=cap, width_cap=self.max_width)
         if feed is not None:
-            ids, rows = feed
-            idx = self.upload_ints("token_feed", np.asarray(rows, dtype=np.int32), capacity=self.max_requests)
-            torch.index_select(ids, 0, idx, out=ctx.tokens[:S])
+            self._feed_tokens(ctx, feed)
         self.storage.zero_new_slots()
         caches = self.storage.layer_views(self._tables)
         self.model.prepare(ctx, caches)

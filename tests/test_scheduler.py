@@ -186,9 +186,10 @@ def test_prefix_hits_skip_computed_pages():
 
 
 def test_decode_step_decided_ahead_of_its_tokens():
-    """``schedule_ahead``: the step after a decode step, decided before that step's tokens are known. It
-    holds the same requests one position further, leaves out a request that ends by length with the
-    unread token, and declines (None) while a request waits or when a page is missing."""
+    """``schedule_ahead``: the step after a step in flight, decided before that step's tokens are known. It
+    holds the same requests one position further (their tokens fed on the device), leaves out a request that
+    ends by length with the unread token, admits a waiting request with its prompt beside them, and declines
+    (None) when a page is missing."""
     s, cache = make(num_pages=8, page_size=4, max_seqs=3, budget=64, max_gen=6)
     a = s.add_request([1, 2, 3], SamplingParams(max_tokens=6))
     b = s.add_request([4, 5, 6, 7, 8], SamplingParams(max_tokens=2))
@@ -209,13 +210,46 @@ def test_decode_step_decided_ahead_of_its_tokens():
     assert seq_a.outputs[-2:] == [50, 52] and seq_a.num_computed == 5
     assert [q.id for q in s.finished] == [b]
     cache.check_invariant()
-    # a waiting request: the next step may admit it, which is not decided blind
+    assert all(it.fed for it in ahead)
+    # a waiting request is admitted blind as well: its prompt runs beside the row that is fed
     items = s.schedule()
     for it in items:
         cache.commit(it.seq.id, it.start + 1)
-    s.add_request([9] * 3)
-    assert s.schedule_ahead(items) is None
+    c = s.add_request([9] * 3)
+    ahead = s.schedule_ahead(items)
+    assert [(it.seq.id, it.start, it.count, it.want_logits, it.fed) for it in ahead] == \
+        [(a, 6, 1, True, True), (c, 0, 3, True, False)]
     s.update(items, {a: 53})
+    for it in ahead:
+        cache.commit(it.seq.id, it.start + it.count)
+    s.update(ahead, {a: 54, c: 60})
+    assert seq_a.outputs[-2:] == [53, 54] and next(q for q in s.running if q.id == c).outputs == [60]
+    cache.check_invariant()
+
+
+def test_prompt_portions_go_on_in_the_step_ahead():
+    """A prompt cut by the budget: the step ahead takes its next portion from where the step in flight leaves
+    it, and the portion that reaches the prompt's end asks for logits; the step after that feeds its token."""
+    s, cache = make(num_pages=16, page_size=4, max_seqs=2, budget=4, max_gen=4)
+    a = s.add_request(list(range(1, 11)), SamplingParams(max_tokens=4))
+    items = s.schedule()
+    assert [(it.start, it.count, it.want_logits) for it in items] == [(0, 4, False)]
+    cache.commit(a, 4)
+    ahead = s.schedule_ahead(items)
+    assert [(it.start, it.count, it.want_logits, it.fed) for it in ahead] == [(4, 4, False, False)]
+    s.update(items, {})
+    cache.commit(a, 8)
+    third = s.schedule_ahead(ahead)
+    assert [(it.start, it.count, it.want_logits, it.fed) for it in third] == [(8, 2, True, False)]
+    s.update(ahead, {})
+    cache.commit(a, 10)
+    fourth = s.schedule_ahead(third)
+    assert [(it.start, it.count, it.want_logits, it.fed) for it in fourth] == [(10, 1, True, True)]
+    s.update(third, {a: 77})
+    cache.commit(a, 11)
+    s.update(fourth, {a: 78})
+    assert s.running[0].outputs == [77, 78] and s.running[0].num_computed == 11
+    cache.check_invariant()
 
 
 def test_no_step_ahead_without_a_page():
@@ -251,7 +285,7 @@ def test_step_ahead_counts_pages_row_by_row():
     cache.check_invariant()
 
 
-@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("seed", range(12))
 def test_random_serving_with_and_without_steps_ahead(seed):
     """A stand-in model (the token of request r at output index i is a fixed function of both) under random
     arrivals, small pools, stop tokens and shared prefixes: with steps decided ahead where the scheduler allows
@@ -283,7 +317,7 @@ def test_random_serving_with_and_without_steps_ahead(seed):
                 for it in items:
                     cache.commit(it.seq.id, it.start + it.count)
             inflight = None
-            if ahead and items and all(it.count == 1 and it.want_logits for it in items):
+            if ahead and items:
                 nxt = s.schedule_ahead(items)
                 if nxt is not None:
                     for it in nxt:
