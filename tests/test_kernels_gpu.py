@@ -598,6 +598,57 @@ def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
           f"{gbs:.0f} GB/s of cache read")
 
 
+@pytest.mark.parametrize("lens", [[8192] * 8, [8192] + [512] * 7, [8192, 4096, 2048, 1024, 512, 256, 128, 64],
+                                  [8192] + [256] * 63], ids=["even", "one_long", "halving", "one_long_of_64"])
+def test_attention_decode_shares_at_serving_size(lens):
+    """Sequences of unequal length at the Llama-3.1-8B head layout: shares of equal length (``split_work``)
+    against the same number of splits for every sequence; the same outputs, and the time of both (printed)."""
+    o = ops()
+    H, KV, hs, page_size = 32, 8, 128, 16
+    batch = len(lens)
+    g = torch.Generator(device=DEV).manual_seed(11)
+    blocks = [-(-n // page_size) for n in lens]
+    num_pages = sum(blocks)
+    kc = torch.randn(num_pages, KV, page_size, hs, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    vc = torch.randn(num_pages, KV, page_size, hs, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    perm = torch.randperm(num_pages, generator=g, device=DEV).to(torch.int32)
+    table = torch.full((batch, max(blocks)), -1, dtype=torch.int32, device=DEV)
+    at = 0
+    for s_, nb in enumerate(blocks):
+        table[s_, :nb] = perm[at:at + nb]
+        at += nb
+    q = torch.randn(batch, H * hs, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    items = torch.tensor([(s_, s_, 1, n - 1) for s_, n in enumerate(lens)], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    nsplit = max(1, min(32, 296 // (batch * KV)))
+    scratch = torch.zeros(max(1, o.attn_decode_tma_scratch_floats(batch, H, KV, hs, nsplit)), device=DEV)
+    entries = 296 // KV + batch
+    work = torch.tensor(o.split_work([-(-n // 64) for n in lens], 296 // KV, entries, 32, 2), dtype=torch.int32, device=DEV)
+    scratch2 = torch.zeros(o.attn_decode_tma_work_floats(entries, H, KV, hs), device=DEV)
+    outs, times = [], []
+    for kw in ({"nsplit": nsplit, "scratch": scratch if nsplit > 1 else None}, {"work": work, "scratch": scratch2}):
+        out = torch.empty_like(q)
+        run = lambda: o.attn_decode_tma(q, kc, vc, table, items, out, page_size, batch, H, KV, hs, scale, 0,
+                                        status=status, max_rows=H // KV, **kw)
+        for _ in range(3):
+            run()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(10):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+        outs.append(out)
+        times.append(a.elapsed_time(b) * 100)
+    assert status.item() == 0
+    assert (outs[0].float() - outs[1].float()).abs().max().item() <= 2 ** -8 * 4
+    mb = sum(lens) * KV * hs * 2 * 2 / 1e6
+    print(f"attn_decode tma {batch} sequences, {sum(lens)} tokens ({mb:.0f} MB): {nsplit} splits each {times[0]:.1f} us, "
+          f"shares of equal length {times[1]:.1f} us ({mb / times[1]:.2f} TB/s)")
+
+
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 1000, 96), (3, 513, 320), (8, 200, 1336), (16, 64, 16), (9, 37, 8), (5, 4096, 4096)])
 def test_gemm_skinny(M, N, K, out_dtype):
