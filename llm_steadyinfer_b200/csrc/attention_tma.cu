@@ -43,7 +43,7 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
 template <int NH, int MT, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(160)
 attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kmap,
-                       const __grid_constant__ CUtensorMap vmap, int log2_page, const int4* __restrict__ work) {
+                       const __grid_constant__ CUtensorMap vmap, int log2_page, const int4* __restrict__ work, int trigger) {
   constexpr int NWARPS = 4, THREADS = 128, BLOCK_N = 64, ROWS = 16 * MT, HS_PAD = NH * 64;   // consumer warps/threads
   constexpr int KT = HS_PAD / 16, DT = HS_PAD / 8;
   constexpr int TILE = NH * BLOCK_N * 64;             // elements of one K (or V) tile
@@ -57,7 +57,9 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   bf16* Vs = Ks + STAGES * TILE;
   bf16* Qs = Vs + STAGES * TILE;                     // [NH][ROWS][64]
 
-  pdl_prologue();
+  if (trigger) pdl_trigger();
+  // Until pdl_wait() below nothing is read that the kernel before this one writes (the queries and the
+  // newest keys and values): the work list, the items and the block table were copied in before it began.
   // Which share of which item: with a work list, entry blockIdx.x = (item, split, splits of the item, first
   // partial-result slot of the item), so that long sequences are cut into more shares than short ones;
   // without one, item blockIdx.x and split blockIdx.z of p.nsplit.
@@ -105,6 +107,7 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   };
   if (ntiles > 0 && (kv_end - kv_begin) % BLOCK_N != 0) clear_stage((ntiles - 1) % STAGES);
   if (ntiles > 0 && kv_begin + page_rows <= kv_lo) clear_stage(0);
+  pdl_wait();
   // query rows: tile row r is token r / G, head g*G + r % G
   for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += blockDim.x) {
     const int row = id / (HS_PAD / 8), c = id % (HS_PAD / 8);
@@ -524,7 +527,8 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
     if (e != cudaSuccess) return (int)e;
   }
   const dim3 grid = work ? dim3(num_work, p.KV, 1) : dim3(num_items, p.KV, p.nsplit);
-  si_launch(k, grid, dim3(160), smem, stream, p, km, vm, log2_page, work);
+  si_launch(k, grid, dim3(160), smem, stream, p, km, vm, log2_page, work,
+            si_pdl_trigger_mode((long long)grid.x * grid.y * grid.z, 296) == 1 ? 1 : 0);
   return si_last_error();
 }
 

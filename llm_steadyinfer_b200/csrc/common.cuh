@@ -95,6 +95,33 @@ __device__ __forceinline__ void l2_prefetch_share(const void* base, long long by
     asm volatile("prefetch.global.L2 [%0];\n" :: "l"(reinterpret_cast<const char*>(base) + c * LINE) : "memory");
 }
 
+// The two halves of pdl_prologue() for kernels that place them themselves. A small kernel (a norm, the
+// position encoding) calls pdl_trigger() at its start: the kernel after it may then become resident and do
+// whatever does not depend on this one (set-up, the first loads of its weights) before its own pdl_wait().
+// Kernels of more than one wave do not trigger: blocks of the next kernel that sit waiting would take the
+// places of their own later blocks.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// SI_PDL_TRIGGER: 0 no kernel triggers; 1 (default) the small kernels; 2 also every kernel of one wave of
+// blocks, at its start; 3 also kernels of several waves, once their main loop is done.
+static inline int si_pdl_trigger_level() {
+  static int level = -1;
+  if (level < 0) {
+    const char* e = getenv("SI_PDL_TRIGGER");
+    level = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 1;
+  }
+  return level;
+}
+static inline bool si_pdl_trigger_enabled() { return si_pdl_trigger_level() >= 1; }
+// What a kernel of `blocks` blocks, `slots` of which run at once, is told: 0 do not trigger, 1 at the
+// start, 2 after the main loop.
+static inline int si_pdl_trigger_mode(long long blocks, long long slots) {
+  const int level = si_pdl_trigger_level();
+  if (blocks <= slots) return level >= 2 ? 1 : 0;
+  return level >= 3 ? 2 : 0;
+}
+
 static inline bool si_pdl_enabled() {
   static int on = -1;
   if (on < 0) {

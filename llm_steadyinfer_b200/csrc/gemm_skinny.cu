@@ -48,23 +48,51 @@ __device__ __forceinline__ uint4 ld_cached(const bf16* p) {      // x: small, sh
 template <int MT, int WARPS, int UNROLL, typename TO, bool SWIGLU = false>
 __global__ void __launch_bounds__(WARPS * 32, 512 / (WARPS * 32))
 gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W, long long ldw,
-                   TO* __restrict__ out, long long ldo, int M, int N, int K) {
+                   TO* __restrict__ out, long long ldo, int M, int N, int K, int trigger) {
   __shared__ float red[WARPS][MT][32][4];
-  pdl_prologue();
+  if (trigger == 1) pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const bf16* w0 = W + (size_t)(n0 + g < N ? n0 + g : 0) * ldw + t * 8;
   const bf16* w1 = W + (size_t)(n0 + g + 8 < N ? n0 + g + 8 : 0) * ldw + t * 8;
-  const bf16* xr[MT];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) xr[mt] = x + (size_t)(mt * 8 + g < M ? mt * 8 + g : 0) * ldx + t * 8;
   float acc[MT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
 
   const int full = K >> 5;                      // whole 32-wide chunks
   int c = warp;
+  const bf16* xr[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) xr[mt] = x + (size_t)(mt * 8 + g < M ? mt * 8 + g : 0) * ldx + t * 8;
+  // The weights do not depend on the kernel before this one: the first round of their loads is in flight
+  // before this kernel waits for that kernel's results (x).
+  if (c + (UNROLL - 1) * WARPS < full) {
+    uint4 a_lo[UNROLL], a_hi[UNROLL], xb[UNROLL][MT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (c + u * WARPS) * 32;
+      a_lo[u] = ld_stream(w0 + k);
+      a_hi[u] = ld_stream(w1 + k);
+    }
+    pdl_wait();
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (c + u * WARPS) * 32;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) xb[u][mt] = ld_cached(xr[mt] + k);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma16816(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, xb[u][mt].x, xb[u][mt].y);
+        mma16816(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, xb[u][mt].z, xb[u][mt].w);
+      }
+    c += WARPS * UNROLL;
+  } else {
+    pdl_wait();
+  }
   for (; c + (UNROLL - 1) * WARPS < full; c += WARPS * UNROLL) {
     uint4 a_lo[UNROLL], a_hi[UNROLL], xb[UNROLL][MT];
 #pragma unroll
@@ -83,6 +111,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __rest
         mma16816(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, xb[u][mt].z, xb[u][mt].w);
       }
   }
+  if (trigger == 2) pdl_trigger();
   // what is left: whole chunks one at a time, then the part of a chunk (K is a multiple of 8).
   // Lanes past the end load nothing and feed zeros; every lane of the warp issues the same mma
   // (mma.sync must not sit in a divergent branch).
@@ -149,11 +178,11 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
   if (out_dtype == SI_BF16) {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K);
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
   } else {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K);
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
   }
   return si_last_error();
 }
@@ -169,7 +198,7 @@ SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W,
   const unsigned blocks = (unsigned)(F / 8);
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K);
-  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K);
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 296));
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 296));
   return si_last_error();
 }

@@ -49,8 +49,9 @@ template <typename TX, typename TW, int CHUNKS>
 __global__ void __launch_bounds__(512) add_rmsnorm_vec_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
                                        const int* __restrict__ rows, const TW* __restrict__ weight,
                                        TX* __restrict__ out, int hidden, float eps, int num_rows,
-                                       const void* ahead, long long ahead_bytes) {
+                                       const void* ahead, long long ahead_bytes, int trigger) {
   __shared__ float scratch[33];
+  if (trigger) pdl_trigger();
   if ((int)blockIdx.x >= num_rows) {              // blocks behind the rows only fetch ahead
     l2_prefetch_share(ahead, ahead_bytes, blockIdx.x - num_rows, gridDim.x - num_rows);
     return;
@@ -143,11 +144,12 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
     const int per = (nchunks + threads - 1) / threads;
     // with something to fetch ahead: enough further blocks that every SM takes part
     if (ahead && ahead_bytes < 4096) ahead = nullptr;
+    const int trigger = si_pdl_trigger_enabled() && num_rows <= 64;      // a launch of one wave
     const int extra = ahead ? max(0, 148 - num_rows) + 148 : 0;
     const dim3 grid(num_rows + extra);
-    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes);
-    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes);
-    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes);
+    if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
+    else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
+    else si_launch(add_rmsnorm_vec_kernel<TX, TW, 4>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
     return si_last_error();
   }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);

@@ -92,9 +92,10 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, long l
                                          const int* __restrict__ block_table, int table_width,
                                          __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                          int num_pages, int page_size, int num_seqs, int H, int KV, int hs,
-                                         int hpb, int* status) {
+                                         int hpb, int* status, int trigger) {
   typedef __nv_bfloat16 T;
-  pdl_prologue();
+  if (trigger) pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int seq = row_seq[t];
@@ -199,7 +200,8 @@ SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const
     if (vthreads < cpr) vthreads = ((cpr + 31) / 32) * 32;
     si_launch(rope_kv_write_vec_kernel, grid, dim3(vthreads), 0, stream,
               (__nv_bfloat16*)qkv, row_stride, positions, row_seq, inv_freq, rot_dim, block_table, table_width,
-              (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, hpb, status);
+              (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, H, KV, hs, hpb, status,
+              (int)(si_pdl_trigger_enabled() && num_tokens <= 64));
     return si_last_error();
   }
   if (dtype == SI_BF16)
