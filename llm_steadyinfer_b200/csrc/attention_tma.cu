@@ -58,7 +58,7 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   bf16* Qs = Vs + STAGES * TILE;                     // [NH][ROWS][64]
 
   if (trigger) pdl_trigger();
-  // Until pdl_wait() below nothing is read that the kernel before this one writes (the queries and the
+  // Until its pdl_wait() below no thread reads what the kernel before this one writes (the queries and the
   // newest keys and values): the work list, the items and the block table were copied in before it began.
   // Which share of which item: with a work list, entry blockIdx.x = (item, split, splits of the item, first
   // partial-result slot of the item), so that long sequences are cut into more shares than short ones;
@@ -107,18 +107,21 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
   };
   if (ntiles > 0 && (kv_end - kv_begin) % BLOCK_N != 0) clear_stage((ntiles - 1) % STAGES);
   if (ntiles > 0 && kv_begin + page_rows <= kv_lo) clear_stage(0);
-  pdl_wait();
-  // query rows: tile row r is token r / G, head g*G + r % G
-  for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += blockDim.x) {
-    const int row = id / (HS_PAD / 8), c = id % (HS_PAD / 8);
-    const int tok = row / p.G, hh = row - tok * p.G;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tok < item.ntok && c * 8 < p.hs)
-      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
-    *reinterpret_cast<uint4*>(half_tile_ptr<ROWS>(Qs, row, c)) = v;
-  }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  __syncthreads();
+  __syncthreads();                              // the barriers stand, the cleared rows are there for the copies
+  if (warp < NWARPS) {
+    pdl_wait();
+    // query rows: tile row r is token r / G, head g*G + r % G
+    for (int id = threadIdx.x; id < ROWS * (HS_PAD / 8); id += THREADS) {
+      const int row = id / (HS_PAD / 8), c = id % (HS_PAD / 8);
+      const int tok = row / p.G, hh = row - tok * p.G;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (tok < item.ntok && c * 8 < p.hs)
+        v = *reinterpret_cast<const uint4*>(p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(g * p.G + hh) * p.hs + c * 8);
+      *reinterpret_cast<uint4*>(half_tile_ptr<ROWS>(Qs, row, c)) = v;
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+  }
 
   if (warp == NWARPS) {
     // ---- producer warp: lane l fetches box (page l / (2 NH), half (l / 2) % NH, K or V) of each tile
@@ -135,7 +138,11 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
       return slot < p.table_width ? __ldg(table + slot) : -1;
     };
     int ahead0 = lookup(0), ahead1 = lookup(1), ahead2 = lookup(2);
+    // Tiles that end before the item's first position hold nothing that the kernel before this one writes
+    // (it stores the keys and values of the step's own tokens): their copies start before this kernel waits.
+    bool waited = false;
     for (int t = 0; t < ntiles; ++t) {
+      if (!waited && kv_begin + (t + 1) * BLOCK_N > item.pos0) { pdl_wait(); waited = true; }
       const int stage = t % STAGES;
       int page = ahead0;
       ahead0 = ahead1; ahead1 = ahead2; ahead2 = lookup(t + 3);
