@@ -384,11 +384,11 @@ def split_work(tiles, budget: int, entries: int, max_splits: int = 128, min_tile
     (0: an empty item, which gets no entry). ``budget``: shares that run at the same time. With no more
     items than that, the shares are as short as ``budget`` shares in all allow (the smallest length L with
     sum(ceil(tiles / L)) <= budget): more would run in a second round, fewer would leave the longest item
-    to few blocks. With more items than that, L is the mean load of a share, so that a long item among
-    many short ones is still cut. No share is shorter than ``min_tiles``, no item has more than
-    ``max_splits``. Returns an int32 array [entries, 4] of (item, split, splits of the item, first slot
-    of the item), longest shares first, the rest filled with item -1: ``attn_decode_tma(work=...)``;
-    ``entries >= budget + len(tiles)`` always suffices."""
+    to few blocks. With more items than that the cut is chosen by an estimate of the time (see the code), so
+    that a long item among many short ones is still cut and the last blocks do not run alone. No share is shorter than ``min_tiles``, no item has more than ``max_splits``. Returns
+    an int32 array [entries, 4] of (item, split, splits of the item, first slot of the item), longest
+    shares first, the rest filled with item -1: ``attn_decode_tma(work=...)``. ``entries >= budget +
+    len(tiles)`` always suffices; more entries allow finer cuts when items outnumber the budget."""
     import numpy as np
     key = (tuple(tiles), budget, entries, max_splits, min_tiles)
     if _split_memo.get("key") == key:               # tile counts change once in 64 decode steps of a sequence
@@ -422,19 +422,39 @@ def _split_work(np, tiles, budget, entries, max_splits, min_tiles):
                 lo = mid + 1
         sp = splits_for(lo)
     else:
-        sp = splits_for(-(-int(tl.sum()) // max(budget, 1)))
+        # More items than shares that run at once. Blocks follow one another on the block slots; what counts is
+        # the longest chain on a slot (about ceil(shares / slots) shares of length L, at most load / slots + L),
+        # the time HBM needs for everything (reached with about four fifths of the slots busy), and what a
+        # share costs beside its tiles (about eight tiles' time for a full round of them: start, partial
+        # results, merge). The cut with the least of these wins among 1 to 32 cuts of the longest item, as far
+        # as the entries reach: many equal sequences stay whole, a few more sequences than slots are cut in
+        # four or five so that the last blocks do not run alone, a long one among many short ones is cut most.
+        load, slots, tmax = float(tl.sum()), float(max(budget, 1)), int(tl.max())
+        best = None
+        for k in (1, 2, 3, 4, 5, 6, 8, 12, 16, 32):
+            L = max(-(-tmax // k), min_tiles, 1)
+            cand = splits_for(L)
+            n = int(cand.sum())
+            if n > entries and best is not None:
+                break
+            longest = int((-(-tl // cand)).max())
+            chain = min(-(-n // int(slots)) * longest, load / slots + longest)
+            cost = max(chain, load / (0.8 * slots)) + 8.0 * n / slots
+            if best is None or cost < best[0]:
+                best = (cost, cand)
+            if L <= max(min_tiles, 1):
+                break
+        sp = best[1]
     if int(sp.sum()) > entries:
         raise ValueError(f"split_work: {int(sp.sum())} shares do not fit {entries} entries")
-    first = np.concatenate([[0], np.cumsum(sp)[:-1]])
+    first = np.cumsum(sp) - sp
     order = np.argsort(-(-(-tl // sp)), kind="stable")          # longest shares first: they start first
-    row = 0
-    for j in order:
-        n = int(sp[j])
-        out[row:row + n, 0] = live[j]
-        out[row:row + n, 1] = np.arange(n)
-        out[row:row + n, 2] = n
-        out[row:row + n, 3] = first[j]
-        row += n
+    so = sp[order]
+    total = int(so.sum())
+    out[:total, 0] = np.repeat(live[order], so)
+    out[:total, 1] = np.arange(total) - np.repeat(np.cumsum(so) - so, so)
+    out[:total, 2] = np.repeat(so, so)
+    out[:total, 3] = np.repeat(first[order], so)
     return out
 
 

@@ -139,8 +139,13 @@ class Attention(Mixer):
             for (_, _, n, pos0) in dec:
                 first = max(0, pos0 - self.window + 1) // 64 * 64 if self.window else 0
                 tiles.append(-(-(pos0 + n - first) // 64) if n > 0 else 0)
-            entries = TARGET_BLOCKS // self.KV + len(dec)
-            work = ops.split_work(tiles, TARGET_BLOCKS // self.KV, entries, MAX_SPLITS, MIN_TILES_PER_SPLIT)
+            # Entries: every item whole, the shares that run at once, and room for finer cuts when items outnumber
+            # those (entries without work are blocks that start and leave, so not more room than pays)
+            budget = TARGET_BLOCKS // self.KV
+            entries = budget + len(dec) + min(3 * len(dec), 2 * budget)
+            work = ops.split_work(tiles, budget, entries, MAX_SPLITS, MIN_TILES_PER_SPLIT)
+            if ctx.seq_cap is None:                    # shapes are free: only the entries with work
+                work = work[:max(1, int((work[:, 0] >= 0).sum()))]
             both = ctx.upload_ints(f"attn_dec_{self.H}_{self.KV}_{self.hs}_{self.window}",
                                    np.concatenate([np.asarray(dec, dtype=np.int32).reshape(-1), work.reshape(-1)]))
             plan["dec"] = both[:4 * len(dec)].view(-1, 4)

@@ -599,7 +599,7 @@ def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
 
 
 @pytest.mark.parametrize("lens", [[8192] * 8, [8192] + [512] * 7, [8192, 4096, 2048, 1024, 512, 256, 128, 64],
-                                  [8192] + [256] * 63], ids=["even", "one_long", "halving", "one_long_of_64"])
+                                  [8192] + [256] * 63, [8192] * 40], ids=["even", "one_long", "halving", "one_long_of_64", "forty"])
 def test_attention_decode_shares_at_serving_size(lens):
     """Sequences of unequal length at the Llama-3.1-8B head layout: shares of equal length (``split_work``)
     against the same number of splits for every sequence; the same outputs, and the time of both (printed)."""
@@ -623,7 +623,7 @@ def test_attention_decode_shares_at_serving_size(lens):
     scale = 1.0 / math.sqrt(hs)
     nsplit = max(1, min(32, 296 // (batch * KV)))
     scratch = torch.zeros(max(1, o.attn_decode_tma_scratch_floats(batch, H, KV, hs, nsplit)), device=DEV)
-    entries = 296 // KV + batch
+    entries = 296 // KV + 4 * batch
     work = torch.tensor(o.split_work([-(-n // 64) for n in lens], 296 // KV, entries, 32, 2), dtype=torch.int32, device=DEV)
     scratch2 = torch.zeros(o.attn_decode_tma_work_floats(entries, H, KV, hs), device=DEV)
     outs, times = [], []

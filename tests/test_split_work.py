@@ -53,3 +53,18 @@ def test_a_long_item_among_short_ones_is_cut_most():
 def test_no_share_is_shorter_than_the_least_and_no_item_has_more_than_the_most():
     sp, _ = _shares(split_work([3, 1, 1000], 200, 203, 32, 2))
     assert sp[0] <= 2 and sp[1] == 1 and sp[2] == 32
+
+
+def test_more_items_than_slots():
+    # many equal sequences stay whole: HBM is busy either way, and every share has its cost
+    sp, live = _shares(split_work([128] * 64, 37, 37 + 256, 32, 2))
+    assert set(sp.values()) == {1}
+    sp, _ = _shares(split_work([16] * 100, 37, 37 + 400, 32, 2))
+    assert set(sp.values()) == {1}
+    # a few more sequences than slots: whole, the last three blocks of each head would run alone for as long
+    # as all the others took; cut, the chains on the slots are about equal
+    sp, live = _shares(split_work([128] * 40, 37, 37 + 160, 32, 2))
+    assert len(set(sp.values())) == 1 and 3 <= sp[0] <= 5 and len(live) <= 37 + 160
+    # with no room for finer cuts the items stay whole
+    sp, _ = _shares(split_work([128] * 40, 37, 37 + 40, 32, 2))
+    assert set(sp.values()) == {1}
