@@ -477,14 +477,12 @@ attn_decode_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap k
         }
     }
     const float L = L_s[r];
-    const float inv = L > 0.f ? 1.f / L : 0.f;
     const int tok = r / p.G, hh = r - tok * p.G;
     bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(g * p.G + hh) * p.hs + d;
     dst[0] = __float2bfloat16_rn(L > 0.f ? acc.x / L : 0.f);
     dst[1] = __float2bfloat16_rn(L > 0.f ? acc.y / L : 0.f);
     dst[2] = __float2bfloat16_rn(L > 0.f ? acc.z / L : 0.f);
     dst[3] = __float2bfloat16_rn(L > 0.f ? acc.w / L : 0.f);
-    (void)inv;
   }
   if (threadIdx.x == 0) p.counters[item_idx * p.KV + g] = 0;      // ready for the next launch
 }
