@@ -30,19 +30,30 @@ def _dt(t: torch.Tensor) -> int:
     raise KernelError(f"kernels take float32 or bfloat16 tensors, found {t.dtype}")
 
 
-def _ptr(t: Optional[torch.Tensor]) -> _c_p:
-    return _c_p(0 if t is None else t.data_ptr())
+def _ptr(t: Optional[torch.Tensor]):
+    """The tensor's address as ctypes takes it for a ``void*`` argument (an int, or None for a null pointer)."""
+    return None if t is None else t.data_ptr()
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
-def _stream() -> _c_p:
+_device_index: Optional[int] = None
+
+
+def set_device(index: Optional[int]) -> None:
+    """The device whose current stream the kernels are launched on, when the caller knows it (an engine that
+    lives on one device); None: ask torch for the current device at every call."""
+    global _device_index
+    _device_index = index
+
+
+def _stream():
     """The current stream's handle. Every kernel call asks for it, so it comes from the one C call that
     returns the handle (torch.cuda.current_stream() builds a Python object around it at ten times the cost)."""
     if _raw_stream is not None:
-        return _c_p(_raw_stream(torch.cuda.current_device()))
-    return _c_p(torch.cuda.current_stream().cuda_stream)
+        return _raw_stream(_device_index if _device_index is not None else torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _need(cond: bool, msg: str) -> None:

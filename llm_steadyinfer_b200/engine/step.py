@@ -114,6 +114,7 @@ class ModelRunner:
             raise KernelError("the engine runs on a CUDA device only; there is no CPU path")
         self.model = model
         self.device = model.device
+        ops.set_device(self.device.index)        # the engine lives on one device: kernels ask for its stream
         build.prebuild(model.kernel_files(page_size))       # together now, not one by one inside the first step
         spec = model.spec
         # Caches and state belong to the places of the run order: a layer that runs twice keeps a
@@ -140,6 +141,7 @@ class ModelRunner:
         self.max_width = max(1, min(num_pages, -(-self.max_seq_len // page_size)))
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}
         self._uploads: Dict[str, _PinnedRing] = {}
         G = max(1, len(self.manager.groups))
         T, S, W = self.max_step_tokens, max_requests, self.max_width
@@ -153,6 +155,11 @@ class ModelRunner:
 
     # ---- scratch -----------------------------------------------------------------------
     def workspace(self, key: str, shape, dtype) -> torch.Tensor:
+        # the same (key, shape) is asked for at every layer of every step: the views are kept
+        shape = tuple(shape)
+        view = self._views.get((key, shape, dtype))
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -163,8 +170,13 @@ class ModelRunner:
                 raise StepError(f"scratch {key!r} would have to grow during graph capture")
             t = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._scratch[k] = t
+            self._views = {vk: v for vk, v in self._views.items() if (vk[0], vk[2]) != k}
             self._drop_graphs()
-        return t[:n].view(*shape)
+        view = t[:n].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[(key, shape, dtype)] = view
+        return view
 
     def upload_ints(self, key: str, values: np.ndarray, capacity: Optional[int] = None) -> torch.Tensor:
         values = np.ascontiguousarray(values, dtype=np.int32).reshape(-1)
