@@ -4,12 +4,13 @@ import pytest
 
 from llm_steadyinfer_b200.cache import CacheLayout, CacheManager
 from llm_steadyinfer_b200.engine.scheduler import RequestRejected, Scheduler, SeqState
-from llm_steadyinfer_b200.parts.base import CacheNeed
+from llm_steadyinfer_b200.parts.base import CacheNeed, StateNeed
 from llm_steadyinfer_b200.sampling import SamplingParams
 
 
-def make(num_pages=64, page_size=4, max_seqs=4, budget=16, max_len=256, max_gen=8, prefix=False, eos=()):
-    cache = CacheManager(CacheLayout([CacheNeed(1, 8, None)], [None]), page_size, num_pages, max_seqs, prefix)
+def make(num_pages=64, page_size=4, max_seqs=4, budget=16, max_len=256, max_gen=8, prefix=False, eos=(), layout=None):
+    layout = layout or CacheLayout([CacheNeed(1, 8, None)], [None])
+    cache = CacheManager(layout, page_size, num_pages, max_seqs, prefix)
     return Scheduler(cache, max_seqs, max_len, max_gen, token_budget=budget, eos_token_ids=eos), cache
 
 
@@ -285,8 +286,9 @@ def test_step_ahead_counts_pages_row_by_row():
     cache.check_invariant()
 
 
+@pytest.mark.parametrize("windowed", [False, True], ids=["one_group", "window_and_state"])
 @pytest.mark.parametrize("seed", range(12))
-def test_random_serving_with_and_without_steps_ahead(seed):
+def test_random_serving_with_and_without_steps_ahead(seed, windowed):
     """A stand-in model (the token of request r at output index i is a fixed function of both) under random
     arrivals, small pools, stop tokens and shared prefixes: with steps decided ahead where the scheduler allows
     it and without, every request ends with the same tokens and reason, and the cache keeps its books."""
@@ -297,8 +299,12 @@ def test_random_serving_with_and_without_steps_ahead(seed):
 
     def serve(ahead):
         rng = random.Random(seed)
+        # windowed: a layer with all keys, a layer with a window of 6 (its pages come back while requests
+        # run, and nothing of a preempted request can be kept) and a layer with state of fixed size
+        layout = CacheLayout([CacheNeed(1, 8, None), CacheNeed(1, 8, 6), None],
+                             [None, None, StateNeed((3,))]) if windowed else None
         s, cache = make(num_pages=rng.choice([12, 20, 40]), page_size=4, max_seqs=4, budget=rng.choice([8, 32]),
-                        max_len=64, max_gen=12, prefix=True, eos=(5, 6, 7))
+                        max_len=64, max_gen=12, prefix=True, eos=(5, 6, 7), layout=layout)
         shared = [11, 12, 13, 14, 15, 16, 17, 18]
         todo = []
         for i in range(16):
