@@ -189,7 +189,6 @@ def main(argv: Optional[List[str]] = None) -> int:
     args = parse_args(argv)
     import torch
     from llm_steadyinfer_b200 import LLM
-    from llm_steadyinfer_b200.config import load_config
     from llm_steadyinfer_b200.models import Model
     from llm_steadyinfer_b200.weights import init_random, load_model
 

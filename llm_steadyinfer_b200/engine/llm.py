@@ -16,7 +16,7 @@ import torch
 
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_model
-from .scheduler import ScheduledItem, Scheduler, SeqState, Sequence_
+from .scheduler import ScheduledItem, Scheduler, Sequence_
 from .step import ModelRunner, StepEntry
 
 

@@ -4,7 +4,7 @@ cache and kernels are the engine's.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

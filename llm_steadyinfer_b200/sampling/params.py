@@ -3,8 +3,8 @@
 tokenizer's end-of-sentence id (src/source/scheduler/scheduler.cpp:655-694)."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Optional, Tuple
 
 
 @dataclass(frozen=True)

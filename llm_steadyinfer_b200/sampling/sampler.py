@@ -3,7 +3,7 @@ top-p, seed and the index of the output token travel in one pinned buffer; token
 back in one device-to-host copy."""
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import numpy as np
 import torch
