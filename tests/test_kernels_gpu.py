@@ -551,7 +551,7 @@ def test_split_decode_shares_its_scratch_between_shapes(tma):
         assert (out.double().cpu() - want).abs().max().item() <= 2 ** -8 * vmax, (which, nsplit)
 
 
-@pytest.mark.parametrize("batch,ctx,nsplit", [(8, 8192, 4), (64, 2048, 1)])
+@pytest.mark.parametrize("batch,ctx,nsplit", [(8, 8192, 4), (64, 2048, 1), (1, 8192, 32)])
 @pytest.mark.parametrize("tma", [False, True], ids=["cp_async", "tma"])
 def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
     """Decode rows at the Llama-3.1-8B head layout over long contexts (a cache larger than L2):
