@@ -469,10 +469,17 @@ def _split_work(np, tiles, budget, entries, max_splits, min_tiles):
     return out
 
 
+_work_floats_memo: dict = {}
+
+
 def attn_decode_tma_work_floats(slots: int, H: int, KV: int, hs: int) -> int:
-    lib = build.load("attention_tma")
-    lib.si_attn_decode_tma_work_floats.restype = _c_llr
-    return lib.si_attn_decode_tma_work_floats(_c_int(slots), _c_int(H), _c_int(KV), _c_int(hs))
+    key = (slots, H, KV, hs)
+    n = _work_floats_memo.get(key)
+    if n is None:
+        lib = build.load("attention_tma")
+        lib.si_attn_decode_tma_work_floats.restype = _c_llr
+        n = _work_floats_memo[key] = lib.si_attn_decode_tma_work_floats(_c_int(slots), _c_int(H), _c_int(KV), _c_int(hs))
+    return n
 
 
 def attn_decode_tma(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int,
@@ -522,20 +529,22 @@ def gemm_skinny_ok(a, w, out) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(a, w, out) -> None:
-    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weights stream through mma.sync fragments."""
+def gemm_skinny(a, w, out, checked: bool = False) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weights stream through mma.sync fragments.
+    ``checked``: the caller has just asked ``gemm_skinny_ok`` for these tensors."""
     _cuda(a, w, out)
     M, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (M, N), "gemm_skinny: shapes")
-    _need(gemm_skinny_ok(a, w, out), "gemm_skinny: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    _need(checked or gemm_skinny_ok(a, w, out),
+          "gemm_skinny: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
     f = _fn("gemm_skinny", "si_gemm_skinny",
             [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _dt(out), M, N, K, _stream()),
            f"gemm_skinny(M={M}, N={N}, K={K})")
 
 
-def gemm_skinny_swiglu(a, w, out) -> None:
+def gemm_skinny_swiglu(a, w, out, checked: bool = False) -> None:
     """out[M,F] = silu(gate) * up of a[M,K] @ w[2F,K]^T for M <= 16, the rows of w interleaved in groups of 8
     (8 gates, their 8 ups, ...): the activation runs in the product's epilogue."""
     _cuda(a, w, out)
@@ -543,7 +552,7 @@ def gemm_skinny_swiglu(a, w, out) -> None:
     F = out.shape[1]
     _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
           "gemm_skinny_swiglu: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
-    _need(gemm_skinny_ok(a, w, out), "gemm_skinny_swiglu: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    _need(checked or gemm_skinny_ok(a, w, out), "gemm_skinny_swiglu: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
     f = _fn("gemm_skinny", "si_gemm_skinny_swiglu", [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, F, K, _stream()),
            f"gemm_skinny_swiglu(M={M}, F={F}, K={K})")

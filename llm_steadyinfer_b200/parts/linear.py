@@ -37,7 +37,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32:
         ops.gemm_f32(x, w, out)
     elif USE_SKINNY and ops.gemm_skinny_ok(x, w, out):
-        ops.gemm_skinny(x, w, out)
+        ops.gemm_skinny(x, w, out, checked=True)
     elif (USE_OWN_GEMM and x.shape[0] >= OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available()
           and ops.gemm_tc05_ok(x, w, out)):
         ops.gemm_tc05(x, w, out)

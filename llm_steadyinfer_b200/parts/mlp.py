@@ -60,7 +60,7 @@ class GatedMLP(FeedForward):
         act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
         if (self.group == INTERLEAVE and linear_mod.USE_SKINNY and act.dtype == torch.bfloat16
                 and ops.gemm_skinny_ok(x, self.gate_up, act)):
-            ops.gemm_skinny_swiglu(x, self.gate_up, act)
+            ops.gemm_skinny_swiglu(x, self.gate_up, act, checked=True)
         elif (self.group == INTERLEAVE and USE_TC05_GEMM and T >= TC05_MIN_ROWS and act.dtype == torch.bfloat16
                 and ops.gemm_tc05_available() and ops.gemm_tc05_ok(x, self.gate_up, act)):
             ops.gemm_tc05_swiglu(x, self.gate_up, act, ctx.status)
