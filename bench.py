@@ -41,7 +41,7 @@ def peaks():
             with open(path) as f:
                 d = json.load(f)
             return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}, "measured"
-        except (ValueError, KeyError):
+        except (ValueError, KeyError, TypeError, OSError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
 
