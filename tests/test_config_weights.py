@@ -100,6 +100,35 @@ def test_random_model_folder_is_seeded_and_bf16(tmp_path):
     assert all(torch.equal(lib[n], fa.tensor(n)) for n in names)
 
 
+FIRST_DRAWS = [-0.44682979583740234, 0.6466436386108398, -0.1698441505432129]
+
+
+def test_random_draws_are_a_function_of_seed_name_and_index():
+    from llm_steadyinfer_b200.weights import random_init as ri
+    key = ri.tensor_key(3, "model.layers.0.mlp.up_proj.weight")
+    z = ri.standard_draws(key, 0, 1 << 18, "cpu")
+    assert z.dtype == torch.float64
+    # a draw depends on its index alone, not on where the chunk starts or how long it is
+    assert torch.equal(ri.standard_draws(key, 1000, 77, "cpu"), z[1000:1077])
+    assert abs(z.mean().item()) < 0.01 and abs(z.std().item() - 1.0) < 0.01 and z.abs().max().item() <= 6.0
+    assert abs(((z ** 4).mean() / z.var() ** 2).item() - 2.9) < 0.05        # twelve uniforms: kurtosis 3 - 1/10
+    assert abs(torch.corrcoef(torch.stack([z[:-1], z[1:]]))[0, 1].item()) < 0.01
+    other = ri.standard_draws(ri.tensor_key(3, "model.layers.1.mlp.up_proj.weight"), 0, 1 << 18, "cpu")
+    assert abs(torch.corrcoef(torch.stack([z, other]))[0, 1].item()) < 0.01
+    assert ri.tensor_key(3, "a") != ri.tensor_key(4, "a") != ri.tensor_key(4, "b")
+    # a tensor drawn in several chunks equals the same tensor drawn in one
+    was = ri._CHUNK
+    try:
+        whole = ri._draw("w", (37, 29), False, 5, "cpu", torch.float32)
+        ri._CHUNK = 100
+        assert torch.equal(ri._draw("w", (37, 29), False, 5, "cpu", torch.float32), whole)
+    finally:
+        ri._CHUNK = was
+    # fixed values: the draw is part of what a seed means, on every machine
+    first = ri.standard_draws(ri.tensor_key(0, "model.embed_tokens.weight"), 0, 3, "cpu").tolist()
+    assert first == pytest.approx(FIRST_DRAWS, abs=0)
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     d = tmp_path / "m"
     write_random_model(str(d), TINY_A, 0)
