@@ -153,10 +153,11 @@ class CacheManager:
         return all(m <= g.pool.num_free for m, g in zip(self.pages_missing(req, new_length), self.groups))
 
     # ---- life of a request -----------------------------------------------------------
-    def admit(self, req, tokens: Optional[Sequence[int]] = None) -> int:
+    def admit(self, req, tokens: Optional[Sequence[int]] = None, chain: Optional[List[bytes]] = None) -> int:
         """Give the request a state slot and empty tables. With prefix reuse and its prompt
         ``tokens``, mount the longest stored chain of whole pages that leaves at least one
-        token to compute. Returns the number of tokens already held."""
+        token to compute (``chain``: ``chain_hashes(tokens)`` if the caller has them already).
+        Returns the number of tokens already held."""
         if req in self.requests:
             raise ValueError(f"request {req!r} is already live")
         slot = self.slots.take()
@@ -169,7 +170,7 @@ class CacheManager:
         for g in self.groups:
             g.tables[req] = []
         if self.prefix_reuse and tokens is not None:
-            pages = self.match_prefix(tokens)
+            pages = self.match_prefix(tokens, chain)
             pool = self.groups[0].pool
             for p in pages:
                 pool.retain(p)
@@ -248,33 +249,38 @@ class CacheManager:
         g.pool.release(page, park=self.prefix_reuse and page in self._page_to_hash)
 
     # ---- prefix reuse ---------------------------------------------------------------
-    def _chain(self, tokens: Sequence[int], n_blocks: int):
-        h = b""
-        ps = self.page_size
-        for b in range(n_blocks):
-            blk = tokens[b * ps:(b + 1) * ps]
-            h = hashlib.blake2b(h + struct.pack(f"<{ps}i", *blk), digest_size=16).digest()
-            yield b, h
-
-    def match_prefix(self, tokens: Sequence[int]) -> List[int]:
+    def chain_hashes(self, tokens: Sequence[int]) -> List[bytes]:
+        """One hash per whole page of ``tokens``, each chained over every token up to the page's end. A
+        caller that asks about the same tokens again and again keeps the list and hands it back."""
         if not self.prefix_reuse:
             return []
+        out, h, ps = [], b"", self.page_size
+        for b in range(len(tokens) // ps):
+            h = hashlib.blake2b(h + struct.pack(f"<{ps}i", *tokens[b * ps:(b + 1) * ps]), digest_size=16).digest()
+            out.append(h)
+        return out
+
+    def match_prefix(self, tokens: Sequence[int], chain: Optional[List[bytes]] = None) -> List[int]:
+        if not self.prefix_reuse:
+            return []
+        chain = self.chain_hashes(tokens) if chain is None else chain
         pages = []
-        for _, h in self._chain(tokens, (len(tokens) - 1) // self.page_size):
+        for h in chain[:(len(tokens) - 1) // self.page_size]:      # at least one token is left to compute
             p = self._hash_to_page.get(h)
             if p is None:
                 break
             pages.append(p)
         return pages
 
-    def remember_prefix(self, req, tokens: Sequence[int]) -> None:
+    def remember_prefix(self, req, tokens: Sequence[int], chain: Optional[List[bytes]] = None) -> None:
         """Key the request's whole, fully written pages by their chained hashes."""
         if not self.prefix_reuse:
             return
         rc = self.requests[req]
         t = self.groups[0].tables[req]
         n = min(rc.length, len(tokens)) // self.page_size
-        for b, h in self._chain(tokens, n):
+        chain = self.chain_hashes(tokens) if chain is None else chain
+        for b, h in enumerate(chain[:n]):
             if h in self._hash_to_page or t[b] in self._page_to_hash:
                 continue
             self._hash_to_page[h] = t[b]

@@ -531,13 +531,21 @@ SI_EXPORT long long si_attn_decode_scratch_floats(int num_items, int H, int KV, 
   return SI_ATTN_TICKETS + (long long)num_items * KV * nsplit * rows * (hs + 2);
 }
 
+template <int HS_PAD> constexpr int decode_stages() { return HS_PAD <= 128 ? 3 : 2; }
+
+// Dynamic shared memory of the decode kernel: the q rows and the K/V stages, or the merge's staging if larger.
+template <int HS_PAD, int MT>
+constexpr size_t decode_smem_bytes() {
+  constexpr int ROWS = 16 * MT;
+  constexpr size_t tiles = (size_t)(ROWS + 2 * decode_stages<HS_PAD>() * 64) * HS_PAD * sizeof(bf16);
+  constexpr size_t merge = (size_t)4 * ROWS * (2 + HS_PAD + 4) * sizeof(float);
+  return merge > tiles ? merge : tiles;
+}
+
 template <int HS_PAD, int MT>
 static int launch_decode(AttnParams& p, int num_items, cudaStream_t stream) {
-  constexpr int ROWS = 16 * MT;
-  constexpr int STAGES = HS_PAD <= 128 ? 3 : 2;
-  size_t smem = (size_t)(ROWS + 2 * STAGES * 64) * HS_PAD * sizeof(bf16);
-  const size_t merge = (size_t)4 * ROWS * (2 + HS_PAD + 4) * sizeof(float);
-  if (merge > smem) smem = merge;
+  constexpr int STAGES = decode_stages<HS_PAD>();
+  const size_t smem = decode_smem_bytes<HS_PAD, MT>();
   auto k = attn_decode_kernel<HS_PAD, MT, STAGES>;
   int rc = set_smem(k, smem);
   if (rc) return rc;

@@ -1,8 +1,10 @@
 // Split decode attention with library-owned scratch: see attention_noalloc.h for who needs
 // this and the rules. The kernel is the cp.async decode kernel of attention_mma.cu, compiled
 // into this library again by including that file; only where its scratch comes from differs.
+#define SI_EXPORT extern "C" __attribute__((visibility("hidden")))   // attention_mma.cu's entry points stay in its own library
 #include "attention_noalloc.h"
 #include "attention_mma.cu"
+#include <atomic>
 #include <stdio.h>
 
 // The scratch itself: tickets first (a fixed region, so their place never depends on a
@@ -11,7 +13,7 @@
 static __device__ __align__(256) float g_noalloc_scratch[SI_NOALLOC_MAX_UNITS + SI_NOALLOC_SCRATCH_WORDS];
 
 #define SI_NOALLOC_MAX_DEVICES 64
-static float* g_scratch_addr[SI_NOALLOC_MAX_DEVICES];      // device address per device, once looked up
+static std::atomic<float*> g_scratch_addr[SI_NOALLOC_MAX_DEVICES];      // device address per device, once looked up
 static thread_local char g_error[256] = "";
 
 extern "C" __attribute__((visibility("default"))) const char* si_noalloc_last_error(void) { return g_error; }
@@ -25,6 +27,16 @@ long long si_attn_decode_noalloc_words(int num_items, int H, int KV, int hs, int
   return (long long)num_items * KV * nsplit * rows * (hs + 2);
 }
 
+template <int HS_PAD, int MT>
+static bool decode_smem_limit() {
+  return set_smem(attn_decode_kernel<HS_PAD, MT, decode_stages<HS_PAD>()>, decode_smem_bytes<HS_PAD, MT>()) == 0;
+}
+// Every variant that si_attn_decode_noalloc may launch; touching them also loads the module on the device.
+static bool set_decode_smem_limits() {
+  return decode_smem_limit<64, 1>() && decode_smem_limit<64, 2>() && decode_smem_limit<64, 4>() &&
+         decode_smem_limit<128, 1>() && decode_smem_limit<128, 2>() && decode_smem_limit<256, 1>();
+}
+
 // Device address of the scratch array on the current device; looked up on the first call.
 static int scratch_for_current_device(float** out) {
   int dev = -1;
@@ -33,17 +45,37 @@ static int scratch_for_current_device(float** out) {
     snprintf(g_error, sizeof g_error, "cannot identify the current device (%s)", cudaGetErrorString(e));
     return SI_NOALLOC_SETUP_FAILED;
   }
-  if (!g_scratch_addr[dev]) {
-    float* ptr = nullptr;
+  float* ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    // Threads that get here together each ask the runtime; it gives them all the same address.
     e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
     if (e != cudaSuccess || !ptr) {
       snprintf(g_error, sizeof g_error, "cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
       return SI_NOALLOC_SETUP_FAILED;
     }
-    g_scratch_addr[dev] = ptr;
+    if (!set_decode_smem_limits()) {
+      snprintf(g_error, sizeof g_error, "setting the kernels' shared-memory limits failed on device %d", dev);
+      return SI_NOALLOC_SETUP_FAILED;
+    }
+    g_scratch_addr[dev].store(ptr, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = ptr;
   return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int si_noalloc_init(void) {
+  g_error[0] = 0;
+  float* base = nullptr;
+  return scratch_for_current_device(&base);
+}
+
+extern "C" __attribute__((visibility("default"))) int si_noalloc_poison_tickets(int units, cudaStream_t stream) {
+  g_error[0] = 0;
+  if (units < 0 || units > SI_NOALLOC_MAX_UNITS) return -2;
+  float* base = nullptr;
+  const int rc = scratch_for_current_device(&base);
+  if (rc) return rc;
+  return (int)cudaMemsetAsync(base, 0x5a, (size_t)units * sizeof(int), stream);
 }
 
 extern "C" __attribute__((visibility("default")))

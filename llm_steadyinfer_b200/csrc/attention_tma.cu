@@ -540,7 +540,7 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
   }
   const dim3 grid = work ? dim3(num_work, p.KV, 1) : dim3(num_items, p.KV, p.nsplit);
   si_launch(k, grid, dim3(160), smem, stream, p, km, vm, log2_page, work,
-            si_pdl_trigger_mode((long long)grid.x * grid.y * grid.z, 296) == 1 ? 1 : 0);
+            si_pdl_trigger_mode((long long)grid.x * grid.y * grid.z, 2 * si_sm_count()) == 1 ? 1 : 0);
   return si_last_error();
 }
 

@@ -9,7 +9,11 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+// A file that includes another .cu file to reuse its kernels defines SI_EXPORT first (hidden visibility),
+// so that the included file's entry points are not exported a second time from its library.
+#ifndef SI_EXPORT
 #define SI_EXPORT extern "C" __attribute__((visibility("default")))
+#endif
 
 // Status codes written (atomicMax) into the engine's device status word.
 enum SiStatus : int {
@@ -120,6 +124,20 @@ static inline int si_pdl_trigger_mode(long long blocks, long long slots) {
   const int level = si_pdl_trigger_level();
   if (blocks <= slots) return level >= 2 ? 1 : 0;
   return level >= 3 ? 2 : 0;
+}
+
+// Streaming multiprocessors of the current device, asked once per device. Grid sizes that should fill the
+// device once ("one wave") are derived from it; no kernel's result depends on it.
+static inline int si_sm_count() {
+  static int count[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    count[dev] = n;
+  }
+  return count[dev];
 }
 
 static inline bool si_pdl_enabled() {

@@ -178,11 +178,11 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
   if (out_dtype == SI_BF16) {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
   } else {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 296));
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
   }
   return si_last_error();
 }
@@ -198,7 +198,7 @@ SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W,
   const unsigned blocks = (unsigned)(F / 8);
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 296));
-  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 296));
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
   return si_last_error();
 }

@@ -145,7 +145,8 @@ static int launch2(float* resid, const void* delta, const int* rows, const void*
     // with something to fetch ahead: enough further blocks that every SM takes part
     if (ahead && ahead_bytes < 4096) ahead = nullptr;
     const int trigger = si_pdl_trigger_enabled() && num_rows <= 64;      // a launch of one wave
-    const int extra = ahead ? max(0, 148 - num_rows) + 148 : 0;
+    const int sms = si_sm_count();
+    const int extra = ahead ? max(0, sms - num_rows) + sms : 0;
     const dim3 grid(num_rows + extra);
     if (per <= 1) si_launch(add_rmsnorm_vec_kernel<TX, TW, 1>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);
     else if (per <= 2) si_launch(add_rmsnorm_vec_kernel<TX, TW, 2>, grid, dim3(threads), 0, stream, resid, d, rows, w, o, hidden, eps, num_rows, ahead, ahead_bytes, trigger);

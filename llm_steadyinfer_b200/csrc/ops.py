@@ -48,6 +48,20 @@ def set_device(index: Optional[int]) -> None:
     _device_index = index
 
 
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (default: the current one), asked once per device."""
+    index = torch.device(device).index if device is not None else None
+    if index is None:
+        index = _device_index if _device_index is not None else torch.cuda.current_device()
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return n
+
+
 def _stream():
     """The current stream's handle. Every kernel call asks for it, so it comes from the one C call that
     returns the handle (torch.cuda.current_stream() builds a Python object around it at ten times the cost)."""
@@ -275,6 +289,15 @@ def argmax(logits, out, scratch) -> None:
     _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(scratch), capacity, _ptr(out), _stream()), "argmax")
 
 
+def selftest_wait_runs_out(status, limit: int = 4096, gave_up=None) -> None:
+    """Launch the self-test kernel whose bounded wait nothing ends: after ``limit`` probes it writes the
+    wait-limit code into ``status`` (int32 [1]) and returns; ``gave_up`` (int32 [1], optional) is set to 1."""
+    _cuda(status, gave_up)
+    _i32(status, "status"); _i32(gave_up, "gave_up")
+    f = _fn("selftest", "si_selftest_wait_runs_out", [_c_p, _c_int, _c_p, _c_p])
+    _check(f(_ptr(status), int(limit), _ptr(gave_up), _stream()), f"selftest_wait_runs_out(limit={limit})")
+
+
 # ---- tensor-core attention (bf16) ---------------------------------------------------------
 
 _c_llr = ctypes.c_longlong
@@ -351,6 +374,18 @@ def attn_decode(q, k_cache, v_cache, block_table, items, out, page_size: int, nu
 
 # ---- decode attention with TMA-fed tiles ----------------------------------------------------
 
+MAX_KEPT_MAPS = 4096      # descriptors kept per table; the oldest goes when a new one would exceed it
+
+
+def _keep_map(table: dict, key, ent) -> None:
+    """Descriptors are kept by (device, address, shape): a tensor at the same place with the same shape has
+    the same descriptor, so an entry that outlives its tensor is still right for the next one there. The
+    table is bounded, so that a process that builds engine after engine does not grow it for ever."""
+    while len(table) >= MAX_KEPT_MAPS:
+        table.pop(next(iter(table)))
+    table[key] = ent
+
+
 _tensor_maps = {}
 
 
@@ -375,7 +410,7 @@ def attn_decode_tma_scratch_floats(num_items: int, H: int, KV: int, hs: int, nsp
 
 def _cache_map(cache: torch.Tensor):
     """The TMA descriptor of one layer's K or V cache; made once per tensor and kept."""
-    key = (cache.data_ptr(), tuple(cache.shape))
+    key = (cache.device.index, cache.data_ptr(), tuple(cache.shape))
     ent = _tensor_maps.get(key)
     if ent is None:
         raw = ctypes.create_string_buffer(128 + 64)
@@ -386,7 +421,7 @@ def _cache_map(cache: torch.Tensor):
         if rc != 0:
             raise KernelError(f"cannot describe the cache {tuple(cache.shape)} to the TMA unit (code {rc})")
         ent = (raw, addr)
-        _tensor_maps[key] = ent
+        _keep_map(_tensor_maps, key, ent)
     return _c_p(ent[1])
 
 
@@ -584,7 +619,7 @@ def gemm_tc05_ok(a, w, out) -> bool:
 
 
 def _weight_map(w: torch.Tensor):
-    key = (w.data_ptr(), tuple(w.shape), w.stride(0))
+    key = (w.device.index, w.data_ptr(), tuple(w.shape), w.stride(0))
     ent = _weight_maps.get(key)
     if ent is None:
         raw = ctypes.create_string_buffer(128 + 64)
@@ -594,7 +629,7 @@ def _weight_map(w: torch.Tensor):
         if rc != 0:
             raise KernelError(f"cannot describe the weight {tuple(w.shape)} to the TMA unit (code {rc})")
         ent = (raw, addr)
-        _weight_maps[key] = ent
+        _keep_map(_weight_maps, key, ent)
     return _c_p(ent[1])
 
 

@@ -184,7 +184,7 @@ SI_EXPORT int si_rope_kv_write(void* qkv, int dtype, long long row_stride, const
   const int heads = H + 2 * KV;
   // heads per block: all of them when there are many rows, fewer when rows alone cannot fill the GPU
   int hpb = heads;
-  while (hpb > 1 && (long long)num_tokens * ((heads + hpb - 1) / hpb) < 592) hpb = (hpb + 1) / 2;
+  while (hpb > 1 && (long long)num_tokens * ((heads + hpb - 1) / hpb) < 4 * si_sm_count()) hpb = (hpb + 1) / 2;
   const int blocks_y = (heads + hpb - 1) / hpb;
   if (blocks_y > 65535) return -2;
   const int work = hpb * hs / 2;

@@ -22,12 +22,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tma_smem_u32(bar)) : "memory");
 }
-// Bounded wait: false when the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+// Bounded wait: false when the phase did not complete within `limit` further probes.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, unsigned parity, int limit) {
   if (mbar_try_wait(bar, parity)) return true;       // the common case costs one probe, not a loop
-  for (int it = 0; it < (1 << 20); ++it)
+  for (int it = 0; it < limit; ++it)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
+}
+// The limit every kernel of the package waits with (tens of milliseconds; a tile arrives in microseconds).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  return mbar_wait_limited(bar, parity, 1 << 20);
 }
 // The same wait for a whole warp: after one probe by all lanes, one lane polls and the others get
 // its answer.

@@ -31,6 +31,7 @@ When pages run out:
 """
 from __future__ import annotations
 
+import hashlib
 import itertools
 import time
 from collections import deque
@@ -67,6 +68,7 @@ class Sequence_:
     token_times: List[float] = field(default_factory=list)
     finish_time: Optional[float] = None
     admit_order: int = -1
+    prefix_chain: Optional[list] = None    # chained hashes of the prompt's whole pages, made once
 
     @property
     def tokens(self) -> List[int]:
@@ -103,6 +105,12 @@ class ScheduledItem:
 
 class RequestRejected(ValueError):
     pass
+
+
+def default_seed(request_id: Hashable) -> int:
+    """The seed of a request that names none: a digest of its id, the same in every process (Python's own
+    ``hash`` of a string changes from run to run)."""
+    return int.from_bytes(hashlib.blake2b(repr(request_id).encode(), digest_size=4).digest(), "little") & 0x7FFFFFFF
 
 
 class Scheduler:
@@ -150,7 +158,7 @@ class Scheduler:
             rid = next(self._ids)
         if self._is_live(rid):
             raise RequestRejected(f"a request with the id {rid!r} is waiting or running")
-        seed = params.seed if params.seed is not None else (hash(rid) & 0x7FFFFFFF)
+        seed = params.seed if params.seed is not None else default_seed(rid)
         seq = Sequence_(id=rid, prompt=prompt, params=params, max_gen=max_gen, seed=seed,
                         arrival_time=self.clock())
         self.waiting.append(seq)
@@ -253,12 +261,14 @@ class Scheduler:
             if not self.cache.has(seq.id):
                 if self.cache.slots.num_free == 0:
                     break
-                matched = len(self.cache.match_prefix(seq.prompt)) * self.cache.page_size
-                need = self.cache.blocks_for(seq.num_tokens) - matched // self.cache.page_size
-                if any(need > self.cache.free_pages(g) - self._parked_in_match(seq, g)
+                if seq.prefix_chain is None:               # a request that waits at the head is hashed once
+                    seq.prefix_chain = self.cache.chain_hashes(seq.prompt)
+                pages = self.cache.match_prefix(seq.prompt, seq.prefix_chain)
+                need = self.cache.blocks_for(seq.num_tokens) - len(pages)
+                if any(need > self.cache.free_pages(g) - self._parked_among(pages, g)
                        for g in range(len(self.cache.groups))):
                     break
-                seq.num_computed = self.cache.admit(seq.id, seq.prompt)
+                seq.num_computed = self.cache.admit(seq.id, seq.prompt, seq.prefix_chain)
                 seq.prefix_hit_tokens = seq.num_computed
             elif not self.cache.can_grow(seq.id, seq.num_tokens):
                 break
@@ -270,12 +280,12 @@ class Scheduler:
             self.running.append(seq)
             self.running.sort(key=lambda s: s.admit_order)
 
-    def _parked_in_match(self, seq: Sequence_, g: int) -> int:
+    def _parked_among(self, pages: List[int], g: int) -> int:
         """Matched prefix pages that are counted as free (parked) but will be taken back."""
         if g != 0 or not self.cache.prefix_reuse:
             return 0
         pool = self.cache.groups[0].pool
-        return sum(1 for p in self.cache.match_prefix(seq.prompt) if pool.is_parked(p))
+        return sum(1 for p in pages if pool.is_parked(p))
 
     def _page_for_decode(self, seq: Sequence_) -> bool:
         """Make room for one more token of ``seq``; newer requests give pages if needed."""
@@ -368,7 +378,7 @@ class Scheduler:
                 continue
             seq.num_computed = it.start + it.count
             if it.start < len(seq.prompt) <= seq.num_computed:
-                self.cache.remember_prefix(seq.id, seq.prompt)
+                self.cache.remember_prefix(seq.id, seq.prompt, seq.prefix_chain)
             if not it.want_logits:
                 continue
             tok = int(sampled[seq.id])

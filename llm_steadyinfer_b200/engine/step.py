@@ -148,6 +148,10 @@ class ModelRunner:
         self._stage = _PinnedRing(4 * (T + 4) + 3 * (S + 4) + 8 + G * S * W, self.device)
         self._table_arrays: Dict[Tuple[int, Hashable], Tuple[int, np.ndarray]] = {}
         self._graphs: Dict[Tuple[int, int], dict] = {}
+        # Shapes whose recording failed: they run directly from then on, as the reference marks a batch size
+        # capture_failed and keeps to its direct path (src/source/model/model.cpp:189-227, 251).
+        self.capture_failed: Dict[Tuple[int, int], str] = {}
+        self.fail_next_capture = False    # host-side fault injection for tests: the next recording raises
         self._generation = 0              # bumped when a captured address may have changed
         self.ctx = StepContext(self)
         self.launches_last_step = 0
@@ -262,24 +266,9 @@ class ModelRunner:
             before = ops.launch_count()
             logits = self.model.forward(ctx, caches)            # runs this step, allocates all scratch
             launches = ops.launch_count() - before
-            gen = self._generation
-            graph = torch.cuda.CUDAGraph()
-            torch.cuda.current_stream().synchronize()
-            # No garbage collection while the stream records: collecting an engine that is no longer
-            # used destroys its graphs, a call that is not allowed during capture and spoils it.
-            collecting = gc.isenabled()
-            gc.collect()
-            gc.disable()
-            try:
-                with torch.cuda.graph(graph):
-                    captured = self.model.forward(ctx, caches)      # recorded, not run
-            finally:
-                if collecting:
-                    gc.enable()
-            ops.add_launches(-launches)                          # recording launched nothing
-            if gen == self._generation:                           # no buffer moved while capturing
-                self._graphs[key] = {"graph": graph, "logits": captured, "launches": launches}
             self.launches_last_step = launches
+            if key not in self.capture_failed:
+                self._record(key, ctx, caches, launches)
         else:
             g["graph"].replay()
             ops.add_launches(g["launches"])
@@ -287,6 +276,35 @@ class ModelRunner:
             logits = g["logits"]
         self._commit(entries)
         return logits[:S]
+
+    def _record(self, key, ctx, caches, launches: int) -> None:
+        """Record the step that has just run into a CUDA graph for later steps of the same shape. A
+        recording that fails costs nothing but itself: the step's results are there already, the shape is
+        marked and runs directly from then on."""
+        gen = self._generation
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.current_stream().synchronize()
+        # No garbage collection while the stream records: collecting an engine that is no longer
+        # used destroys its graphs, a call that is not allowed during capture and spoils it.
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        before = ops.launch_count()
+        try:
+            with torch.cuda.graph(graph):
+                if self.fail_next_capture:
+                    self.fail_next_capture = False
+                    raise StepError("recording failed (injected by fail_next_capture)")
+                captured = self.model.forward(ctx, caches)      # recorded, not run
+        except Exception as e:                                   # noqa: BLE001 - any failure means: run directly
+            self.capture_failed[key] = f"{type(e).__name__}: {e}"
+            captured = None
+        finally:
+            ops.add_launches(before - ops.launch_count())        # recording launched nothing
+            if collecting:
+                gc.enable()
+        if captured is not None and gen == self._generation:      # no buffer moved while recording
+            self._graphs[key] = {"graph": graph, "logits": captured, "launches": launches}
 
     def _prepare(self, entries: Sequence[StepEntry], seq_cap: Optional[int] = None,
                  width_cap: Optional[int] = None) -> StepContext:
@@ -329,6 +347,7 @@ class ModelRunner:
                                 f"of {self.max_width * self.page_size}")
             mgr.grow(e.req, new_len)
             self._new_lengths.append(new_len)
+        self._check_pages_written(entries)
 
         R = sum(len(e.want) for e in entries)
         G = len(mgr.groups)
@@ -404,6 +423,26 @@ class ModelRunner:
         dtabs = dev[table_off:table_off + G * S_cap * W_cap].view(G, S_cap, W_cap)
         self._tables = [dtabs[g] for g in range(G)]
         return ctx
+
+    def _check_pages_written(self, entries: Sequence[StepEntry]) -> None:
+        """A step may store keys and values only into pages that its request holds alone. A page with more
+        than one holder carries a prefix that other requests read (or will read again from the prefix index):
+        a store into it is a fault of whoever decided the step, and is refused here, before anything runs.
+        (The reference's decode row re-stores the last prompt token's keys into what may be a shared block,
+        src/source/scheduler/scheduler.cpp:382-400.)"""
+        mgr, ps = self.manager, self.page_size
+        for e, new_len in zip(entries, self._new_lengths):
+            first = mgr.length(e.req) // ps
+            last = (new_len - 1) // ps
+            for g, grp in enumerate(mgr.groups):
+                t = grp.tables[e.req]
+                for b in range(first, min(last + 1, len(t))):
+                    page = t[b]
+                    if page >= 0 and grp.pool.refcount(page) != 1:
+                        raise StepError(
+                            f"request {e.req!r} would store positions {max(mgr.length(e.req), b * ps)}.."
+                            f"{min(new_len, (b + 1) * ps) - 1} into page {page} of group {g}, which "
+                            f"{grp.pool.refcount(page)} holders share; a shared page is never written")
 
     def _table_array(self, group: int, req) -> np.ndarray:
         """A request's block table as an int32 array, rebuilt only when the table has changed."""

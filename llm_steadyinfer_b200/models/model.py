@@ -91,7 +91,7 @@ class Model:
 
     def capturable(self) -> bool:
         """True if every part's ``forward`` may be captured into a CUDA graph (see ``Part.capturable``)."""
-        return all(part.capturable for _, part in self._named_parts())
+        return all(part.capturable for _, part in self._named_parts()) and all(b.capturable for b in self.blocks)
 
     # ---- forward -------------------------------------------------------------------
     def prepare(self, ctx, caches) -> None:

@@ -19,7 +19,7 @@ from .linear import linear
 USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
 USE_TMA = True               # decode tiles by TMA where the layout allows
 USE_TC05 = True              # prompt portions on tcgen05 where the layout allows
-TARGET_BLOCKS = 2 * 148      # decode attention blocks that run at once
+DECODE_BLOCKS_PER_SM = 2     # decode attention blocks that one multiprocessor holds at once
 MAX_SPLITS = 32
 MIN_TILES_PER_SPLIT = 2      # a split covers at least this many 64-key tiles
 
@@ -94,6 +94,10 @@ class Attention(Mixer):
         return out
 
     # ---- kernels ---------------------------------------------------------------------
+    def target_blocks(self) -> int:
+        """Decode attention blocks that run at once on this part's device."""
+        return DECODE_BLOCKS_PER_SM * ops.sm_count(self.device)
+
     def uses_tensor_cores(self) -> bool:
         return self.dtype == torch.bfloat16 and USE_TENSOR_CORES and self.hs % 16 == 0
 
@@ -141,7 +145,7 @@ class Attention(Mixer):
                 tiles.append(-(-(pos0 + n - first) // 64) if n > 0 else 0)
             # Entries: every item whole, the shares that run at once, and room for finer cuts when items outnumber
             # those (entries without work are blocks that start and leave, so not more room than pays)
-            budget = TARGET_BLOCKS // self.KV
+            budget = max(1, self.target_blocks() // self.KV)
             entries = budget + len(dec) + min(3 * len(dec), 2 * budget)
             work = ops.split_work(tiles, budget, entries, MAX_SPLITS, MIN_TILES_PER_SPLIT)
             if ctx.seq_cap is None:                    # shapes are free: only the entries with work
@@ -154,7 +158,7 @@ class Attention(Mixer):
                                       torch.float32)
         elif dec:
             # as many blocks as run at once (two per SM), not more: a second wave would wait
-            nsplit = max(1, min(MAX_SPLITS, TARGET_BLOCKS // (len(dec) * self.KV)))
+            nsplit = max(1, min(MAX_SPLITS, self.target_blocks() // (len(dec) * self.KV)))
             if ctx.seq_cap is None:
                 longest = max(d[3] + d[2] for d in dec)
                 nsplit = min(nsplit, max(1, -(-longest // (64 * MIN_TILES_PER_SPLIT))))

@@ -480,3 +480,106 @@ def test_windowed_layers_generate_through_the_entry_point(tmp_path, ahead):
     assert (llm.stats["ahead_steps"] > 0) == ahead
     llm.runner.manager.check_invariant()
     assert not llm.runner.manager.requests
+
+
+# ---- another arrangement of a block, registered from this test ------------------------------------
+
+PARALLEL = {
+    "architectures": ["ParallelToyForCausalLM"], "hidden_size": 80, "intermediate_size": 136,
+    "num_hidden_layers": 3, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 16,
+    "vocab_size": 333, "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "rope_scaling": None, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+
+
+def _parallel_register():
+    """A block whose mixer and feed-forward both read the one normalised stream and whose results are added
+    together: ``h += delta_in; x = norm1(h); return mixer(x) + ffn(x)``. The second norm of the spec is not run.
+    Middle layer only; the layers around it keep the built-in arrangement."""
+    from dataclasses import replace
+    from llm_steadyinfer_b200.config.base import ModelConfig, register_architecture
+    from llm_steadyinfer_b200.models.llama import LlamaConfig
+    from llm_steadyinfer_b200.parts import register_arrangement
+
+    def parallel(block, resid, delta, ctx, cache):
+        T, d = resid.shape
+        x = ctx.buf("block_x", (T, d), block.mixer.dtype)
+        block.norm(block.mixer_norm, resid, delta, x)
+        a = block.mixer.forward(x, ctx, cache)
+        kept = ctx.buf("toy_parallel_a", (T, d), a.dtype)         # the feed-forward writes where the mixer wrote
+        kept.copy_(a)
+        m = block.feed_forward.forward(x, ctx)
+        m.add_(kept)
+        return m
+
+    @dataclass(frozen=True)
+    class ParallelConfig(ModelConfig):
+        d: dict
+        architecture = "ParallelToyForCausalLM"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(dict(d))
+
+        def to_dict(self):
+            return dict(self.d)
+
+        def model_spec(self):
+            base = LlamaConfig.from_dict({**self.d, "architectures": ["LlamaForCausalLM"]}).model_spec()
+            layers = [replace(l, arrangement="toy_parallel") if i == 1 else l for i, l in enumerate(base.layers)]
+            return replace(base, layers=layers)
+
+    register_arrangement("toy_parallel", parallel, capturable=True)
+    register_architecture("ParallelToyForCausalLM", ParallelConfig)
+
+
+def _parallel_plain(cfg, w, tokens):
+    d, H, hs, eps = cfg["hidden_size"], cfg["num_attention_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    KV = cfg["num_key_value_heads"]
+    pos = torch.arange(len(tokens))
+    freqs = pl.rope_frequencies(hs, cfg["rope_theta"], None)
+    h = pl.embedding(torch.tensor(tokens), w["model.embed_tokens.weight"])
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        x = pl.rmsnorm(h, w[p + "input_layernorm.weight"], eps)
+        q = pl.rope((x @ w[p + "self_attn.q_proj.weight"].T).view(-1, H, hs), pos, freqs)
+        k = pl.rope((x @ w[p + "self_attn.k_proj.weight"].T).view(-1, KV, hs), pos, freqs)
+        v = (x @ w[p + "self_attn.v_proj.weight"].T).view(-1, KV, hs)
+        a = pl.attention(q, k, v, hs ** -0.5).reshape(-1, H * hs) @ w[p + "self_attn.o_proj.weight"].T
+        if l != 1:
+            h = h + a
+            x = pl.rmsnorm(h, w[p + "post_attention_layernorm.weight"], eps)
+        m = pl.swiglu(x @ w[p + "mlp.gate_proj.weight"].T, x @ w[p + "mlp.up_proj.weight"].T) @ w[p + "mlp.down_proj.weight"].T
+        h = h + a + m if l == 1 else h + m
+    return pl.rmsnorm(h, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_another_block_arrangement_is_registered_and_replayed(tmp_path, dtype):
+    _parallel_register()
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    from llm_steadyinfer_b200.weights import write_random_model
+    folder = os.path.join(str(tmp_path), "parallel")
+    write_random_model(folder, PARALLEL, seed=9, store_dtype=torch.bfloat16)
+    _, w = pl.read_model_folder(folder)
+    reqs = {"x": ru.random_tokens(PARALLEL["vocab_size"], 90, 1), "y": ru.random_tokens(PARALLEL["vocab_size"], 47, 2),
+            "z": ru.random_tokens(PARALLEL["vocab_size"], 130, 3)}
+    want = {r: _parallel_plain(PARALLEL, w, t) for r, t in reqs.items()}
+    # the arrangement matters: the built-in one gives other logits
+    assert (pl.forward({**PARALLEL, "num_key_value_heads": 5}, w, reqs["y"]) - want["y"]).abs().max().item() > 1e-3
+    atol = 1e-5 if dtype == torch.float32 else 1e-2
+    for mode in ("whole", "tail", "portions", "mixed"):
+        rp = Replayer(folder, dtype, max_tokens=320, page_size=16)
+        steps = {"whole": ru.trace_whole, "tail": ru.trace_tail,
+                 "portions": ru.trace_portions}.get(mode, lambda r: ru.trace_mixed(r, 320, seed=2))(reqs)
+        for rid, p, row in ru.replay_in_process(rp, steps):
+            diff = (row.double() - want[rid][p]).abs().max().item()
+            assert diff <= atol, f"parallel block, {mode}: request {rid} position {p} differs by {diff:.2e}"
+    if dtype == torch.float32:
+        # through the entry point with recorded decode steps: the arrangement says that it can be captured
+        prompts = [reqs["y"][:9], reqs["x"][:30]]
+        greedy = [_greedy(lambda t: _parallel_plain(PARALLEL, w, t), p, 12) for p in prompts]
+        llm = LLM(folder, dtype="float32", max_batch=2, max_seq_len=64, max_gen_len=12)
+        assert [g.token_ids for g in llm.generate(prompts, SamplingParams(ignore_eos=True))] == greedy
+        assert llm.stats["graph_steps"] > 0

@@ -53,7 +53,21 @@ def test_a_norm_is_given_the_hint_only_if_it_says_it_takes_one():
 
     dev = torch.device("cpu")
     w = torch.zeros(2)
-    Block._norm(Plain({}, torch.float32, dev), None, None, None, w)
-    Block._norm(Hinted({}, torch.float32, dev), None, None, None, w)
-    Block._norm(Hinted({}, torch.float32, dev), None, None, None, None)
+    Block.norm(Plain({}, torch.float32, dev), None, None, None, w)
+    Block.norm(Hinted({}, torch.float32, dev), None, None, None, w)
+    Block.norm(Hinted({}, torch.float32, dev), None, None, None, None)
     assert calls == [("plain", None), ("hinted", w), ("hinted", None)]
+
+
+def test_block_arrangements_are_a_registry():
+    from llm_steadyinfer_b200.parts import arrangement, register_arrangement
+    import pytest
+    assert callable(arrangement("pre_norm"))
+    with pytest.raises(KeyError) as e:
+        arrangement("sandwich")
+    assert "pre_norm" in str(e.value) and "sandwich" in str(e.value)
+    calls = []
+    register_arrangement("host_test_order", lambda block, resid, delta, ctx, cache: calls.append(block) or "out")
+    b = Block(None, None, None, None, "host_test_order")
+    assert b.forward(None, None, None, None) == "out" and calls == [b] and b.capturable is False
+    assert Block(None, None, None, None).capturable is True          # the built-in arrangement can be recorded

@@ -358,3 +358,40 @@ def test_an_id_cannot_be_live_twice():
         run_step(s, cache)
     s.add_request([4, 5], req_id="a")                    # ended: the id is free again
     assert s.add_request([6], req_id=None) != "a"
+
+
+def test_default_seed_is_the_same_in_every_process():
+    """A request that names no seed gets one from a digest of its id, not from Python's salted hash."""
+    import subprocess
+    import sys
+    from llm_steadyinfer_b200.engine.scheduler import default_seed
+    s, _ = make()
+    s.add_request([1, 2, 3], SamplingParams(temperature=0.8), req_id="chat-17")
+    s.add_request([1, 2, 3], SamplingParams(temperature=0.8, seed=5), req_id="chat-18")
+    seeds = {q.id: q.seed for q in s.waiting}
+    assert seeds == {"chat-17": default_seed("chat-17"), "chat-18": 5}
+    assert default_seed("chat-17") != default_seed("chat-18") and 0 <= default_seed(("a", 1)) < 2 ** 31
+    code = "from llm_steadyinfer_b200.engine.scheduler import default_seed; print(default_seed('chat-17'))"
+    for salt in ("1", "2"):
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, check=True,
+                             env={**__import__("os").environ, "PYTHONHASHSEED": salt,
+                                  "PYTHONPATH": __import__("os").path.dirname(__import__("os").path.dirname(__file__))})
+        assert int(out.stdout) == default_seed("chat-17")
+
+
+def test_a_waiting_prompt_is_hashed_once():
+    """While a request waits at the head of the queue for pages, every step asks the prefix index about it;
+    the chained hashes of its prompt are made at the first asking and kept."""
+    s, cache = make(num_pages=6, page_size=4, max_seqs=4, budget=64, max_gen=3, prefix=True)
+    calls = []
+    real = cache.chain_hashes
+    cache.chain_hashes = lambda tokens: calls.append(len(tokens)) or real(tokens)
+    s.add_request(list(range(20)))               # 5 pages + growth: fills the pool
+    run_step(s, cache)
+    s.add_request(list(range(100, 112)))         # 3 pages: waits until the first one ends
+    n = 0
+    while s.has_unfinished():
+        run_step(s, cache)
+        n += 1
+    assert n >= 3 and calls.count(12) == 1 and calls.count(20) == 1
+    cache.check_invariant()
