@@ -56,11 +56,13 @@ def trace_portions(reqs: Dict[str, List[int]], sizes: Sequence[int] = (17, 5, 2,
 
 
 def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4,
-                prompt_frac: float = 0.6) -> List[dict]:
+                prompt_frac: float = 0.6, cut_every: int = 0, kept=None) -> List[dict]:
     """Up to ``max_live`` live requests: portions of some prompts beside single "decoded" tokens
     of others; a request is admitted only when its whole length (rounded up to 64) still fits
     in ``max_tokens``, so pages of ended requests are used again by later ones. Some requests
-    sit a step out."""
+    sit a step out. With ``cut_every`` = n, every n-th step first cuts one live request back to a
+    random length as a preemption does (a "truncate" record; ``kept(held, keep)`` says how many tokens
+    stay) and the trace computes the cut tokens again, in portions, beside the others."""
     rng = random.Random(seed)
     waiting = list(reqs.items())
     live: Dict[str, dict] = {}
@@ -72,7 +74,17 @@ def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_
             live[rid] = {"toks": toks, "pos": 0, "prompt": max(1, int(len(toks) * prompt_frac))}
             held += round64(len(toks))
         assert live, "max_tokens is too small for the next request"
-        entries, end = [], []
+        entries, end, cuts = [], [], []
+        if cut_every and len(steps) % cut_every == cut_every - 1:
+            cand = [r for r, st in live.items() if st["pos"] > 1]
+            if cand:
+                rid = rng.choice(cand)
+                st = live[rid]
+                keep = rng.randrange(0, st["pos"])
+                cuts.append({"id": rid, "keep": keep})
+                # what was computed behind the cut is a prompt now: it comes again in portions
+                st["prompt"] = max(st["prompt"], st["pos"])
+                st["pos"] = kept(st["pos"], keep)
         for rid, st in list(live.items()):
             if len(live) > 1 and rng.random() < 0.2:
                 continue                                   # left out of this step
@@ -88,8 +100,8 @@ def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_
                 end.append(rid)
                 held -= round64(len(toks))
                 del live[rid]
-        if entries:
-            steps.append({"step": len(steps), "entries": entries, "end": end})
+        if entries or cuts:
+            steps.append({"step": len(steps), "entries": entries, "end": end, **({"truncate": cuts} if cuts else {})})
     return steps
 
 
@@ -97,7 +109,9 @@ def replay_in_process(replayer, steps: List[dict]):
     """Yields (request id, position, logits row) for every wanted row."""
     pos: Dict[str, int] = {}
     for rec in steps:
-        out = replayer.run_step(rec["entries"], rec["end"])
+        out = replayer.run_step(rec["entries"], rec["end"], rec.get("truncate", ()))
+        for t in rec.get("truncate", ()):
+            pos[t["id"]] = replayer.kept_after_truncate(pos[t["id"]], t["keep"])
         r = 0
         for e in rec["entries"]:
             base = pos.get(e["id"], 0)

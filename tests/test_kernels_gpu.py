@@ -294,6 +294,18 @@ def test_sampling_distribution():
 
 # ---- tensor-core attention -----------------------------------------------------------------
 
+def _torch_attention(q_row, kc, vc, table_row, pos, H, KV, hs, scale, window=0):
+    """One query row [H * hs] at position ``pos`` against the pages of its sequence, in float32 with torch
+    alone (no kernel of the package): softmax(scale q K^T) V over keys first..pos."""
+    G = H // KV
+    n_blocks = pos // kc.shape[2] + 1
+    k = kc[table_row[:n_blocks].long()].float().permute(1, 0, 2, 3).reshape(KV, -1, hs)[:, :pos + 1]
+    v = vc[table_row[:n_blocks].long()].float().permute(1, 0, 2, 3).reshape(KV, -1, hs)[:, :pos + 1]
+    first = max(0, pos - window + 1) if window else 0
+    sc = torch.einsum("kgd,kjd->kgj", q_row.float().view(KV, G, hs), k[:, first:]) * scale
+    return torch.einsum("kgj,kjd->kgd", torch.softmax(sc, -1), v[:, first:]).reshape(-1)
+
+
 def _items_for(lengths, tails, dec_tokens, por_tokens):
     """Rows = the last ``tails[s]`` tokens of each sequence, cut into kernel items."""
     dec, por, rows = [], [], []
@@ -583,6 +595,10 @@ def test_attention_decode_at_serving_size(batch, ctx, nsplit, tma):
     run()
     assert status.item() == 0
     assert (out.float() - want.float()).abs().max().item() <= 2 ** -8 * 4       # outputs of size up to ~4 in bf16
+    # and against torch alone, so that the yardstick is not a kernel of the package: the first, a middle and the last row
+    for s_ in sorted({0, batch // 2, batch - 1}):
+        ref = _torch_attention(q[s_], kc, vc, table[s_], lens[s_] - 1, H, KV, hs, scale)
+        assert (out[s_].float() - ref).abs().max().item() <= 2 ** -8 * 4, f"sequence {s_} against torch"
     for _ in range(3):
         run()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -764,9 +780,12 @@ def test_gemm_tc05_at_prefill_size():
             torch.cuda.synchronize()
             res[label] = e0.elapsed_time(e1) * 100
         assert status.item() == 0
+        out.fill_(float("nan"))
         ops().gemm_tc05(a, w, out, status)
-        want = a[:64].double() @ w.double().T
-        assert (out[:64].double() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item()
+        want = a.double() @ w.double().T                     # every element of every tile
+        assert not torch.isnan(out).any()
+        assert (out.double() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item()
+        del want
         tf = 2.0 * M * N * K / 1e6
         print(f"{name}: tcgen05 {res['tcgen05']:.1f} us ({tf / res['tcgen05']:.0f} TFLOP/s), "
               f"library {res['library']:.1f} us ({tf / res['library']:.0f} TFLOP/s)")
@@ -797,6 +816,9 @@ def test_attention_portion_at_prefill_size():
         run()
         assert status.item() == 0 and not torch.isnan(out).any()
         assert (out[rows].float() - want.float()).abs().max().item() <= 2 ** -8 * 4
+        for r in rows.tolist():                            # and against torch alone
+            ref = _torch_attention(q[r], kc, vc, table[0], r, H, KV, hs, scale)
+            assert (out[r].float() - ref).abs().max().item() <= 2 ** -8 * 4, f"{label}: row {r} against torch"
         for _ in range(2):
             run()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

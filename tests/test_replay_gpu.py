@@ -335,3 +335,275 @@ def test_a_name_used_again(folders, plains, dtype):
             ref = plains[name].of(toks)[start + w]
             assert (out[w].double().cpu() - ref).abs().max().item() <= ATOL[dtype], (rid, start + w)
     rp.runner.manager.check_invariant()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_replay_with_requests_cut_back(folders, plains, name, dtype):
+    """The mixed replay with a "truncate" record every few steps: a live request is cut back to a random
+    length as a preemption cuts it (whole pages stay, the rest goes back to the pool and is used by others),
+    and its cut tokens are computed again in portions beside the other requests. Every row that is computed
+    again, and every row after it, against the plain implementation."""
+    reqs = requests_of(name)
+    page = CONFIGS[name][2]
+    max_tokens = ru.round64(max(len(t) for t in reqs.values())) + 128
+    kept = lambda held, keep: min(keep // page * page, held // page * page)
+    steps = ru.trace_mixed(reqs, max_tokens, seed=13, cut_every=3, kept=kept)
+    cuts = [t for s in steps for t in s.get("truncate", ())]
+    assert len(cuts) >= 4
+    rp = replayer(folders[name], name, dtype, max_tokens)
+    assert all(rp.kept_after_truncate(h, k) == kept(h, k) for h, k in ((37, 20), (64, 64), (5, 100), (200, 17)))
+    worst = ru.compare(rp, steps, reqs, plains[name], ATOL[dtype], f"{name}/cut back/{dtype}")
+    rp.runner.manager.check_invariant()
+    assert not rp.runner.manager.requests
+    assert rp.runner.manager.free_pages(0) == rp.runner.manager.groups[0].pool.num_pages
+    print(f"{name} cut back {dtype}: {len(cuts)} cuts, worst difference {worst:.2e}")
+
+
+def test_trace_run_program_with_truncate_records(folders, plains, tmp_path):
+    """The "truncate" record through the program itself, in bfloat16."""
+    name = "C"
+    reqs = requests_of(name)
+    page = CONFIGS[name][2]
+    max_tokens = 384 + 128
+    kept = lambda held, keep: min(keep // page * page, held // page * page)
+    steps = ru.trace_mixed(reqs, max_tokens, seed=5, cut_every=4, kept=kept)
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[name], "--dtype", "bfloat16",
+         "--out", str(out), "--max-tokens", str(max_tokens), "--page-size", str(page)],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    import numpy as np
+    V = CONFIGS[name][0]["vocab_size"]
+    pos, checked = {}, 0
+    for s in steps:
+        for t in s.get("truncate", ()):
+            pos[t["id"]] = kept(pos[t["id"]], t["keep"])
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        if n_want == 0:
+            continue
+        got = torch.from_numpy(np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(n_want, V))
+        r = 0
+        for e in s["entries"]:
+            base = pos.get(e["id"], 0)
+            for w in e["want"]:
+                ref = plains[name].of(reqs[e["id"]])[base + w]
+                assert (got[r].double() - ref).abs().max().item() <= ATOL[torch.bfloat16], (s["step"], e["id"], base + w)
+                r += 1
+                checked += 1
+            pos[e["id"]] = base + len(e["tokens"])
+    assert checked > 100
+
+
+@pytest.mark.parametrize("name", ["C"])
+def test_graph_decode_logits_at_17_to_64_rows(folders, plains, name):
+    """Decode steps of 17 to 64 live requests, bfloat16, through the recorded step: above 16 rows every
+    projection leaves the few-row product, the gate/up product and the activation are two kernels, decode
+    attention gets more items than one wave of shares, and the buckets 24, 32, 48 and 64 are recorded.
+    Every row of every step against the plain implementation."""
+    import random
+    from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
+    from llm_steadyinfer_b200.weights import load_model
+    cfg, cseed, page = CONFIGS[name]
+    rng = random.Random(3)
+    lengths = [rng.choice([3, 17, 33, 64, 65, 90, 129, 150]) for _ in range(64)]
+    extra = 14
+    reqs = {f"g{i}": ru.random_tokens(cfg["vocab_size"], n + extra, 8000 + i) for i, n in enumerate(lengths)}
+    model = load_model(folders[name], torch.bfloat16, "cuda:0")
+    pages = sum(-(-(n + extra) // page) for n in lengths) + 8
+    rn = ModelRunner(model, page_size=page, num_pages=pages, max_requests=64, max_step_tokens=1024)
+    pos = {}
+    ids = list(reqs)
+    for a in range(0, 64, 8):                                   # prompts, eight requests a step
+        rn.step([StepEntry(r, reqs[r][:lengths[int(r[1:])]], []) for r in ids[a:a + 8]])
+    for r in ids:
+        pos[r] = lengths[int(r[1:])]
+    worst, sizes = 0.0, []
+    for step, size in enumerate([64, 17, 33, 24, 48, 64, 17, 40, 64, 20, 33, 64, 25, 57]):
+        chosen = rng.sample([r for r in ids if pos[r] < len(reqs[r])], size)
+        logits = rn.step_decode_graph([StepEntry(r, [reqs[r][pos[r]]], [0]) for r in chosen])
+        sizes.append(size)
+        got = logits.double().cpu()
+        for i, r in enumerate(chosen):
+            d = (got[i] - plains[name].of(reqs[r])[pos[r]]).abs().max().item()
+            assert d <= ATOL[torch.bfloat16], f"step {step} of {size} rows, request {r} at position {pos[r]}: {d:.3e}"
+            worst = max(worst, d)
+            pos[r] += 1
+    rn.check_status()
+    assert {b for b, _ in rn._graphs} >= {24, 32, 48, 64} and not rn.capture_failed
+    print(f"{name} graph decode at {sorted(set(sizes))} rows: worst difference {worst:.2e}")
+
+
+def test_graph_decode_logits_at_33_rows_8b_layer_shape(tmp_path_factory):
+    """The same at the widths of one Llama-3.1-8B block (small vocabulary): 33 and 20 live requests, bfloat16,
+    recorded steps; the projections run as library products here and decode attention on the TMA kernel.
+    Allowed: three times the error that the plain implementation predicts with bf16 roundings."""
+    import plain_llama
+    from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
+    from llm_steadyinfer_b200.weights import load_model, write_random_model
+    folder = str(tmp_path_factory.mktemp("layer8b_rows") / "m")
+    write_random_model(folder, LAYER_8B, 6, torch.bfloat16)
+    plain = ru.PlainLogits(folder)
+    lengths = [5 + (7 * i) % 40 for i in range(33)]
+    extra = 4
+    reqs = {f"h{i}": ru.random_tokens(LAYER_8B["vocab_size"], n + extra, 8100 + i) for i, n in enumerate(lengths)}
+    toks = reqs["h32"]
+    atol = 3 * (plain_llama.forward(plain.cfg, plain.w, toks, round_to=torch.bfloat16) - plain.of(toks)).abs().max().item()
+    model = load_model(folder, torch.bfloat16, "cuda:0")
+    rn = ModelRunner(model, page_size=16, num_pages=33 * 4, max_requests=48, max_step_tokens=1024)
+    ids = list(reqs)
+    rn.step([StepEntry(r, reqs[r][:lengths[i]], []) for i, r in enumerate(ids)])
+    pos = {r: lengths[i] for i, r in enumerate(ids)}
+    worst = 0.0
+    for step, chosen in enumerate([ids, ids[:20], ids[5:], ids]):
+        chosen = [r for r in chosen if pos[r] < len(reqs[r])]
+        logits = rn.step_decode_graph([StepEntry(r, [reqs[r][pos[r]]], [0]) for r in chosen]).double().cpu()
+        for i, r in enumerate(chosen):
+            d = (logits[i] - plain.of(reqs[r])[pos[r]]).abs().max().item()
+            assert d <= atol, f"step {step} of {len(chosen)} rows, request {r} at position {pos[r]}: {d:.3e} (allowed {atol:.2e})"
+            worst = max(worst, d)
+            pos[r] += 1
+    rn.check_status()
+    print(f"8B layer shape, 20 to 33 decode rows: worst difference {worst:.2e} (allowed {atol:.2e})")
+
+
+LONG = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 512, "intermediate_size": 1024, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 128,
+    "vocab_size": 500, "max_position_embeddings": 16384, "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True, "hidden_act": "silu", "attention_bias": False,
+    "mlp_bias": False, "torch_dtype": "bfloat16", "bos_token_id": 0, "eos_token_id": 1,
+}
+
+
+@pytest.fixture(scope="module")
+def long_model(tmp_path_factory):
+    """The folder of the long-context model and its plain logits (half a minute on the host: made once)."""
+    from safetensors.torch import load_file
+    from llm_steadyinfer_b200.weights import write_random_model, write_safetensors
+    folder = str(tmp_path_factory.mktemp("long") / "m")
+    write_random_model(folder, LONG, 7, torch.bfloat16)
+    path = os.path.join(folder, "model.safetensors")
+    t = load_file(path)
+    for k in t:
+        if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
+            t[k] = (t[k].float() * 3.0).to(torch.bfloat16)
+    write_safetensors(path, t)
+    plain = ru.PlainLogits(folder)
+    toks = ru.random_tokens(LONG["vocab_size"], 9016, 1)
+    plain.of(toks)
+    return folder, plain, toks
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_long_context_replay(long_model, dtype):
+    """A narrow model with the Llama-3.1-8B head size and frequency scaling taken to 9,016 tokens: the prompt in
+    portions of 2,048 up to 8,152, 80 tokens one by one across position 8,192, a further portion up to 9,000 and
+    16 more tokens, with a short request decoding beside it (so that the long one is cut into many more shares
+    than the short one). Block tables of 564 pages, decode attention in up to 32 splits, positions beyond the
+    original range of the scaled frequencies. The query and key projections are scaled up so that the softmax
+    picks out few keys at whatever distance they lie, and a fault in one far tile shows in the logits."""
+    import plain_llama
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    folder, plain, long_toks = long_model
+    V = LONG["vocab_size"]
+    short_toks = ru.random_tokens(V, 40 + 96, 2)
+    ref = plain.of(long_toks)
+    steps, p = [], 0
+
+    def portion(n, beside=None):
+        nonlocal p
+        want = sorted(set(range(0, n, 97)) | {n - 1})
+        e = [{"id": "L", "tokens": long_toks[p:p + n], "want": want}]
+        if beside is not None:
+            e.append(beside)
+        steps.append({"step": len(steps), "entries": e, "end": []})
+        p += n
+
+    sp = 0
+
+    def short_row():
+        nonlocal sp
+        if sp == 0:
+            e, sp = {"id": "S", "tokens": short_toks[:40], "want": [39]}, 40
+        else:
+            e, sp = {"id": "S", "tokens": [short_toks[sp]], "want": [0]}, sp + 1
+        return e
+
+    for n in (2048, 2048, 2048, 2008):
+        portion(n)
+    for _ in range(80):
+        portion(1, short_row())
+    portion(768)
+    for _ in range(16):
+        portion(1, short_row())
+    steps[-1]["end"] = ["L", "S"]
+    assert p == 9016 and sp == 136
+    reqs = {"L": long_toks, "S": short_toks}
+    if dtype == torch.float32:
+        atol = 5e-5
+    else:
+        probe = long_toks[:600]
+        atol = 3 * (plain_llama.forward(plain.cfg, plain.w, probe, round_to=torch.bfloat16) - plain.of(probe)).abs().max().item()
+    rp = Replayer(folder, dtype, max_tokens=9088 + 192, page_size=16)
+    worst = ru.compare(rp, steps, reqs, plain, atol, f"long context/{dtype}")
+    assert not rp.runner.manager.requests
+    rp.runner.manager.check_invariant()
+    print(f"long context {dtype}: worst difference {worst:.2e} (allowed {atol:.2e}); logits up to {ref.abs().max().item():.1f}")
+
+
+def test_random_weights_drawn_on_the_gpu_equal_a_written_folder(tmp_path):
+    """``init_random`` on the device and ``write_random_model`` on the host give the same tensors, bit for bit."""
+    from llm_steadyinfer_b200.config import config_from_dict
+    from llm_steadyinfer_b200.models import Model
+    from llm_steadyinfer_b200.weights import init_random, load_model, write_random_model
+    cfg = CONFIGS["B"][0]
+    folder = str(tmp_path / "m")
+    write_random_model(folder, cfg, 4, torch.bfloat16)
+    a = load_model(folder, torch.bfloat16, "cuda:0")
+    b = Model(config_from_dict(cfg), torch.bfloat16, "cuda:0")
+    init_random(b, seed=4)
+    assert torch.equal(a.embed, b.embed) and torch.equal(a.lm_head, b.lm_head)
+    assert torch.equal(a.final_norm.weight, b.final_norm.weight)
+    for x, y in zip(a.blocks, b.blocks):
+        assert torch.equal(x.mixer.qkv, y.mixer.qkv) and torch.equal(x.mixer.o, y.mixer.o)
+        assert torch.equal(x.feed_forward.gate_up, y.feed_forward.gate_up) and torch.equal(x.feed_forward.down, y.feed_forward.down)
+        assert torch.equal(x.mixer_norm.weight, y.mixer_norm.weight)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_8b_shape_drawn_on_the_gpu_against_plain_on_the_same_draw(dtype):
+    """One block of the Llama-3.1-8B shape with its weights drawn on the device, as the benchmark draws its 32
+    blocks, against the plain implementation on the same draw made on the host: the counter-based draw is what
+    lets a model that was never written to disk be checked."""
+    import plain_llama
+    from llm_steadyinfer_b200.config import config_from_dict
+    from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
+    from llm_steadyinfer_b200.models import Model
+    from llm_steadyinfer_b200.weights import init_random
+    from llm_steadyinfer_b200.weights.random_init import random_tensors
+    cfg = config_from_dict(LAYER_8B)
+    model = Model(cfg, dtype, "cuda:0")
+    init_random(model, seed=12)
+    w = {k: v.double() for k, v in random_tensors(Model(cfg, torch.float32, "cpu"), 12, torch.bfloat16).items()}
+    toks = ru.random_tokens(LAYER_8B["vocab_size"], 150, 5)
+    want = plain_llama.forward(LAYER_8B, w, toks)
+    rn = ModelRunner(model, page_size=16, num_pages=16, max_requests=2, max_step_tokens=256)
+    rows = [0, 1, 63, 127, 128]
+    got = rn.step([StepEntry("r", toks[:129], rows)]).double().cpu()
+    tail = [rn.step([StepEntry("r", [toks[p]], [0])]).double().cpu()[0] for p in range(129, 150)]
+    rn.check_status()
+    if dtype == torch.float32:
+        atol = 5e-5
+    else:
+        atol = 3 * (plain_llama.forward(LAYER_8B, w, toks, round_to=torch.bfloat16) - want).abs().max().item()
+    for r, g in list(zip(rows, got)) + list(zip(range(129, 150), tail)):
+        d = (g - want[r]).abs().max().item()
+        assert d <= atol, f"position {r}: {d:.3e} (allowed {atol:.2e})"
