@@ -171,12 +171,37 @@ def main() -> int:
         runner.step([StepEntry("prefill", ptoks, [PT - 1])])
         runner.finish("prefill")
 
+    def kernel_time_shares():
+        """Share of the summed kernel time per kind of kernel, for one prompt step of 2,048 tokens and one direct
+        (not recorded) decode step of the bench's batch and context; events sit between the kernels, so these
+        are shares, not the step's time."""
+        from llm_steadyinfer_b200.engine.kernel_times import KernelTimes
+        out = {}
+        with KernelTimes() as kt:
+            prefill_once(0)
+        out["prefill"] = {k: v["share"] for k, v in kt.report().items()}
+        ids = [f"k{i}" for i in range(B)]
+        for r in ids:
+            mgr.admit(r)
+            mgr.grow(r, CTX - 8)
+            mgr.commit(r, CTX - 8)
+        step = lambda: llm.sampler.sample(runner.step([StepEntry(r, [1], [0]) for r in ids]), [(SamplingParams(), 0, 0)] * B)
+        step()
+        with KernelTimes() as kt:
+            step()
+        out["decode"] = {k: v["share"] for k, v in kt.report().items()}
+        for r in ids:
+            runner.finish(r)
+        return out
+
     if args.section == "decode":
         pre_ms = own_ms = float("nan")
     else:
         for i in range(3):
             prefill_once(i)
         runner.check_status()
+        pre_clocks = ClockSampler()
+        pre_clocks.start()
         pre_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
         # the same step with every many-row product on this package's tcgen05 kernel (none in the library)
         from llm_steadyinfer_b200.parts import linear as linear_mod
@@ -187,6 +212,7 @@ def main() -> int:
         runner.check_status()
         own_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
         linear_mod.USE_OWN_GEMM = was
+        pre_clocks.stop()
     if args.section == "prefill":
         print(json.dumps({"section": "prefill", "tokens": PT, "ms": round(pre_ms, 3), "own_gemm_ms": round(own_ms, 3)}))
         return 0
@@ -196,13 +222,16 @@ def main() -> int:
                "own_gemm_ms": round(own_ms, 3)}          # with no product in the library (SI_OWN_GEMM=1)
     if "bf16_tflops_sustained" in pk:                     # the prompt step is tens of milliseconds of products
         prefill["frac_of_sustained"] = round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+    prefill["clocks"] = pre_clocks.summary()
 
     # ---- decode on the device: contexts filled synthetically, fixed next tokens ----------------
     for t in runner.storage.keys + runner.storage.values:
         t.normal_(0.0, 0.5)
 
-    def decode_run(batch, steps, warm, sample=True):
-        start = CTX - (steps + warm) - 1
+    def decode_run(batch, steps, warm, sample=True, ctx_end=None):
+        """``steps`` timed decode steps of ``batch`` requests after ``warm`` untimed ones; the contexts end at
+        ``ctx_end`` tokens (default: the bench's context length)."""
+        start = (ctx_end or CTX) - (steps + warm) - 1
         ids = [f"d{i}" for i in range(batch)]
         for r in ids:
             mgr.admit(r)
@@ -231,25 +260,42 @@ def main() -> int:
         mean_ctx = start + warm + (steps - 1) / 2 + 1
         return ms, launches, mean_ctx
 
+    def hbm_frac(batch, mean_ctx, step_ms):
+        """Bytes a decode step has to read (every weight once, the cache of the live requests) over its time."""
+        step_bytes = weight_bytes + batch * mean_ctx * kv_bytes_per_token + batch * d * 2
+        achieved = step_bytes / (step_ms * 1e-3) / 1e9
+        return achieved, achieved / pk["hbm_gbs"]
+
     clocks.start()
     ms, launches, mean_ctx = decode_run(B, K, W)
     clocks.stop()
     ms_per_step = ms / K
     value = B * K / ms * 1e3
-    step_bytes = weight_bytes + B * mean_ctx * kv_bytes_per_token + B * d * 2
-    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    achieved, frac = hbm_frac(B, mean_ctx, ms_per_step)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
+                "frac": round(frac, 4), "peaks": pk_src}
 
     if args.section == "decode":
         print(json.dumps({"section": "decode", "ms_per_step": round(ms_per_step, 4), "roofline": roofline,
                           "gpu_launches": launches}))
         return 0
+    # Further points: batch 1 and 64 at the bench's context, and the workload of the baseline configuration
+    # (1,024-token prompts, 256 generated tokens: contexts from 1,024 to 1,280) at batch 1, 8 and 64. Each with
+    # tokens a second, milliseconds a step and the fraction of the memory roofline.
     points = {}
     if not args.no_points:
+        def point(name, b, steps, ctx_end=None):
+            pm, _, mc = decode_run(b, steps, 4, ctx_end=ctx_end)
+            points[name] = round(b * steps / pm * 1e3, 1)
+            points[name + "_ms"] = round(pm / steps, 4)
+            points[name + "_frac"] = round(hbm_frac(b, mc, pm / steps)[1], 4)
         for b in (1, 64):
-            pm, _, _ = decode_run(b, min(K, 32), 4)
-            points[f"decode_b{b}"] = round(b * min(K, 32) / pm * 1e3, 1)
+            point(f"decode_b{b}", b, min(K, 32))
+        for b in (1, 8, 64):
+            point(f"decode_b{b}_ctx1280", b, 256, ctx_end=1280)
+    kernel_times = {}
+    if not args.no_points:
+        kernel_times = kernel_time_shares()
 
     # ---- end to end through the Python entry point -------------------------------------------
     # The prompts are prefilled in portions, so the first requests decode while the last ones are still in
@@ -285,7 +331,7 @@ def main() -> int:
                    "heads": H, "kv_heads": KV, "head_dim": hs, "intermediate": F, "vocab": V,
                    "global_batch": B, "seq_len": CTX, "prefill_tokens": PT, "page_size": PAGE,
                    "parallelism": "single_gpu", "cuda_graph": True, "l2": "inputs larger than L2 (weights 16 GB)"},
-        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e, "kernel_time_shares": kernel_times,
         "gpu_launches": launches, "clocks": clocks.summary(),
     }
     print(json.dumps(out))

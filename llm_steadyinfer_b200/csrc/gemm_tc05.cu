@@ -191,17 +191,6 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem, 2 * BN);
 }
 
-static int si_sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 1;
-  }
-  return n;
-}
-
 template <int STAGES, typename TO, bool SWIGLU>
 static int launch(const CUtensorMap& am, const CUtensorMap& bm, void* out, long long ldo, int M, int N, int K,
                   int* status, cudaStream_t stream) {

@@ -31,6 +31,16 @@ def configure_library_gemm() -> None:
     torch.backends.cuda.matmul.allow_tf32 = False
 
 
+def library_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """The library product (cuBLAS behind ``torch.mm``), bf16 inputs, fp32 accumulation."""
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        raise ops.KernelError(f"linear: unsupported output dtype {out.dtype}")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if not x.is_cuda:
         raise ops.KernelError("linear: CUDA tensors only; there is no CPU path")
@@ -42,12 +52,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
           and ops.gemm_tc05_ok(x, w, out)):
         ops.gemm_tc05(x, w, out)
     elif x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        if out.dtype == torch.bfloat16:
-            torch.mm(x, w.t(), out=out)
-        elif out.dtype == torch.float32:
-            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
-        else:
-            raise ops.KernelError(f"linear: unsupported output dtype {out.dtype}")
+        library_mm(x, w, out)
     else:
         raise ops.KernelError(f"linear: unsupported dtypes x={x.dtype} w={w.dtype} out={out.dtype}")
     return out
