@@ -88,6 +88,139 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(mhz)}
 
 
+def write_reference_weights(path: str, cfg: dict, seq_len: int, layers: int) -> int:
+    """A weights file in the reference's own format for the shape ``cfg``: the 36-byte header and raw fp32
+    tensors in its grouped order (src/source/model/llama3.cpp:307-431), matrices ~ N(0, 0.02), norm weights 1.
+    The values are one 64 MiB block of draws written over and over (the file is 32 GB at the 8B shape; timing
+    does not depend on the values, only on their not being all alike). Returns the bytes written."""
+    import struct
+    import numpy as np
+    d, F, H, KV, V = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
+                      cfg["num_key_value_heads"], cfg["vocab_size"])
+    hs = d // H
+    L = layers
+    rng = np.random.default_rng(0)
+    tile = (rng.standard_normal(1 << 24) * 0.02).astype("<f4")
+    ones = np.ones(1 << 20, dtype="<f4")
+    total = 0
+    with open(path, "wb", buffering=1 << 24) as f:
+        f.write(struct.pack("<8if", d, F, L, H, KV, -V, seq_len, 0, float(cfg["rope_theta"])))   # negative: untied head
+        total += 36
+
+        def put(n, src):
+            nonlocal total
+            while n > 0:
+                k = min(n, src.size)
+                f.write(memoryview(src[:k]))
+                n -= k
+                total += 4 * k
+        put(V * d, tile)                       # embedding
+        put(L * d, ones)                       # attention norms
+        put(L * H * hs * d, tile)              # wq
+        put(L * KV * hs * d, tile)             # wk
+        put(L * KV * hs * d, tile)             # wv
+        put(L * d * H * hs, tile)              # wo
+        put(L * d, ones)                       # feed-forward norms
+        put(L * F * d, tile)                   # w1
+        put(L * d * F, tile)                   # w2
+        put(L * F * d, tile)                   # w3
+        put(d, ones)                           # final norm
+        put(seq_len * hs, ones)                # the skipped frequency tables
+        put(V * d, tile)                       # output head
+    return total
+
+
+def reference_arm(args) -> int:
+    """The same decode workload through the unmodified reference project: its binary (built by
+    baseline/build_ref.py from the reference's sources, continuous KV layout) reads a random weights file of the
+    same shape and runs ``Model::decode_step`` (device-timed ``value``) and ``Scheduler::step`` (``e2e``).
+    Prints the JSON line of the contract with "impl": "reference", or why it is unavailable."""
+    import shutil
+    import tempfile
+
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())}))
+        return 0
+
+    try:
+        gpus = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=60)
+        if gpus.returncode != 0 or "GPU 0" not in gpus.stdout:
+            return unavailable("no CUDA device on this machine (nvidia-smi -L lists none)")
+    except (OSError, subprocess.TimeoutExpired):
+        return unavailable("no CUDA device on this machine (nvidia-smi cannot be run)")
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import build_ref
+    except ImportError as e:
+        return unavailable(f"baseline/build_ref.py cannot be imported: {e}")
+    exe = build_ref.binary_path()
+    if not os.path.isfile(exe):
+        ref = build_ref.default_reference()
+        if not os.path.isdir(ref):
+            return unavailable("the reference is a CMake/C++ project without a Python package (pip has nothing to install); "
+                               "its binary baseline/_ref/ref_bench has not been built and its sources are not on this machine")
+        try:
+            build_ref.build(ref, verbose=False)
+        except Exception as e:      # noqa: BLE001
+            return unavailable(f"building the reference failed: {e}")
+    K, W = args.steps, max(3, args.warmup)
+    B, CTX = args.batch, args.context
+    cfg = dict(LLAMA_3_1_8B)
+    L = args.layers or cfg["num_hidden_layers"]
+    d, F, V, H, KV = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hs = d // H
+    floats = 2 * V * d + L * (2 * d + 2 * H * hs * d + 2 * KV * hs * d + 3 * F * d) + d + CTX * hs
+    need = 4 * floats + 36
+    folder = None
+    for cand in (os.environ.get("TMPDIR"), tempfile.gettempdir(), "/dev/shm"):
+        if cand and os.path.isdir(cand) and shutil.disk_usage(cand).free > need + (4 << 30):
+            folder = tempfile.mkdtemp(prefix="si_ref_", dir=cand)
+            break
+    if folder is None:
+        return unavailable(f"no temporary folder has room for the reference's {need >> 30} GB fp32 weights file")
+    path = os.path.join(folder, "llama31_8b_shape.bin")
+    rows = max(B, args.ref_rows)
+    clocks = ClockSampler()
+    try:
+        write_reference_weights(path, cfg, CTX, L)
+        env = dict(os.environ, SHIM_VOCAB=str(V))
+        clocks.start()
+        proc = subprocess.run([exe, "bench", path, str(B), str(CTX), str(K), str(W), str(rows)], env=env,
+                              capture_output=True, text=True, timeout=1500)
+        clocks.stop()
+    except subprocess.TimeoutExpired:
+        clocks.stop()
+        return unavailable("the reference's run did not end within 25 minutes")
+    except OSError as e:
+        return unavailable(f"the reference's binary could not be run: {e}")
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    lines = [l for l in proc.stdout.strip().splitlines() if l.startswith("{")]
+    if proc.returncode != 0 or not lines:
+        return unavailable(f"the reference's run failed (exit {proc.returncode}): {(lines[-1] if lines else proc.stderr[-300:])}")
+    r = json.loads(lines[-1])
+    if "error" in r:
+        return unavailable(f"the reference's run failed: {r['error']}")
+    ms_per_step = r["device_ms"] / K
+    out = {
+        "metric": "decode tokens/s, Llama-3.1-8B shape, batch 8, context 8192", "value": round(B * K / r["device_ms"] * 1e3, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (its stock dtype; products in TF32)",
+        "data": "synthetic: random weights, random token ids", "impl": "reference",
+        "config": {"model": "Llama-3.1-8B shape", "layers": L, "layers_full": cfg["num_hidden_layers"], "hidden": d, "heads": H,
+                   "kv_heads": KV, "head_dim": hs, "intermediate": F, "vocab": V, "global_batch": B, "seq_len": CTX,
+                   "parallelism": "single_gpu", "cuda_graph": True, "kv_layout": "continuous (USE_PAGED_ATTENTION off)",
+                   "scheduler_rows": rows},
+        "e2e": {"value": round(r["e2e_tokens"] / r["e2e_s"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"],
+                "context_at_start": r["e2e_context_start"], "requests_running_at_end": r["running_at_end"],
+                "prefill_steps": r["prefill_steps"], "prefill_s": r["prefill_s"]},
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -98,6 +231,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--ref-rows", type=int, default=32,
+                    help="--impl reference: rows a step of its scheduler (its max_batch_size, which also caps a prompt portion)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region of --section with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off)")
@@ -105,15 +240,11 @@ def main() -> int:
                     help="run only the device-timed decode steps or only the prefill (for profiling)")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake/C++ project with no Python package and no offline "
-                          "dependencies (glog, armadillo, sentencepiece, re2 tarballs are not shipped); "
-                          "pip cannot install it and its default CUDA path computes wrong attention"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
     K, W = args.steps, max(3, args.warmup)
 
     import torch
@@ -203,10 +334,10 @@ def main() -> int:
         pre_clocks = ClockSampler()
         pre_clocks.start()
         pre_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
-        # the same step with every many-row product on this package's tcgen05 kernel (none in the library)
+        # for comparison: the same step with the library product (cuBLAS) in place of this package's tcgen05 kernel
         from llm_steadyinfer_b200.parts import linear as linear_mod
         was = linear_mod.USE_OWN_GEMM
-        linear_mod.USE_OWN_GEMM = True
+        linear_mod.USE_OWN_GEMM = False
         for i in range(2):
             prefill_once(i)
         runner.check_status()
@@ -214,12 +345,12 @@ def main() -> int:
         linear_mod.USE_OWN_GEMM = was
         pre_clocks.stop()
     if args.section == "prefill":
-        print(json.dumps({"section": "prefill", "tokens": PT, "ms": round(pre_ms, 3), "own_gemm_ms": round(own_ms, 3)}))
+        print(json.dumps({"section": "prefill", "tokens": PT, "ms": round(pre_ms, 3), "library_gemm_ms": round(own_ms, 3)}))
         return 0
     pre_flops = 2 * PT * block_params + L * 4 * H * hs * PT * (PT + 1) / 2 + 2 * V * d
     prefill = {"value": round(PT / pre_ms * 1e3, 1), "tokens": PT, "ms": round(pre_ms, 3),
                "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-               "own_gemm_ms": round(own_ms, 3)}          # with no product in the library (SI_OWN_GEMM=1)
+               "library_gemm_ms": round(own_ms, 3)}      # the same step with cuBLAS for the products (SI_OWN_GEMM=0)
     if "bf16_tflops_sustained" in pk:                     # the prompt step is tens of milliseconds of products
         prefill["frac_of_sustained"] = round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
     prefill["clocks"] = pre_clocks.summary()

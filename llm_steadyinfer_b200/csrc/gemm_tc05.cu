@@ -191,6 +191,168 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem, 2 * BN);
 }
 
+
+// The same product with two CTAs (a cluster of two, on neighbouring SMs) on one 256 x 256 tile: each CTA fetches
+// its 128 rows of x and its 128 of the tile's 256 rows of W per k step (32 KB instead of 48 KB a stage, so six
+// stages fit), the leader CTA issues tcgen05.mma.cta_group::2 over both CTAs' shared memory, and each CTA ends
+// up with its 128 rows of the accumulator in its own tensor memory, which its four epilogue warps store. Per
+// output a CTA reads a third less from L2 and each CTA reads only half of the W tile from shared memory; at the
+// power cap, where long products run, that energy is what sets their time. Loads are plain TMA loads, one box per
+// CTA, their bytes counted at the leader's barrier; only arrivals are sent to both CTAs (tcgen05.commit).
+// Barriers: full[s] (leader: one arrival with the bytes of all four boxes), empty[s] (each CTA: the commit
+// after the stage's instructions), acc_full[b] (each CTA: the commit after a tile's last instruction),
+// acc_empty[b] (leader: the eight epilogue warps of both CTAs).
+template <int STAGES, typename TO, bool SWIGLU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192)
+gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
+                      TO* __restrict__ out, long long ldo, int M, int N, int K, int* status) {
+  constexpr int BM = 128, BN = 256, BK = 64;             // BM, and BN / 2 rows of W, per CTA
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
+  __shared__ unsigned tmem_slot;
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* As = smem;
+  unsigned char* Bs = smem + STAGES * A_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_cta_rank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  const int nk = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }   // 4 epilogue warps of each CTA
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(&tmem_slot, 2 * BN);
+  tc05_fence_before_sync();
+  cluster_sync_all();                                     // both CTAs' barriers and tensor memory are ready
+  tc05_fence_after_sync();
+  const unsigned tmem = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok; tile += pairs) {
+        const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
+        const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty_bar[s], (unsigned)(((it / STAGES) - 1) & 1))) {
+            set_status(status, SI_WAIT_LIMIT);
+            ok = false;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * (A_BYTES + B_BYTES));
+          const unsigned bar = cluster_map_u32(&full_bar[s], 0);
+          tma_load_2d_pair(As + s * A_BYTES, &amap, bar, kb * BK, m0);
+          tma_load_2d_pair(Bs + s * B_BYTES, &bmap, bar, kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0) {
+      constexpr unsigned idesc = umma_idesc_bf16(2 * BM, BN, false);
+      const unsigned long long ad0 = umma_desc_sw128(As, 16, 1024), bd0 = umma_desc_sw128(Bs, 16, 1024);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
+        const int buf = local & 1;
+        if (local >= 2) ok = mbar_wait_warp(&acc_empty[buf], (unsigned)(((local >> 1) - 1) & 1));
+        if (!ok) break;
+        tc05_fence_after_sync();
+        const unsigned acc = tmem + buf * BN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait_warp(&full_bar[s], (unsigned)((it / STAGES) & 1));
+          if (!ok) break;
+          tc05_fence_after_sync();
+          const unsigned long long ad = ad0 + (unsigned)s * (A_BYTES / 16), bd = bd0 + (unsigned)s * (B_BYTES / 16);
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              tc05_mma_bf16_pair(acc, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc05_commit_pair(&empty_bar[s], 3);     // both CTAs' stages are free once these have read them
+            if (kb == nk - 1) tc05_commit_pair(&acc_full[buf], 3);
+          }
+          __syncwarp();
+        }
+      }
+      if (!ok && lane == 0) set_status(status, SI_WAIT_LIMIT);
+    }
+  } else {
+    const int q = warp & 3;
+    const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
+    int local = 0;
+    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * BN;
+      if (!mbar_wait_warp(&acc_full[buf], (unsigned)((local >> 1) & 1))) {
+        if (lane == 0) set_status(status, SI_WAIT_LIMIT);
+        break;
+      }
+      tc05_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const unsigned src = tmem + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN);
+#pragma unroll 1
+      for (int h = 0; h < BN / 128; ++h) {
+        float v[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32_issue(src + h * 128 + c * 32, v[c]);
+        tmem_ld_wait();
+        if (h == BN / 128 - 1) {                // in registers: the leader's issuer may have the accumulator back
+          tc05_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(cluster_map_u32(&acc_empty[buf], 0));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int n = n0 + h * 128 + c * 32;
+          if (row < M && n < N) {
+            if (SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            else store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
+          }
+        }
+      }
+    }
+  }
+  tc05_fence_before_sync();
+  cluster_sync_all();                                     // no CTA frees tensor memory the other one's instructions use
+  if (warp == 1) tmem_dealloc_pair(tmem, 2 * BN);
+}
+
+// SI_GEMM_PAIR=0 in the environment keeps every product on the one-CTA kernel.
+static bool pair_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("SI_GEMM_PAIR");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename TO, bool SWIGLU>
+static int launch_pair(const CUtensorMap& am, const CUtensorMap& bm_half, void* out, long long ldo, int M, int N, int K,
+                       int* status, cudaStream_t stream) {
+  constexpr int STAGES = 6;
+  const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 128 * 64 * 2) + 1024;
+  auto k = gemm_tc05_pair_kernel<STAGES, TO, SWIGLU>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const int pairs = tiles < si_sm_count() / 2 ? tiles : si_sm_count() / 2;
+  if (pairs < 1) return -2;
+  k<<<dim3(2 * pairs), 192, smem, stream>>>(am, bm_half, (TO*)out, ldo, M, N, K, status);
+  return si_last_error();
+}
+
 template <int STAGES, typename TO, bool SWIGLU>
 static int launch(const CUtensorMap& am, const CUtensorMap& bm, void* out, long long ldo, int M, int N, int K,
                   int* status, cudaStream_t stream) {
@@ -208,11 +370,15 @@ static int launch(const CUtensorMap& am, const CUtensorMap& bm, void* out, long 
 SI_EXPORT int si_gemm_tc05_ok() { return si_encode_fn() != nullptr; }
 
 // The weight's tensor map (boxes of [256, 64]); made once per weight. `map_out`: 128 bytes, 64-byte aligned.
-SI_EXPORT int si_gemm_tc05_encode_weight(void* map_out, const void* W, int N, int K, long long ldw) {
-  if ((K % 8) || (ldw % 8) || ((uintptr_t)W % 16)) return -2;
+// `box_rows`: 256 for the one-CTA kernel, 128 for the kernel of CTA pairs (each CTA fetches half of the tile's rows).
+SI_EXPORT int si_gemm_tc05_encode_weight(void* map_out, const void* W, int N, int K, long long ldw, int box_rows) {
+  if ((K % 8) || (ldw % 8) || ((uintptr_t)W % 16) || (box_rows != 128 && box_rows != 256)) return -2;
   return si_encode_bf16_2d((CUtensorMap*)map_out, W, (unsigned long long)N, (unsigned long long)K,
-                           (unsigned long long)ldw, 256);
+                           (unsigned long long)ldw, (unsigned)box_rows);
 }
+
+// Products of more than 128 rows go to the kernel of CTA pairs when the caller has a map with boxes of 128 rows.
+static bool use_pair(int M, const void* wmap_half) { return wmap_half && M > 128 && pair_enabled() && si_sm_count() >= 2; }
 
 static int gemm_tc05_common(const void* x, long long ldx, const void* wmap, CUtensorMap* am, int M, int K) {
   if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x % 16) || !wmap) return -2;
@@ -220,12 +386,18 @@ static int gemm_tc05_common(const void* x, long long ldx, const void* wmap, CUte
 }
 
 // out_dtype: SI_BF16 or SI_F32. x: [M, K] bf16 rows `ldx` apart. Returns -2 for unsupported sizes.
-SI_EXPORT int si_gemm_tc05(const void* x, long long ldx, const void* wmap, void* out, long long ldo, int out_dtype,
-                           int M, int N, int K, int* status, cudaStream_t stream) {
+// `wmap`: the weight's map with boxes of 256 rows; `wmap_half` (may be null): the one with boxes of 128 rows.
+SI_EXPORT int si_gemm_tc05(const void* x, long long ldx, const void* wmap, const void* wmap_half, void* out, long long ldo,
+                           int out_dtype, int M, int N, int K, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   CUtensorMap am;
   const int rc = gemm_tc05_common(x, ldx, wmap, &am, M, K);
   if (rc) return rc;
+  if (use_pair(M, wmap_half)) {
+    const CUtensorMap& bh = *(const CUtensorMap*)wmap_half;
+    if (out_dtype == SI_BF16) return launch_pair<bf16, false>(am, bh, out, ldo, M, N, K, status, stream);
+    return launch_pair<float, false>(am, bh, out, ldo, M, N, K, status, stream);
+  }
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
   if (out_dtype == SI_BF16) return launch<4, bf16, false>(am, bm, out, ldo, M, N, K, status, stream);
   return launch<4, float, false>(am, bm, out, ldo, M, N, K, status, stream);
@@ -233,13 +405,14 @@ SI_EXPORT int si_gemm_tc05(const void* x, long long ldx, const void* wmap, void*
 
 // out[M, F] = silu(gate) * up (bf16) of the stacked projection x[M, K] W[2F, K]^T whose rows are interleaved in
 // groups of 8 (8 gates, their 8 ups, ...); F a multiple of 8.
-SI_EXPORT int si_gemm_tc05_swiglu(const void* x, long long ldx, const void* wmap, void* out, long long ldo,
-                                  int M, int F, int K, int* status, cudaStream_t stream) {
+SI_EXPORT int si_gemm_tc05_swiglu(const void* x, long long ldx, const void* wmap, const void* wmap_half, void* out,
+                                  long long ldo, int M, int F, int K, int* status, cudaStream_t stream) {
   if (M <= 0 || F <= 0) return 0;
   if (F % 8) return -2;
   CUtensorMap am;
   const int rc = gemm_tc05_common(x, ldx, wmap, &am, M, K);
   if (rc) return rc;
+  if (use_pair(M, wmap_half)) return launch_pair<bf16, true>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, 2 * F, K, status, stream);
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
   return launch<4, bf16, true>(am, bm, out, ldo, M, 2 * F, K, status, stream);
 }

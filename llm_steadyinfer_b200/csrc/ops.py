@@ -618,14 +618,15 @@ def gemm_tc05_ok(a, w, out) -> bool:
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def _weight_map(w: torch.Tensor):
-    key = (w.device.index, w.data_ptr(), tuple(w.shape), w.stride(0))
+def _weight_map(w: torch.Tensor, box_rows: int = 256):
+    """The weight's TMA descriptor with boxes of ``box_rows`` rows (256: one CTA a tile; 128: a pair of CTAs)."""
+    key = (w.device.index, w.data_ptr(), tuple(w.shape), w.stride(0), box_rows)
     ent = _weight_maps.get(key)
     if ent is None:
         raw = ctypes.create_string_buffer(128 + 64)
         addr = (ctypes.addressof(raw) + 63) & ~63
-        f = _fn("gemm_tc05", "si_gemm_tc05_encode_weight", [_c_p, _c_p, _c_int, _c_int, _c_ll])
-        rc = f(_c_p(addr), _ptr(w), w.shape[0], w.shape[1], w.stride(0))
+        f = _fn("gemm_tc05", "si_gemm_tc05_encode_weight", [_c_p, _c_p, _c_int, _c_int, _c_ll, _c_int])
+        rc = f(_c_p(addr), _ptr(w), w.shape[0], w.shape[1], w.stride(0), box_rows)
         if rc != 0:
             raise KernelError(f"cannot describe the weight {tuple(w.shape)} to the TMA unit (code {rc})")
         ent = (raw, addr)
@@ -641,8 +642,9 @@ def gemm_tc05(a, w, out, status=None) -> None:
     _need(w.shape[1] == K and out.shape == (M, N), "gemm_tc05: shapes")
     _need(gemm_tc05_ok(a, w, out), "gemm_tc05: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
     f = _fn("gemm_tc05", "si_gemm_tc05",
-            [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
-    _check(f(_ptr(a), a.stride(0), _weight_map(w), _ptr(out), out.stride(0), _dt(out), M, N, K, _ptr(status),
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    half = _weight_map(w, 128) if M > 128 else None          # more than one tile of rows: pairs of CTAs take tiles together
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(out), out.stride(0), _dt(out), M, N, K, _ptr(status),
              _stream()), f"gemm_tc05(M={M}, N={N}, K={K})")
 
 
@@ -655,9 +657,65 @@ def gemm_tc05_swiglu(a, w, out, status=None) -> None:
     _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
           "gemm_tc05_swiglu: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
     _need(gemm_tc05_ok(a, w, out), "gemm_tc05_swiglu: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
-    f = _fn("gemm_tc05", "si_gemm_tc05_swiglu", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p])
-    _check(f(_ptr(a), a.stride(0), _weight_map(w), _ptr(out), out.stride(0), M, F, K, _ptr(status), _stream()),
+    f = _fn("gemm_tc05", "si_gemm_tc05_swiglu", [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p])
+    half = _weight_map(w, 128) if M > 128 else None
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(out), out.stride(0), M, F, K, _ptr(status), _stream()),
            f"gemm_tc05_swiglu(M={M}, F={F}, K={K})")
+
+
+# ---- tcgen05 matrix product for up to 128 rows ------------------------------------------------------
+
+ROWS_MAX = 128
+_rows_scratch: dict = {}
+
+
+def gemm_rows_ok(a, w, out) -> bool:
+    """True when the product for up to 128 rows takes these tensors (bf16, K a multiple of 8, aligned rows)."""
+    return a.shape[0] <= ROWS_MAX and gemm_tc05_ok(a, w, out)
+
+
+def _rows_scratch_for(device) -> torch.Tensor:
+    """The kernel's scratch on ``device`` (partial sums of the blocks that share a tile, and their flags):
+    one buffer for all calls, which run one after the other on the engine's stream. Allocated at the first call
+    (before any graph is recorded: a shape's first step runs directly); calls on several streams at once would
+    have to bring their own."""
+    t = _rows_scratch.get(device.index)
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("gemm_rows: the scratch would have to be allocated while a graph is recorded")
+        lib = build.load("gemm_rows")
+        lib.si_gemm_rows_scratch_words.restype = _c_ll
+        with torch.cuda.device(device):
+            words = int(lib.si_gemm_rows_scratch_words())
+        t = _rows_scratch[device.index] = torch.zeros(words, dtype=torch.float32, device=device)
+    return t
+
+
+def gemm_rows(a, w, out, status=None) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 128 on the tcgen05 tensor cores, W streamed once through all SMs
+    in equal shares (see gemm_rows.cu)."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), "gemm_rows: shapes")
+    _need(gemm_rows_ok(a, w, out), "gemm_rows: bf16 inputs, at most 128 rows, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_rows", "si_gemm_rows", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_ptr(a), a.stride(0), _weight_map(w, 128), _ptr(out), out.stride(0), _dt(out), M, N, K,
+             _ptr(_rows_scratch_for(a.device)), _ptr(status), _stream()), f"gemm_rows(M={M}, N={N}, K={K})")
+
+
+def gemm_rows_swiglu(a, w, out, status=None) -> None:
+    """out[M,F] = silu(gate) * up of a[M,K] @ w[2F,K]^T for M <= 128, the rows of w interleaved in groups of 8
+    (8 gates, their 8 ups, ...): the activation runs in the product's epilogue."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    F = out.shape[1]
+    _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
+          "gemm_rows_swiglu: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
+    _need(gemm_rows_ok(a, w, out), "gemm_rows_swiglu: bf16 inputs, at most 128 rows, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_rows", "si_gemm_rows_swiglu", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_ptr(a), a.stride(0), _weight_map(w, 128), _ptr(out), out.stride(0), M, F, K,
+             _ptr(_rows_scratch_for(a.device)), _ptr(status), _stream()), f"gemm_rows_swiglu(M={M}, F={F}, K={K})")
 
 
 # ---- prompt-portion attention on tcgen05 ---------------------------------------------------------

@@ -145,6 +145,57 @@ __device__ __forceinline__ void tc05_mma_bf16_tmem_a(unsigned d_tmem, unsigned a
                ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// ---- pairs of CTAs on one tile (tcgen05 with cta_group::2) ----------------------------------------
+// The two CTAs of a cluster of two take one 256-row tile together: each holds 128 rows of A, half of the rows
+// of B and its 128 rows of the accumulator; CTA 0 (the leader) issues the instructions, which read both CTAs'
+// shared memory at equal offsets. Every helper below is for such a pair.
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// The shared::cluster address of `p` (a shared-memory object of this CTA) as CTA `rank` of the cluster holds it.
+__device__ __forceinline__ unsigned cluster_map_u32(const void* p, unsigned rank) {
+  unsigned a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(tma_smem_u32(p)), "r"(rank));
+  return a;
+}
+// One arrival at an mbarrier given by its shared::cluster address (this CTA's or the peer's).
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose bytes are counted at an mbarrier of either CTA of the pair
+// (`bar_cluster_addr`: shared::cluster address). No multicast: each CTA fetches its own boxes.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, unsigned bar_cluster_addr, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(tma_smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+// Tensor memory of both CTAs of the pair; one warp of each CTA runs this.
+__device__ __forceinline__ void tmem_alloc_pair(unsigned* slot, unsigned ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tma_smem_u32(slot)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned taddr, unsigned ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair's 256 rows; issued by one thread of the leader CTA.
+__device__ __forceinline__ void tc05_mma_bf16_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                                   unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// One arrival at the mbarrier at this offset in each CTA of `cta_mask` once every tcgen05.mma issued so far
+// by this thread has completed. (A multicast of an arrival, not of a load.)
+__device__ __forceinline__ void tc05_commit_pair(uint64_t* bar, unsigned short cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(tma_smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
 // Shared-memory matrix descriptor of a bf16 tile whose rows are 128 bytes (64 elements) apart and
 // swizzled in 8-row, 1024-byte groups (the 128-byte TMA swizzle); the tile must start on a 1024-byte
 // boundary. K-major operand (rows = M or N, the 64 columns = K): groups of 8 rows lie `sbo` bytes apart.

@@ -84,7 +84,7 @@ class Model:
 
     def kernel_files(self, page_size: int) -> List[str]:
         """CUDA sources of the model's own kernels and of its parts (see ``Part.kernel_files``)."""
-        names = {"embedding", "sampling", "gemm_f32" if self.dtype == torch.float32 else "gemm_skinny"}
+        names = {"embedding", "sampling"} | ({"gemm_f32"} if self.dtype == torch.float32 else {"gemm_skinny", "gemm_rows", "gemm_tc05"})
         for _, part in self._named_parts():
             names.update(part.kernel_files(page_size))
         return sorted(names)
@@ -116,5 +116,5 @@ class Model:
         x = ctx.buf("final_x", (R, d), self.dtype)
         self.final_norm.forward(resid, delta, x, rows=ctx.logit_rows)
         logits = ctx.buf("logits", (R, self.spec.vocab_size), torch.float32)
-        linear(x, self.lm_head, logits)
+        linear(x, self.lm_head, logits, ctx.status)
         return logits

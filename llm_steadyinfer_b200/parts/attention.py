@@ -65,7 +65,7 @@ class Attention(Mixer):
         return self.qkv if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
 
     def kernel_files(self, page_size):
-        names = ["rope_kv", "gemm_f32" if self.dtype == torch.float32 else "gemm_skinny"]
+        names = ["rope_kv"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_skinny", "gemm_rows", "gemm_tc05"])
         if not self.uses_tensor_cores():
             return tuple(names + ["attention_ref"])
         names.append("attention_mma")
@@ -77,7 +77,7 @@ class Attention(Mixer):
         T = x.shape[0]
         H, KV, hs = self.H, self.KV, self.hs
         qkv = ctx.buf("attn_qkv", (T, (H + 2 * KV) * hs), self.dtype)
-        linear(x, self.qkv, qkv)
+        linear(x, self.qkv, qkv, ctx.status)
         rot = self.position.rotary() if self.position is not None else None
         if self.position is not None and rot is None:
             q3 = qkv[:, :H * hs].view(T, H, hs)
@@ -90,7 +90,7 @@ class Attention(Mixer):
         attn = ctx.buf("attn_out", (T, H * hs), self.dtype)
         self.attend(qkv[:, :H * hs], cache, ctx, attn)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
-        linear(attn, self.o, out)
+        linear(attn, self.o, out, ctx.status)
         return out
 
     # ---- kernels ---------------------------------------------------------------------

@@ -1,11 +1,14 @@
 """Matrix products of the parts: ``out[M, N] = x[M, K] @ w[N, K]^T``.
 
 fp32 tensors go through this package's own FFMA kernel (true 32-bit, no reduced-precision
-mode). bf16 products of at most 16 rows (decode) go through the package's weight-streaming
-kernel (``gemm_skinny.cu``). Other bf16 products go to the cuBLAS GEMM behind ``torch.mm`` with
-fp32 accumulation, as the reference sends every projection and the LM head to ``cublasGemmEx``
-(src/source/op/kernels/cuda/matmul_kernel.cu:128-150), or, with ``USE_OWN_GEMM``, to the package's
-tcgen05 kernel (``gemm_tc05.cu``).
+mode). bf16 products go to the package's kernels by their number of rows: at most 16 (decode) to the
+weight-streaming kernel on mma.sync (``gemm_skinny.cu``), up to 128 (larger decode batches, short
+portions, mixed steps) to the tcgen05 kernel that streams the weights in equal shares
+(``gemm_rows.cu``), more to the tcgen05 kernel with pairs of CTAs on 256 x 256 tiles
+(``gemm_tc05.cu``). The reference sends every projection and the LM head to ``cublasGemmEx``
+(src/source/op/kernels/cuda/matmul_kernel.cu:128-150); the library product behind ``torch.mm`` (fp32
+accumulation) is kept for tensors that the kernels do not take (rows that are not 16-byte aligned)
+and can be had for every many-row product with SI_OWN_GEMM=0 in the environment.
 """
 from __future__ import annotations
 
@@ -17,12 +20,9 @@ from ..csrc import ops
 
 
 USE_SKINNY = True      # few-row products (decode) through this package's weight-streaming kernel
-# Many-row bf16 products (at least OWN_GEMM_MIN_ROWS rows) through this package's tcgen05 kernel instead of
-# the library. Off by default: on the plain projections the library's 2-CTA kernels are 8 to 19 % faster
-# (the gate/up projection, where the fused activation makes up for it, does not come through here).
-# SI_OWN_GEMM=1 in the environment turns it on.
-USE_OWN_GEMM = os.environ.get("SI_OWN_GEMM", "0") == "1"
-OWN_GEMM_MIN_ROWS = 128
+USE_ROWS = os.environ.get("SI_OWN_ROWS", "1") == "1"      # 17 to 128 rows through gemm_rows.cu (0: the library)
+USE_OWN_GEMM = os.environ.get("SI_OWN_GEMM", "1") == "1"  # more rows through gemm_tc05.cu (0: the library)
+OWN_GEMM_MIN_ROWS = 129
 
 
 def configure_library_gemm() -> None:
@@ -41,16 +41,19 @@ def library_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise ops.KernelError(f"linear: unsupported output dtype {out.dtype}")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status=None) -> torch.Tensor:
+    """``status``: the engine's status word, where a kernel's bounded wait that ran out is reported."""
     if not x.is_cuda:
         raise ops.KernelError("linear: CUDA tensors only; there is no CPU path")
     if x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32:
         ops.gemm_f32(x, w, out)
     elif USE_SKINNY and ops.gemm_skinny_ok(x, w, out):
         ops.gemm_skinny(x, w, out, checked=True)
+    elif USE_ROWS and x.shape[0] <= ops.ROWS_MAX and ops.gemm_tc05_available() and ops.gemm_rows_ok(x, w, out):
+        ops.gemm_rows(x, w, out, status)
     elif (USE_OWN_GEMM and x.shape[0] >= OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available()
           and ops.gemm_tc05_ok(x, w, out)):
-        ops.gemm_tc05(x, w, out)
+        ops.gemm_tc05(x, w, out, status)
     elif x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         library_mm(x, w, out)
     else:

@@ -3,9 +3,9 @@ block computes it (src/source/model/llama3.cpp:1149-1180). gate and up are stack
 [2F, d] matrix at load so one product feeds the activation: when F is a multiple of 8 the rows
 are interleaved in groups of 8 (8 rows of gate, the 8 rows of up that belong to them, ...), so
 that the few-row product holds a gate and its up in one block and applies the activation in
-its epilogue. So does the many-row product on the tcgen05 tensor cores (``gemm_tc05.cu``), which with
-the activation fused is faster than the library product followed by the activation kernel; where
-neither applies, the library product runs and the activation kernel reads the same interleaved columns.
+its epilogue. So do the products on the tcgen05 tensor cores (``gemm_rows.cu`` up to 128 rows,
+``gemm_tc05.cu`` above); where none applies (fp32, an intermediate size that is no multiple of 8), the
+product runs alone and the activation kernel reads the same interleaved columns.
 """
 from __future__ import annotations
 
@@ -17,8 +17,7 @@ from . import linear as linear_mod
 from .linear import linear
 
 INTERLEAVE = 8         # rows of gate, then rows of up, in the stacked weight
-USE_TC05_GEMM = True   # many-row gate/up product through this package's tcgen05 kernel (activation fused)
-TC05_MIN_ROWS = 128    # below one 128-row tile the library product and the activation kernel run
+USE_TC05_GEMM = True   # gate/up product of more than 16 rows through this package's tcgen05 kernels (activation fused)
 
 
 class GatedMLP(FeedForward):
@@ -53,7 +52,7 @@ class GatedMLP(FeedForward):
     def kernel_files(self, page_size):
         if self.dtype == torch.float32:
             return ("gemm_f32", "swiglu")
-        return ("gemm_skinny", "swiglu") + (("gemm_tc05",) if self.group == INTERLEAVE and USE_TC05_GEMM else ())
+        return ("gemm_skinny", "swiglu", "gemm_tc05", "gemm_rows")
 
     def forward(self, x, ctx):
         T = x.shape[0]
@@ -61,15 +60,19 @@ class GatedMLP(FeedForward):
         if (self.group == INTERLEAVE and linear_mod.USE_SKINNY and act.dtype == torch.bfloat16
                 and ops.gemm_skinny_ok(x, self.gate_up, act)):
             ops.gemm_skinny_swiglu(x, self.gate_up, act, checked=True)
-        elif (self.group == INTERLEAVE and USE_TC05_GEMM and T >= TC05_MIN_ROWS and act.dtype == torch.bfloat16
-                and ops.gemm_tc05_available() and ops.gemm_tc05_ok(x, self.gate_up, act)):
-            ops.gemm_tc05_swiglu(x, self.gate_up, act, ctx.status)
+        elif (self.group == INTERLEAVE and USE_TC05_GEMM and act.dtype == torch.bfloat16
+                and ops.gemm_tc05_available() and ops.gemm_tc05_ok(x, self.gate_up, act)
+                and (linear_mod.USE_ROWS if T <= ops.ROWS_MAX else linear_mod.USE_OWN_GEMM)):
+            if T <= ops.ROWS_MAX:
+                ops.gemm_rows_swiglu(x, self.gate_up, act, ctx.status)
+            else:
+                ops.gemm_tc05_swiglu(x, self.gate_up, act, ctx.status)
         else:
             gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
-            linear(x, self.gate_up, gu)
+            linear(x, self.gate_up, gu, ctx.status)
             ops.swiglu(gu, act, self.group)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
-        linear(act, self.down, out)
+        linear(act, self.down, out, ctx.status)
         return out
 
 

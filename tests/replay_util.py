@@ -56,18 +56,20 @@ def trace_portions(reqs: Dict[str, List[int]], sizes: Sequence[int] = (17, 5, 2,
 
 
 def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4,
-                prompt_frac: float = 0.6, cut_every: int = 0, kept=None) -> List[dict]:
+                prompt_frac: float = 0.6, cut_every: int = 0, kept=None, max_cuts: int = 6) -> List[dict]:
     """Up to ``max_live`` live requests: portions of some prompts beside single "decoded" tokens
     of others; a request is admitted only when its whole length (rounded up to 64) still fits
     in ``max_tokens``, so pages of ended requests are used again by later ones. Some requests
     sit a step out. With ``cut_every`` = n, every n-th step first cuts one live request back to a
     random length as a preemption does (a "truncate" record; ``kept(held, keep)`` says how many tokens
-    stay) and the trace computes the cut tokens again, in portions, beside the others."""
+    stay) and the trace computes the cut tokens again, in portions, beside the others; at most ``max_cuts`` cuts in
+    all, so that the trace ends."""
     rng = random.Random(seed)
     waiting = list(reqs.items())
     live: Dict[str, dict] = {}
     steps: List[dict] = []
     held = 0
+    cuts_left = max_cuts
     while waiting or live:
         while waiting and len(live) < max_live and held + round64(len(waiting[0][1])) <= max_tokens:
             rid, toks = waiting.pop(0)
@@ -75,9 +77,10 @@ def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_
             held += round64(len(toks))
         assert live, "max_tokens is too small for the next request"
         entries, end, cuts = [], [], []
-        if cut_every and len(steps) % cut_every == cut_every - 1:
+        if cut_every and cuts_left > 0 and len(steps) % cut_every == cut_every - 1:
             cand = [r for r, st in live.items() if st["pos"] > 1]
             if cand:
+                cuts_left -= 1
                 rid = rng.choice(cand)
                 st = live[rid]
                 keep = rng.randrange(0, st["pos"])

@@ -27,6 +27,22 @@ def plain_generate(folder, prompts, n_new, **kw):
     return [plain_llama.generate(cfg, w, p, n_new, seed=s, **kw) for p, s in zip(prompts, seeds)]
 
 
+def assert_same_until_a_near_tie(folder, prompts, a, b, gap=2e-2):
+    """Two bfloat16 runs whose steps round differently (other splits of the keys, other products) must draw the
+    same greedy tokens up to the first position at which the plain logits' two largest values lie closer than
+    the bf16 error bound allows to tell apart; from there on the runs see different tokens and are not compared."""
+    cfg, w = plain_llama.read_model_folder(folder)
+    for p, x, y in zip(prompts, a, b):
+        n = next((i for i in range(min(len(x), len(y))) if x[i] != y[i]), None)
+        if n is None:
+            assert len(x) == len(y)
+            continue
+        top2 = torch.topk(plain_llama.forward(cfg, w, list(p) + list(x[:n]))[-1], 2).values
+        assert (top2[0] - top2[1]).item() < gap, (
+            f"tokens differ at output {n} ({x[n]} and {y[n]}) although the plain logits tell them apart by "
+            f"{(top2[0] - top2[1]).item():.3e}")
+
+
 def test_greedy_matches_plain_config_a(folders):
     """Config A's workload: 4 requests, prompts 1/7/33/64, greedy, 16 tokens each, page size 16."""
     from llm_steadyinfer_b200 import LLM, SamplingParams
@@ -128,7 +144,10 @@ def test_graph_decode_equals_direct_decode(folders, dtype):
         if graphs:
             assert llm.stats["graph_steps"] > 20 and len(llm.runner._graphs) >= 2
         llm.runner.manager.check_invariant()
-    assert outs[True] == outs[False]
+    if dtype == "float32":
+        assert outs[True] == outs[False]
+    else:           # a recorded step cuts the keys into the shares of its shape, a direct one into its own
+        assert_same_until_a_near_tie(folders["B"], prompts, outs[True], outs[False])
     if dtype == "float32":
         assert outs[True] == plain_generate(folders["B"], prompts, 40)[:0] + [
             o[:p.max_tokens] for o, p in zip(plain_generate(folders["B"], prompts, 40), params)]

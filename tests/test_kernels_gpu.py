@@ -758,6 +758,87 @@ def test_gemm_tc05_swiglu(M, F, K):
     assert (out.double().cpu() - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(17, 128, 64), (1, 1000, 96), (33, 513, 320), (64, 200, 1336), (128, 384, 4096), (100, 6144, 512),
+                                   (16, 64, 16), (127, 37, 8), (48, 4096, 4096), (5, 128256, 256)])
+def test_gemm_rows(M, N, K, out_dtype):
+    """The product for up to 128 rows: tiles shared between blocks (their partial sums added by the tile's
+    owner), tails in every dimension, and the same call twice (the flags are back at zero)."""
+    g = torch.Generator(device=DEV).manual_seed(21)
+    a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g, device=DEV).to(torch.bfloat16)
+    want = a.double() @ w.double().T
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tol = (2 ** -8 if out_dtype == torch.bfloat16 else 2e-6) * max(1.0, want.abs().max().item()) + 1e-5 * K ** 0.5
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        ops().gemm_rows(a, w, out, status)
+        assert status.item() == 0
+        assert not torch.isnan(out).any()
+        assert (out.double() - want).abs().max().item() <= tol
+    # a row's result does not depend on the other rows of the call
+    if M > 1:
+        alone = torch.empty(1, N, dtype=out_dtype, device=DEV)
+        ops().gemm_rows(a[M // 2:M // 2 + 1], w, alone, status)
+        assert torch.equal(alone[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M,F,K", [(17, 64, 96), (64, 1336, 320), (128, 520, 4096), (30, 40, 72), (100, 14336, 256)])
+def test_gemm_rows_swiglu(M, F, K):
+    g = torch.Generator(device=DEV).manual_seed(22)
+    a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+    gate = (0.3 * torch.randn(F, K, generator=g, device=DEV)).to(torch.bfloat16)
+    up = (0.3 * torch.randn(F, K, generator=g, device=DEV)).to(torch.bfloat16)
+    w = torch.stack([gate.view(F // 8, 8, K), up.view(F // 8, 8, K)], 1).reshape(2 * F, K).contiguous()
+    gd = (a.double() @ gate.double().T).to(torch.bfloat16).double()
+    ud = (a.double() @ up.double().T).to(torch.bfloat16).double()
+    want = gd / (1 + torch.exp(-gd)) * ud
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops().gemm_rows_swiglu(a, w, out, status)
+    assert status.item() == 0 and not torch.isnan(out).any()
+    # gate and up are rounded to bf16 before the activation: a rounding that falls the other way moves the result by
+    # one bf16 step of gate or up
+    scale = max(1.0, want.abs().max().item())
+    assert (out.double() - want).abs().max().item() <= 2 ** -6 * scale
+
+
+def test_gemm_rows_at_serving_size():
+    """The projections of the Llama-3.1-8B block and the output head at 8 to 128 rows: achieved bandwidth of the
+    weight stream (printed) beside the few-row kernel (up to 16 rows) and the library."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    shapes = (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336), ("head", 128256, 4096))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for M in (8, 16, 32, 64, 128):
+        for name, N, K in shapes:
+            a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+            w = (0.02 * torch.randn(N, K, generator=g, device=DEV)).to(torch.bfloat16)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+            runs = {"rows": lambda: ops().gemm_rows(a, w, out, status), "library": lambda: torch.mm(a, w.t(), out=out)}
+            if M <= 16:
+                runs["few-row"] = lambda: ops().gemm_skinny(a, w, out)
+            res = {}
+            for label, fn in runs.items():
+                for _ in range(3):
+                    fn()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(10):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                res[label] = e0.elapsed_time(e1) * 100
+            assert status.item() == 0
+            out.fill_(float("nan"))
+            ops().gemm_rows(a, w, out, status)
+            want = a.double() @ w[:4096].double().T
+            assert (out[:, :4096].double() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item()
+            assert not torch.isnan(out).any()
+            gb = N * K * 2 / 1e3
+            print(f"{M:4d} rows {name:8s}: " + ", ".join(f"{k} {v:.1f} us ({gb / v:.0f} GB/s)" for k, v in res.items()))
+
+
 def test_gemm_tc05_at_prefill_size():
     """The projections of the Llama-3.1-8B block at 2,048 rows: achieved TFLOP/s (printed) beside the library."""
     g = torch.Generator(device=DEV).manual_seed(15)
