@@ -59,6 +59,7 @@ def _included_sources(name: str) -> List[str]:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(os.environ.get("SI_NVCC_EXTRA", "").encode())      # other flags, another library
     own = [name + ".cu"] + _included_sources(name)
     for fn in sorted(os.listdir(CSRC_DIR)):
         if fn in own or fn.endswith(".cuh") or fn.endswith(".h"):

@@ -9,11 +9,10 @@
 // * The work is the list of (tile of 128 output columns, k step of 64) pairs in that order, cut into as many
 //   equal contiguous shares as there are blocks (one per SM): every block streams the same number of bytes,
 //   whatever the number of tiles. A share that starts or ends inside a tile computes a partial sum of that
-//   tile. The block that holds a tile's first k step owns the tile: it adds the partial sums of the blocks
-//   after it, in their order, and stores. A block that starts inside a tile writes its partial sum to its
-//   slot of `scratch` first thing and raises a flag; by the time the owner, which reaches that tile last,
-//   looks for it, it is there. Only owners wait, only for blocks that never wait themselves, and every wait
-//   is bounded (SI_WAIT_LIMIT in the status word, and the block stores what it has).
+//   tile, writes it to a slot of `scratch` and takes a ticket of that tile; the block that takes the tile's
+//   last ticket adds the partial sums up, in the order of the blocks (not of their arrival), and stores the
+//   tile. Nobody waits for another block; the only waits are on the block's own barriers, and bounded
+//   (SI_WAIT_LIMIT in the status word).
 //   The cut depends on N and K and the number of blocks only, never on the number of rows: a row's result
 //   does not depend on what else is in the batch.
 // * Warp 0 is the TMA producer (a [128, 64] box of W and a [rows, 64] box of x per k step into a ring of six
@@ -30,15 +29,10 @@ typedef __nv_bfloat16 bf16;
 
 #define SI_ROWS_MAX 128                 // rows of x one call takes
 #define SI_ROWS_SLOT_FLOATS (128 * 128) // one block's partial sum: [row][column of the tile]
-#define SI_ROWS_FLAGS_PER_SLOT 4        // one flag per epilogue warp
+#define SI_ROWS_MAX_TILES 16384         // tiles of 128 output columns a call may have (2 M columns)
 
 // A share never holds fewer k steps than this (a block whose share is shorter would not pay for its start).
 #define SI_ROWS_MIN_STEPS 8
-
-struct RowsPlan {
-  int n_tiles, nk, blocks;
-  long long units;
-};
 
 __host__ __device__ inline long long rows_share_start(long long units, int blocks, int c) {
   return units * c / blocks;
@@ -51,24 +45,49 @@ __device__ inline int rows_block_of(long long units, int blocks, long long u) {
   return c;
 }
 
-__device__ __forceinline__ int ld_flag(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_flag(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-
 template <typename TO> __device__ __forceinline__ void rows_store(TO* p, float v);
 template <> __device__ __forceinline__ void rows_store<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void rows_store<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// 32 rows of this thread's output column: `n` the column, `base` the first column of the warp's 32.
+template <typename TO, bool SWIGLU>
+__device__ __forceinline__ void rows_store_chunk(TO* __restrict__ out, long long ldo, float (&v)[32], int m0, int M, int N,
+                                                 int n, int base, int lane) {
+  if (SWIGLU) {
+    bf16* o = (bf16*)out;
+    const int f = base / 2 + (lane >> 4) * 8 + (lane & 7);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
+      if ((lane & 8) == 0 && m0 + j < M && n + 8 < N)
+        o[(size_t)(m0 + j) * ldo + f] = __float2bfloat16_rn(silu_mul(
+            __bfloat162float(__float2bfloat16_rn(v[j])), __bfloat162float(__float2bfloat16_rn(up))));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (m0 + j < M && n < N) rows_store<TO>(out + (size_t)(m0 + j) * ldo + n, v[j]);
+  }
+}
+
+// Built with -DSI_ROWS_TIMING, every block leaves the times (ns, %globaltimer) of its milestones in
+// g_rows_times, which si_gemm_rows_times() copies out: where a launch spends its time, block by block.
+#ifdef SI_ROWS_TIMING
+__device__ unsigned long long g_rows_times[256][8];
+__device__ __forceinline__ void rows_stamp(int i) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  g_rows_times[blockIdx.x][i] = t;
+}
+#else
+__device__ __forceinline__ void rows_stamp(int) {}
+#endif
 
 template <int STAGES, typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(192)
 gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                  TO* __restrict__ out, long long ldo, int M, int N, int K, float* __restrict__ scratch,
-                 int* __restrict__ flags, int* status) {
+                 int* __restrict__ tickets, int* status) {
   constexpr int BN = 128, BK = 64;                         // output columns a tile, k a step
   constexpr int W_BYTES = BN * BK * 2, X_BYTES = SI_ROWS_MAX * BK * 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -86,6 +105,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
   const long long units = (long long)n_tiles * nk;
   const int blocks = gridDim.x, me = blockIdx.x;
   const long long u0 = rows_share_start(units, blocks, me), u1 = rows_share_start(units, blocks, me + 1);
+  if (threadIdx.x == 0) rows_stamp(0);
 
   if (threadIdx.x == 0) {
 #pragma unroll
@@ -99,6 +119,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
   __syncthreads();
   tc05_fence_after_sync();
   const unsigned tmem = tmem_slot;
+  if (threadIdx.x == 0) rows_stamp(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -146,6 +167,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
         const int s = (int)(it % STAGES);
         ok = mbar_wait_warp(&full_bar[s], (unsigned)((it / STAGES) & 1));
         if (!ok) break;
+        if (it == 0 && lane == 0) rows_stamp(2);
         tc05_fence_after_sync();
         const unsigned long long wd = wd0 + (unsigned)s * (W_BYTES / 16), xd = xd0 + (unsigned)s * (X_BYTES / 16);
         if (elect_one()) {
@@ -159,6 +181,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
       }
     }
     if (!ok && lane == 0) set_status(status, SI_WAIT_LIMIT);
+    if (lane == 0) rows_stamp(3);
   } else {
     pdl_wait();                                           // `out` and `scratch` may still be read by the kernel before
     const int q = warp & 3;                               // tensor-memory lanes q*32 .. q*32+31 = columns of the tile
@@ -167,8 +190,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
       const int tile = (int)(u / nk);
       const long long t0 = (long long)tile * nk, t1 = t0 + nk;
       const long long seg_end = t1 < u1 ? t1 : u1;
-      const bool owner = (u == t0);                       // this share holds the tile's first k step
-      const bool whole = owner && seg_end == t1;
+      const bool whole = (u == t0) && seg_end == t1;
       const int buf = local & 1;
       u = seg_end;
       if (!mbar_wait_warp(&acc_full[buf], (unsigned)((local >> 1) & 1))) {
@@ -176,22 +198,11 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
         break;
       }
       tc05_fence_after_sync();
-      // the blocks after this one that hold the rest of the tile (none for a whole tile)
-      const int last_other = (owner && !whole) ? rows_block_of(units, blocks, t1 - 1) : me;
-      if (owner && !whole) {
-        for (int c = me + 1; c <= last_other; ++c) {     // their partial sums are long written: a bounded look
-          int seen = 0;
-          if (lane == 0) {
-            const int* f = flags + c * SI_ROWS_FLAGS_PER_SLOT + q;
-            for (int i = 0; i < (1 << 20) && !(seen = ld_flag(f)); ++i) __nanosleep(40);
-            if (!seen) set_status(status, SI_WAIT_LIMIT);
-          }
-          __syncwarp();
-        }
-      }
+      if (q == 0 && lane == 0) rows_stamp(local == 0 ? 4 : 6);
       const int n = tile * BN + q * 32 + lane;            // this thread's output column
       const unsigned src = tmem + ((unsigned)(q * 32) << 16) + (unsigned)(buf * SI_ROWS_MAX);
-      float* mine = scratch + (size_t)me * SI_ROWS_SLOT_FLOATS + q * 32 + lane;
+      // a share's first segment goes to the block's first slot, a later one (its last) to the second
+      float* mine = scratch + (size_t)(2 * me + (local == 0 ? 0 : 1)) * SI_ROWS_SLOT_FLOATS + q * 32 + lane;
 #pragma unroll 1
       for (int m0 = 0; m0 < mpad; m0 += 32) {
         float v[32];
@@ -201,61 +212,84 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        if (!owner) {                                      // a partial sum: [row][column], this warp's 32 columns
+        if (whole) {
+          rows_store_chunk<TO, SWIGLU>(out, ldo, v, m0, M, N, n, tile * BN + q * 32, lane);
+        } else {                                           // a partial sum: [row][column], this warp's 32 columns
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (m0 + j < mpad) __stcg(mine + (size_t)(m0 + j) * BN, v[j]);
-          continue;
         }
-        for (int c = me + 1; c <= last_other; ++c) {
-          const float* theirs = scratch + (size_t)c * SI_ROWS_SLOT_FLOATS + q * 32 + lane;
+      }
+      if (whole) continue;
+      // The partial sum is written. Whoever comes last to a tile adds the partial sums up, in the order of the
+      // blocks, whichever block it is itself: nobody waits for anybody. One ticket counter per (tile, warp).
+      __threadfence();
+      __syncwarp();
+      const int c_first = rows_block_of(units, blocks, t0), c_last = rows_block_of(units, blocks, t1 - 1);
+      int* ticket = tickets + (size_t)tile * 4 + q;
+      int mine_is_last = 0;
+      if (lane == 0) mine_is_last = atomicAdd(ticket, 1) == c_last - c_first;
+      if (!__shfl_sync(0xffffffffu, mine_is_last, 0)) continue;
+      __threadfence();
+      if (q == 0 && lane == 0) rows_stamp(5);
+#pragma unroll 1
+      for (int m0 = 0; m0 < mpad; m0 += 32) {
+        float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (m0 + j < mpad) v[j] += __ldcg(theirs + (size_t)(m0 + j) * BN);
-        }
-        if (SWIGLU) {
-          bf16* o = (bf16*)out;
-          const int f = (tile * BN + q * 32) / 2 + (lane >> 4) * 8 + (lane & 7);
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+#pragma unroll 1
+        for (int c = c_first; c <= c_last; c += 4) {       // four partial sums in flight at a time
+          float t[4][32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
-            if ((lane & 8) == 0 && m0 + j < M && n + 8 < N)
-              o[(size_t)(m0 + j) * ldo + f] = __float2bfloat16_rn(silu_mul(
-                  __bfloat162float(__float2bfloat16_rn(v[j])), __bfloat162float(__float2bfloat16_rn(up))));
+          for (int i = 0; i < 4; ++i) {
+            const int ci = c + i <= c_last ? c + i : c_last;
+            const int slot = 2 * ci + (rows_share_start(units, blocks, ci) >= t0 ? 0 : 1);
+            const float* theirs = scratch + (size_t)slot * SI_ROWS_SLOT_FLOATS + q * 32 + lane + (size_t)m0 * BN;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) t[i][j] = (m0 + j < mpad) ? __ldcg(theirs + (size_t)j * BN) : 0.f;
           }
-        } else {
+          asm volatile("" ::: "memory");                   // every load above is issued before the first sum waits
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (m0 + j < M && n < N) rows_store<TO>(out + (size_t)(m0 + j) * ldo + n, v[j]);
+          for (int i = 0; i < 4; ++i)
+            if (c + i <= c_last) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += t[i][j];
+            }
         }
+        rows_store_chunk<TO, SWIGLU>(out, ldo, v, m0, M, N, n, tile * BN + q * 32, lane);
       }
-      if (!owner) {                                        // written and visible, then the flag
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_flag(flags + me * SI_ROWS_FLAGS_PER_SLOT + q, 1);
-      } else if (!whole) {                                 // read: the flags are ready for the next launch
-        __syncwarp();
-        if (lane == 0)
-          for (int c = me + 1; c <= last_other; ++c) st_flag(flags + c * SI_ROWS_FLAGS_PER_SLOT + q, 0);
-      }
+      __syncwarp();
+      if (lane == 0) *ticket = 0;                          // ready for the next launch
     }
   }
   tc05_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) rows_stamp(7);
   if (warp == 1) tmem_dealloc(tmem, 256);
 }
 
+#ifdef SI_ROWS_TIMING
+SI_EXPORT int si_gemm_rows_times(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_rows_times, sizeof(g_rows_times));
+}
+#endif
+
 static int rows_blocks(int N, int K) {
   const long long units = (long long)((N + 127) / 128) * ((K + 63) / 64);
+  if (const char* e = getenv("SI_ROWS_BLOCKS")) {          // for measurements: a fixed number of blocks
+    const long long b = atoll(e);
+    if (b >= 1 && b <= units && b <= si_sm_count()) return (int)b;
+  }
   long long b = units / SI_ROWS_MIN_STEPS;
   if (b < 1) b = 1;
   return (int)(b < si_sm_count() ? b : si_sm_count());
 }
 
-// Words (4 bytes) of scratch a call needs, whatever its sizes: the partial sums of one block per SM and
-// their flags. The flags (the last `sms * 4` words) must be zero before the first call; calls leave them zero.
+// Words (4 bytes) of scratch a call needs, whatever its sizes: two partial sums per block (a share's first and
+// last tile), one block per SM, and the tickets, four per tile. The tickets (the last 4 * SI_ROWS_MAX_TILES
+// words) must be zero before the first call; calls leave them zero.
 SI_EXPORT long long si_gemm_rows_scratch_words() {
-  return (long long)si_sm_count() * (SI_ROWS_SLOT_FLOATS + SI_ROWS_FLAGS_PER_SLOT);
+  return (long long)si_sm_count() * 2 * SI_ROWS_SLOT_FLOATS + 4 * SI_ROWS_MAX_TILES;
 }
 SI_EXPORT int si_gemm_rows_max_rows() { return SI_ROWS_MAX; }
 
@@ -263,6 +297,7 @@ template <typename TO, bool SWIGLU>
 static int rows_launch(const void* x, long long ldx, const void* wmap, void* out, long long ldo, int M, int N, int K,
                        float* scratch, int* status, cudaStream_t stream) {
   if (M > SI_ROWS_MAX || K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x % 16) || !wmap || !scratch) return -2;
+  if ((N + 127) / 128 > SI_ROWS_MAX_TILES) return -2;
   CUtensorMap xm;
   const int mpad = (M + 15) & ~15;
   const int rc = si_encode_bf16_2d(&xm, x, (unsigned long long)M, (unsigned long long)K, (unsigned long long)ldx, (unsigned)mpad);
@@ -272,9 +307,9 @@ static int rows_launch(const void* x, long long ldx, const void* wmap, void* out
   auto k = gemm_rows_kernel<STAGES, TO, SWIGLU>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  int* flags = reinterpret_cast<int*>(scratch + (size_t)si_sm_count() * SI_ROWS_SLOT_FLOATS);
+  int* tickets = reinterpret_cast<int*>(scratch + (size_t)si_sm_count() * 2 * SI_ROWS_SLOT_FLOATS);
   si_launch(k, dim3(rows_blocks(N, K)), dim3(192), smem, stream, xm, *(const CUtensorMap*)wmap, (TO*)out, ldo, M, N, K,
-            scratch, flags, status);
+            scratch, tickets, status);
   return si_last_error();
 }
 

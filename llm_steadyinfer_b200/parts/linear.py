@@ -1,14 +1,15 @@
 """Matrix products of the parts: ``out[M, N] = x[M, K] @ w[N, K]^T``.
 
 fp32 tensors go through this package's own FFMA kernel (true 32-bit, no reduced-precision
-mode). bf16 products go to the package's kernels by their number of rows: at most 16 (decode) to the
-weight-streaming kernel on mma.sync (``gemm_skinny.cu``), up to 128 (larger decode batches, short
-portions, mixed steps) to the tcgen05 kernel that streams the weights in equal shares
-(``gemm_rows.cu``), more to the tcgen05 kernel with pairs of CTAs on 256 x 256 tiles
-(``gemm_tc05.cu``). The reference sends every projection and the LM head to ``cublasGemmEx``
-(src/source/op/kernels/cuda/matmul_kernel.cu:128-150); the library product behind ``torch.mm`` (fp32
-accumulation) is kept for tensors that the kernels do not take (rows that are not 16-byte aligned)
-and can be had for every many-row product with SI_OWN_GEMM=0 in the environment.
+mode). bf16 products go by their number of rows: at most 16 (decode) to the package's
+weight-streaming kernel on mma.sync (``gemm_skinny.cu``); 128 and more (prompt portions) to its
+tcgen05 kernel, pairs of CTAs on 256 x 256 tiles (``gemm_tc05.cu``); 17 to 127 rows (larger decode
+batches, short portions) to the library product behind ``torch.mm`` (cuBLAS, fp32 accumulation), as
+the reference sends every projection and the LM head to ``cublasGemmEx``
+(src/source/op/kernels/cuda/matmul_kernel.cu:128-150). The package has a tcgen05 kernel for those
+row counts too (``gemm_rows.cu``, SI_OWN_ROWS=1 turns it on), but at the shapes measured the library
+is still 1.2 to 3 times faster there. The library also takes what the kernels refuse (rows that are
+not 16-byte aligned), and every many-row product with SI_OWN_GEMM=0.
 """
 from __future__ import annotations
 
@@ -20,9 +21,9 @@ from ..csrc import ops
 
 
 USE_SKINNY = True      # few-row products (decode) through this package's weight-streaming kernel
-USE_ROWS = os.environ.get("SI_OWN_ROWS", "1") == "1"      # 17 to 128 rows through gemm_rows.cu (0: the library)
-USE_OWN_GEMM = os.environ.get("SI_OWN_GEMM", "1") == "1"  # more rows through gemm_tc05.cu (0: the library)
-OWN_GEMM_MIN_ROWS = 129
+USE_ROWS = os.environ.get("SI_OWN_ROWS", "0") == "1"      # 17 to 127 rows through gemm_rows.cu (default: the library)
+USE_OWN_GEMM = os.environ.get("SI_OWN_GEMM", "1") == "1"  # 128 rows and more through gemm_tc05.cu (0: the library)
+OWN_GEMM_MIN_ROWS = 128
 
 
 def configure_library_gemm() -> None:
@@ -49,7 +50,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status=None) -> 
         ops.gemm_f32(x, w, out)
     elif USE_SKINNY and ops.gemm_skinny_ok(x, w, out):
         ops.gemm_skinny(x, w, out, checked=True)
-    elif USE_ROWS and x.shape[0] <= ops.ROWS_MAX and ops.gemm_tc05_available() and ops.gemm_rows_ok(x, w, out):
+    elif USE_ROWS and x.shape[0] < OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available() and ops.gemm_rows_ok(x, w, out):
         ops.gemm_rows(x, w, out, status)
     elif (USE_OWN_GEMM and x.shape[0] >= OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available()
           and ops.gemm_tc05_ok(x, w, out)):

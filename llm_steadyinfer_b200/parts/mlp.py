@@ -3,9 +3,10 @@ block computes it (src/source/model/llama3.cpp:1149-1180). gate and up are stack
 [2F, d] matrix at load so one product feeds the activation: when F is a multiple of 8 the rows
 are interleaved in groups of 8 (8 rows of gate, the 8 rows of up that belong to them, ...), so
 that the few-row product holds a gate and its up in one block and applies the activation in
-its epilogue. So do the products on the tcgen05 tensor cores (``gemm_rows.cu`` up to 128 rows,
-``gemm_tc05.cu`` above); where none applies (fp32, an intermediate size that is no multiple of 8), the
-product runs alone and the activation kernel reads the same interleaved columns.
+its epilogue. So does the product on the tcgen05 tensor cores for 128 rows and more (``gemm_tc05.cu``;
+``gemm_rows.cu`` below that, when it is turned on); where none applies (fp32, an intermediate size that is
+no multiple of 8, 17 to 127 rows by default), the product runs alone and the activation kernel reads the
+same interleaved columns.
 """
 from __future__ import annotations
 
@@ -60,13 +61,13 @@ class GatedMLP(FeedForward):
         if (self.group == INTERLEAVE and linear_mod.USE_SKINNY and act.dtype == torch.bfloat16
                 and ops.gemm_skinny_ok(x, self.gate_up, act)):
             ops.gemm_skinny_swiglu(x, self.gate_up, act, checked=True)
-        elif (self.group == INTERLEAVE and USE_TC05_GEMM and act.dtype == torch.bfloat16
-                and ops.gemm_tc05_available() and ops.gemm_tc05_ok(x, self.gate_up, act)
-                and (linear_mod.USE_ROWS if T <= ops.ROWS_MAX else linear_mod.USE_OWN_GEMM)):
-            if T <= ops.ROWS_MAX:
-                ops.gemm_rows_swiglu(x, self.gate_up, act, ctx.status)
-            else:
+        elif (self.group == INTERLEAVE and USE_TC05_GEMM and act.dtype == torch.bfloat16 and ops.gemm_tc05_available()
+                and ops.gemm_tc05_ok(x, self.gate_up, act)
+                and (linear_mod.USE_OWN_GEMM if T >= linear_mod.OWN_GEMM_MIN_ROWS else linear_mod.USE_ROWS)):
+            if T >= linear_mod.OWN_GEMM_MIN_ROWS:
                 ops.gemm_tc05_swiglu(x, self.gate_up, act, ctx.status)
+            else:
+                ops.gemm_rows_swiglu(x, self.gate_up, act, ctx.status)
         else:
             gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
             linear(x, self.gate_up, gu, ctx.status)

@@ -398,13 +398,16 @@ def test_trace_run_program_with_truncate_records(folders, plains, tmp_path):
     assert checked > 100
 
 
+@pytest.mark.parametrize("own_rows", [False, True], ids=["library", "gemm_rows"])
 @pytest.mark.parametrize("name", ["C"])
-def test_graph_decode_logits_at_17_to_64_rows(folders, plains, name):
+def test_graph_decode_logits_at_17_to_64_rows(folders, plains, name, own_rows, monkeypatch):
     """Decode steps of 17 to 64 live requests, bfloat16, through the recorded step: above 16 rows every
-    projection leaves the few-row product, the gate/up product and the activation are two kernels, decode
-    attention gets more items than one wave of shares, and the buckets 24, 32, 48 and 64 are recorded.
-    Every row of every step against the plain implementation."""
+    projection leaves the few-row product (for the library product, or for the package's tcgen05 kernel for up
+    to 128 rows when that is turned on), decode attention gets more items than one wave of shares, and the
+    buckets 24, 32, 48 and 64 are recorded. Every row of every step against the plain implementation."""
     import random
+    from llm_steadyinfer_b200.parts import linear as linear_mod
+    monkeypatch.setattr(linear_mod, "USE_ROWS", own_rows)
     from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
     from llm_steadyinfer_b200.weights import load_model
     cfg, cseed, page = CONFIGS[name]
