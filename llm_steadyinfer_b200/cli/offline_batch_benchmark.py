@@ -133,7 +133,7 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
     mk = lambda i: SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                                   seed=args.seed * 100003 + i, max_tokens=out_lens[i], ignore_eos=args.ignore_eos)
     rejected, pending, ids = 0, list(range(len(prompts))), {}
-    steps0, pre0 = sched.num_steps, sched.num_preemptions
+    steps0, pre0, rec0 = sched.num_steps, sched.num_preemptions, sched.num_recomputed_tokens
     used_sum = alloc_sum = running_sum = samples = peak_pages = 0
     ps = llm.runner.page_size
     start = time.monotonic()
@@ -180,6 +180,7 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
         "kv_cache_frag_global": round(1 - used_sum / alloc_sum, 4) if alloc_sum else 0.0,
         "peak_kv_blocks": peak_pages, "avg_batch_size": round(running_sum / samples, 3) if samples else 0.0,
         "steps": sched.num_steps - steps0, "preemptions": sched.num_preemptions - pre0,
+        "recomputed_tokens": sched.num_recomputed_tokens - rec0,
         "prefix_hit_tokens": sum(s.prefix_hit_tokens for s in fin),
         "finish_reasons": dict((r, sum(1 for s in fin if s.finish_reason == r)) for r in {s.finish_reason for s in fin}),
     }

@@ -134,6 +134,7 @@ class Scheduler:
         self._admissions = itertools.count()
         self.num_steps = 0
         self.num_preemptions = 0
+        self.num_recomputed_tokens = 0        # tokens whose keys and values a preemption gave up
 
     # ---- requests ------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -356,6 +357,7 @@ class Scheduler:
         newly = []
         for s, keep in plan:
             new_len = self.cache.truncate(s.id, keep * ps)
+            self.num_recomputed_tokens += max(0, s.num_computed - new_len)
             s.num_computed = min(s.num_computed, new_len)
             if s.state is SeqState.RUNNING:
                 s.state = SeqState.PREEMPTED

@@ -517,7 +517,7 @@ def test_long_context_replay(long_model, dtype):
     from llm_steadyinfer_b200.engine.replay import Replayer
     folder, plain, long_toks = long_model
     V = LONG["vocab_size"]
-    short_toks = ru.random_tokens(V, 40 + 96, 2)
+    short_toks = ru.random_tokens(V, 40 + 95, 2)
     ref = plain.of(long_toks)
     steps, p = [], 0
 
@@ -548,7 +548,7 @@ def test_long_context_replay(long_model, dtype):
     for _ in range(16):
         portion(1, short_row())
     steps[-1]["end"] = ["L", "S"]
-    assert p == 9016 and sp == 136
+    assert p == 9016 and sp == 135
     reqs = {"L": long_toks, "S": short_toks}
     if dtype == torch.float32:
         atol = 5e-5
