@@ -5,11 +5,13 @@
 //   ref_bench verify <model.bin> <max_seq> <prompt file>
 //       greedy tokens of two requests through scheduler::Scheduler on the CUDA device ("SEQ <id> gen: ..."),
 //       for comparison with the tokens its CPU device gave (tests/golden).
-//   ref_bench bench <model.bin> <batch> <ctx> <steps> <warmup> <sched_rows>
+//   ref_bench bench <model.bin> <batch> <ctx> <steps> <warmup> <sched_rows> <ctx2>
 //       value: model::Model::decode_step (its CUDA-graph decode path) on `batch` sequences whose contexts end
-//              at `ctx`, timed on the device with CUDA events around `steps` steps after `warmup`;
-//       e2e:   the same workload through scheduler::Scheduler::step (host tokens in, sampled tokens out every
-//              step), prompts prefilled by the scheduler itself, `sched_rows` = its max_batch_size (rows a step).
+//              near `ctx`, timed on the device with CUDA events around `steps` steps after `warmup`;
+//       e2e:   the same steps with host tokens in and sampled tokens out every step (decode_step, stream sync,
+//              post_processing_batch: what its Scheduler runs for a decode step);
+//       and `batch` prompts of 4/5 of `ctx2` tokens through scheduler::Scheduler itself (`sched_rows` = its
+//       max_batch_size, the rows of a step), timed while all of them decode.
 #include "model/llama3.h"
 #include "scheduler/scheduler.h"
 #include <base/alloc.h>
@@ -65,21 +67,25 @@ static int verify(int argc, char** argv) {
 }
 
 static int bench(int argc, char** argv) {
-  if (argc < 8) return 2;
+  if (argc < 9) return 2;
   const char* bin = argv[2];
   const int batch = atoi(argv[3]), ctx = atoi(argv[4]), steps = atoi(argv[5]), warm = atoi(argv[6]);
-  const int rows = atoi(argv[7]);
+  const int rows = atoi(argv[7]), ctx2 = atoi(argv[8]);      // scheduler run: rows a step, context of the short workload
   auto m = load(bin);
   const int L = m->layer_num(), kvd = m->kv_dim(), V = m->vocab_size();
   if (ctx > m->seq_len() || batch < 1 || steps < 1 || rows < batch) {
     printf("{\"error\": \"bad sizes\"}\n");
     return 2;
   }
+  // The reference forms a tensor's size as a product of 32-bit ints (src/source/tensor/tensor.cpp:85).
+  if ((long long)L * batch * kvd * ctx >= (1ll << 31)) {
+    printf("{\"error\": \"cache of %d x %d x %d x %d elements overflows the reference's 32-bit tensor size\"}\n", L, batch, kvd, ctx);
+    return 5;
+  }
   auto cu = base::CUDADeviceAllocatorFactory::get_instance();
   auto cpu = base::CPUDeviceAllocatorFactory::get_instance();
-  double dev_ms = 0.0;
+  double dev_ms = 0.0, e2e_s = 0.0;
   {
-    // ---- device-timed decode steps through Model::decode_step ------------------------------------------
     tensor::Tensor kc(base::DataType::kDataTypeFp32, L, batch, kvd, ctx, true, cu);
     tensor::Tensor vc(base::DataType::kDataTypeFp32, L, batch, kvd, ctx, true, cu);
     tensor::Tensor logits(base::DataType::kDataTypeFp32, batch, V, true, cu);
@@ -92,12 +98,14 @@ static int bench(int argc, char** argv) {
     cudaMemset(vc.ptr<float>(), 0, cache_bytes);
     tensor::Tensor ids(base::DataType::kDataTypeInt32, batch, true, cpu), pos(base::DataType::kDataTypeInt32, batch, true, cpu),
         slots(base::DataType::kDataTypeInt32, batch, true, cpu);
-    const int start = ctx - (steps + warm) - 1;
+    // ---- value: device-timed decode steps through Model::decode_step -----------------------------------
+    const int start = ctx - 2 * (steps + warm) - 2;
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
     unsigned rng = 12345u;
-    for (int i = 0; i < warm + steps; ++i) {
+    int p = start;
+    for (int i = 0; i < warm + steps; ++i, ++p) {
       if (i == warm) {
         m->sync_stream();
         cudaEventRecord(e0, 0);
@@ -105,7 +113,7 @@ static int bench(int argc, char** argv) {
       for (int b = 0; b < batch; ++b) {
         rng = rng * 1664525u + 1013904223u;
         ids.ptr<int32_t>()[b] = (int)((rng >> 8) % (unsigned)V);
-        pos.ptr<int32_t>()[b] = start + i;
+        pos.ptr<int32_t>()[b] = p;
         slots.ptr<int32_t>()[b] = b;
       }
       auto st = m->decode_step(ids, pos, slots, kc, vc, logits);
@@ -120,73 +128,89 @@ static int bench(int argc, char** argv) {
     cudaEventElapsedTime(&ms, e0, e1);
     dev_ms = ms;
     if (!cuda_ok("the decode_step loop")) return 4;
+    // ---- e2e: what its Scheduler does in a decode step (scheduler.cpp:557-610): host tokens and positions in,
+    // decode_step, stream sync, post_processing_batch (argmax kernel, token ids back to the host), and the
+    // sampled tokens are the next step's inputs. The Scheduler itself cannot hold this workload: it caps the
+    // rows of a step, prompt rows included, at max_batch, which also sizes the cache.
+    std::vector<int32_t> next(batch, 1);
+    auto one = [&]() {
+      for (int b = 0; b < batch; ++b) {
+        ids.ptr<int32_t>()[b] = next[b];
+        pos.ptr<int32_t>()[b] = p;
+        slots.ptr<int32_t>()[b] = b;
+      }
+      ++p;
+      auto st = m->decode_step(ids, pos, slots, kc, vc, logits);
+      if (!st) return false;
+      m->sync_stream();
+      next = m->post_processing_batch(logits);
+      return true;
+    };
+    for (int i = 0; i < 2; ++i)
+      if (!one()) { printf("{\"error\": \"decode_step failed\"}\n"); return 6; }
+    auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < steps; ++i)
+      if (!one()) { printf("{\"error\": \"decode_step failed\"}\n"); return 6; }
+    e2e_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (!cuda_ok("the end-to-end loop")) return 4;
   }
   cu->free_idle();
 
-  // ---- end to end through the Scheduler ------------------------------------------------------------------
-  // Prompts are staggered so that, when the last one has been prefilled, every request stands at about the same
-  // context: request j's prompt takes about ceil(P_j / (rows - j)) steps while the j requests before it decode.
-  const int T0 = ctx - (steps + warm) - 8;
-  std::vector<int> P(batch);
-  {
-    long after = 0;
-    for (int j = batch - 1; j >= 0; --j) {
-      P[j] = (int)std::max<long>(16, T0 - after);
-      after += (P[j] + (rows - j) - 1) / (rows - j);
+  // ---- the short workload through the Scheduler itself: `batch` prompts of ctx2 * 4 / 5 tokens. Its prompts go in
+  // one after the other (rows of a step are capped at `rows`), so the first request has generated some hundred
+  // tokens when the last one starts to decode: the requests get room to generate 3/5 of ctx2, and `steps` steps
+  // are timed from the moment all of them decode (their contexts then lie between 4/5 and about ctx2).
+  double sched_tps = 0.0, sched_ms = 0.0, sched_ctx = 0.0;
+  long sched_steps = 0, prefill_steps = 0;
+  const int cap2 = ctx2 * 7 / 5;
+  if (ctx2 > 0 && (long long)L * rows * kvd * cap2 < (1ll << 31) && cap2 <= m->seq_len()) {
+    const int plen = ctx2 * 4 / 5;
+    scheduler::Scheduler s(m, rows, cap2, cap2 - plen, 0);
+    unsigned rng = 777u;
+    for (int j = 0; j < batch; ++j) {
+      std::vector<int> prompt(plen);
+      for (auto& t : prompt) {
+        rng = rng * 1664525u + 1013904223u;
+        t = (int)((rng >> 8) % (unsigned)V);
+      }
+      if (s.add_request(prompt) < 0) {
+        printf("{\"error\": \"request rejected\"}\n");
+        return 7;
+      }
     }
+    auto all_decoding = [&]() {
+      if ((int)s.get_running().size() != batch) return false;
+      for (auto& q : s.get_running())
+        if (!q.is_prefill_complete || q.generated_tokens.empty()) return false;
+      return true;
+    };
+    while (!all_decoding()) {
+      s.step();
+      if (++prefill_steps > 1000000 || (s.get_running().empty() && s.num_waiting() == 0)) {
+        printf("{\"error\": \"the scheduler never reached %d decoding requests\"}\n", batch);
+        return 8;
+      }
+    }
+    for (int i = 0; i < 3; ++i) s.step();
+    m->sync_stream();
+    for (auto& q : s.get_running()) sched_ctx += q.total_tokens() / (double)batch;
+    auto t0 = std::chrono::steady_clock::now();
+    while ((int)s.get_running().size() == batch && sched_steps < steps) {
+      s.step();
+      ++sched_steps;
+    }
+    m->sync_stream();
+    const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    sched_tps = (double)batch * sched_steps / dt;
+    sched_ms = dt * 1e3 / (sched_steps ? sched_steps : 1);
+    if (!cuda_ok("the scheduler steps")) return 4;
   }
-  scheduler::Scheduler s(m, rows, ctx, ctx, 0);
-  unsigned rng = 777u;
-  for (int j = 0; j < batch; ++j) {
-    std::vector<int> prompt(P[j]);
-    for (auto& t : prompt) {
-      rng = rng * 1664525u + 1013904223u;
-      t = (int)((rng >> 8) % (unsigned)V);
-    }
-    if (s.add_request(prompt) < 0) {
-      printf("{\"error\": \"request rejected\"}\n");
-      return 7;
-    }
-  }
-  long prefill_steps = 0;
-  auto all_decoding = [&]() {
-    if ((int)s.get_running().size() != batch) return false;
-    for (auto& q : s.get_running())
-      if (!q.is_prefill_complete || q.generated_tokens.empty()) return false;
-    return true;
-  };
-  auto t_pre = std::chrono::steady_clock::now();
-  while (!all_decoding()) {
-    s.step();
-    if (++prefill_steps > 2000000 || (s.get_running().empty() && s.num_waiting() == 0)) {
-      printf("{\"error\": \"the scheduler never reached %d decoding requests\"}\n", batch);
-      return 8;
-    }
-  }
-  double prefill_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_pre).count();
-  for (int i = 0; i < warm; ++i) s.step();
-  auto tokens_now = [&]() {
-    long n = 0;
-    for (auto& q : s.get_running()) n += q.num_generated_tokens;
-    for (auto& q : s.get_finished()) n += q.num_generated_tokens;
-    return n;
-  };
-  double ctx_sum = 0;
-  for (auto& q : s.get_running()) ctx_sum += q.total_tokens();
-  const double ctx_start = ctx_sum / batch;
-  m->sync_stream();
-  const long n0 = tokens_now();
-  auto t0 = std::chrono::steady_clock::now();
-  for (int i = 0; i < steps; ++i) s.step();
-  m->sync_stream();
-  const double e2e_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-  const long made = tokens_now() - n0;
-  const int still = (int)s.get_running().size();
-  if (!cuda_ok("the scheduler steps")) return 4;
-  printf("{\"device_ms\": %.4f, \"steps\": %d, \"batch\": %d, \"e2e_s\": %.6f, \"e2e_tokens\": %ld, \"running_at_end\": %d, "
-         "\"e2e_context_start\": %.1f, \"prefill_steps\": %ld, \"prefill_s\": %.2f, \"sched_rows\": %d, "
-         "\"h2d_bytes_per_step\": %d, \"d2h_bytes_per_step\": %d}\n",
-         dev_ms, steps, batch, e2e_s, made, still, ctx_start, prefill_steps, prefill_s, rows, 3 * batch * 4, batch * 4);
+  printf("{\"device_ms\": %.4f, \"steps\": %d, \"batch\": %d, \"context\": %d, \"e2e_s\": %.6f, \"e2e_tokens\": %ld, "
+         "\"h2d_bytes_per_step\": %d, \"d2h_bytes_per_step\": %d, \"sched_context\": %d, \"sched_rows\": %d, "
+         "\"sched_prefill_steps\": %ld, \"sched_decode_steps\": %ld, \"sched_tokens_per_s\": %.1f, \"sched_ms_per_step\": %.4f, "
+         "\"sched_mean_context\": %.1f}\n",
+         dev_ms, steps, batch, ctx, e2e_s, (long)batch * steps, 3 * batch * 4, batch * 4, ctx2, rows, prefill_steps,
+         sched_steps, sched_tps, sched_ms, sched_ctx + sched_steps / 2.0);
   fflush(stdout);
   _exit(0);      // skip the destructors of the reference's globals
 }

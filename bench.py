@@ -167,6 +167,11 @@ def reference_arm(args) -> int:
     B, CTX = args.batch, args.context
     cfg = dict(LLAMA_3_1_8B)
     L = args.layers or cfg["num_hidden_layers"]
+    # The reference forms a tensor's size as a product of 32-bit ints (src/source/tensor/tensor.cpp:85): its cache
+    # [layers, batch, kv_dim, context] must stay below 2^31 elements. At this shape and batch 8 that is a context
+    # of 8,191, one token short of the bench's; it runs there.
+    kv_dim = cfg["num_key_value_heads"] * (cfg["hidden_size"] // cfg["num_attention_heads"])
+    CTX = min(CTX, ((1 << 31) - 1) // (L * B * kv_dim))
     d, F, V, H, KV = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
     hs = d // H
     floats = 2 * V * d + L * (2 * d + 2 * H * hs * d + 2 * KV * hs * d + 3 * F * d) + d + CTX * hs
@@ -185,7 +190,7 @@ def reference_arm(args) -> int:
         write_reference_weights(path, cfg, CTX, L)
         env = dict(os.environ, SHIM_VOCAB=str(V))
         clocks.start()
-        proc = subprocess.run([exe, "bench", path, str(B), str(CTX), str(K), str(W), str(rows)], env=env,
+        proc = subprocess.run([exe, "bench", path, str(B), str(CTX), str(K), str(W), str(rows), "1280"], env=env,
                               capture_output=True, text=True, timeout=1500)
         clocks.stop()
     except subprocess.TimeoutExpired:
@@ -197,10 +202,11 @@ def reference_arm(args) -> int:
         shutil.rmtree(folder, ignore_errors=True)
     lines = [l for l in proc.stdout.strip().splitlines() if l.startswith("{")]
     if proc.returncode != 0 or not lines:
-        return unavailable(f"the reference's run failed (exit {proc.returncode}): {(lines[-1] if lines else proc.stderr[-300:])}")
+        return unavailable(f"the reference's run failed (exit {proc.returncode}): {lines[-1] if lines else ''}; "
+                           f"its log ends: {proc.stderr[-400:]}")
     r = json.loads(lines[-1])
     if "error" in r:
-        return unavailable(f"the reference's run failed: {r['error']}")
+        return unavailable(f"the reference's run failed: {r['error']}; its log ends: {proc.stderr[-400:]}")
     ms_per_step = r["device_ms"] / K
     out = {
         "metric": "decode tokens/s, Llama-3.1-8B shape, batch 8, context 8192", "value": round(B * K / r["device_ms"] * 1e3, 1),
@@ -210,11 +216,13 @@ def reference_arm(args) -> int:
         "config": {"model": "Llama-3.1-8B shape", "layers": L, "layers_full": cfg["num_hidden_layers"], "hidden": d, "heads": H,
                    "kv_heads": KV, "head_dim": hs, "intermediate": F, "vocab": V, "global_batch": B, "seq_len": CTX,
                    "parallelism": "single_gpu", "cuda_graph": True, "kv_layout": "continuous (USE_PAGED_ATTENTION off)",
-                   "scheduler_rows": rows},
+                   "scheduler_rows": rows, "seq_len_note": "largest context its 32-bit tensor sizes hold at this batch"},
         "e2e": {"value": round(r["e2e_tokens"] / r["e2e_s"], 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"],
-                "context_at_start": r["e2e_context_start"], "requests_running_at_end": r["running_at_end"],
-                "prefill_steps": r["prefill_steps"], "prefill_s": r["prefill_s"]},
+                "how": "Model::decode_step + post_processing_batch every step, as its Scheduler runs a decode step"},
+        # 1,024-token prompts and 256 generated tokens through its own Scheduler, timed while all requests decode
+        "points": {"decode_b8_ctx1280_scheduler": r["sched_tokens_per_s"], "decode_b8_ctx1280_scheduler_ms": r["sched_ms_per_step"],
+                   "decode_b8_ctx1280_scheduler_mean_context": r.get("sched_mean_context")},
         "clocks": clocks.summary(),
     }
     print(json.dumps(out))

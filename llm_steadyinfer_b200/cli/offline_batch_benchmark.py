@@ -49,6 +49,8 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     ap.add_argument("--kv-block-size", type=int, default=None, help="default 8/16/32 by mean prompt length (scheduler.cpp:11-15)")
     ap.add_argument("--num-kv-blocks", type=int, default=None)
     ap.add_argument("--max-num-batched-tokens", default="adaptive", help="prompt tokens per step, or 'adaptive'")
+    ap.add_argument("--admit-on-first-portion", action="store_true",
+                    help="admit a request when the pages of its first portion are free (default: of its whole prompt)")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-prefix-cache", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=256)
@@ -211,7 +213,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     budget = args.max_num_batched_tokens if args.max_num_batched_tokens == "adaptive" else int(args.max_num_batched_tokens)
     llm = LLM(model, dtype=dtype, max_batch=args.max_batch, max_seq_len=max_len, max_gen_len=args.max_gen,
               block_size=block, num_blocks=args.num_kv_blocks, max_num_batched_tokens=budget,
-              enable_prefix_cache=not args.no_prefix_cache, use_cuda_graph=not args.no_cuda_graph)
+              enable_prefix_cache=not args.no_prefix_cache, use_cuda_graph=not args.no_cuda_graph,
+              reserve="portion" if args.admit_on_first_portion else "prompt")
     rows = []
     for it in range(args.iterations):
         m = run_once(llm, prompts, out_lens, args, it, rng)

@@ -16,9 +16,28 @@
 // groups of 8 rows of W, so that a block's 16 columns are 8 gates and the 8 ups that belong to
 // them: the block stores out[m, f] = silu(gate) * up (both rounded to bf16 first, as when the
 // projection is stored and a second kernel applies the activation) and no second kernel runs.
+//
+// With ROPE the product is the stacked q/k/v projection of a decode step, and what the position-encoding kernel
+// would do next happens in the epilogue: a block's 16 columns are 8 columns of the first half of one head and
+// their rotation partners in the second half (rotate-half pairs (i, i + head_dim / 2), as in
+// src/source/op/kernels/cuda/rope_kernel.cu:113-148), so one thread holds both elements of a pair of one row. It
+// rounds them to bf16 (as the stored projection would be), rotates q and k heads by the row's position (angle,
+// sine and cosine in fp32), writes q heads to the output and k and v heads straight into the row's cache page.
 #include "common.cuh"
 
 typedef __nv_bfloat16 bf16;
+
+// What the ROPE epilogue needs beside the product's own arguments.
+struct SkinnyRope {
+  const int* positions;      // [M]
+  const int* row_seq;        // [M], -1: a padding row, nothing is stored for it
+  const float* inv_freq;     // [head_dim / 2]
+  const int* block_table;    // [num_seqs, table_width]
+  bf16* k_cache;             // [num_pages, KV, page_size, head_dim] or null (nothing is stored)
+  bf16* v_cache;
+  int table_width, num_pages, page_size, num_seqs, H, KV, hs;
+  int* status;
+};
 
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -45,17 +64,20 @@ __device__ __forceinline__ uint4 ld_cached(const bf16* p) {      // x: small, sh
 
 // Rows of W or x beyond N or M are replaced by row 0: their products land in output elements
 // that are never stored, so the loads need no predicate.
-template <int MT, int WARPS, int UNROLL, typename TO, bool SWIGLU = false>
+template <int MT, int WARPS, int UNROLL, typename TO, bool SWIGLU = false, bool ROPE = false>
 __global__ void __launch_bounds__(WARPS * 32, 512 / (WARPS * 32))
 gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W, long long ldw,
-                   TO* __restrict__ out, long long ldo, int M, int N, int K, int trigger) {
+                   TO* __restrict__ out, long long ldo, int M, int N, int K, int trigger, const SkinnyRope rope) {
   __shared__ float red[WARPS][MT][32][4];
   if (trigger == 1) pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * 16;
+  // the block's 16 rows of W: n0 .. n0+7 and n1 .. n1+7 (next to each other, or a rotation's two halves)
+  const int per_head = ROPE ? rope.hs / 16 : 1;
+  const int n0 = ROPE ? (blockIdx.x / per_head) * rope.hs + (blockIdx.x % per_head) * 8 : blockIdx.x * 16;
+  const int n1 = ROPE ? n0 + rope.hs / 2 : n0 + 8;
   const bf16* w0 = W + (size_t)(n0 + g < N ? n0 + g : 0) * ldw + t * 8;
-  const bf16* w1 = W + (size_t)(n0 + g + 8 < N ? n0 + g + 8 : 0) * ldw + t * 8;
+  const bf16* w1 = W + (size_t)(n1 + g < N ? n1 + g : 0) * ldw + t * 8;
   float acc[MT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
@@ -138,7 +160,46 @@ gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __rest
 #pragma unroll
     for (int e = 0; e < 4; ++e) red[warp][mt][lane][e] = acc[mt][e];
   __syncthreads();
-  if constexpr (SWIGLU) {
+  if constexpr (ROPE) {
+    // threads (mt, lane, e) add the partial sums of the two elements of one rotation pair of one row
+    const int head = blockIdx.x / per_head, half = rope.hs / 2;
+    for (int idx = threadIdx.x; idx < MT * 32 * 2; idx += WARPS * 32) {
+      const int mt = idx / 64, ln = (idx >> 1) & 31, e = idx & 1;
+      float a = 0.f, b = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) { a += red[w][mt][ln][e]; b += red[w][mt][ln][e + 2]; }
+      const int m = mt * 8 + (ln & 3) * 2 + e;
+      if (m >= M) continue;
+      const int i = (blockIdx.x % per_head) * 8 + (ln >> 2);       // index in the head's first half
+      const float x0 = __bfloat162float(__float2bfloat16_rn(a)), x1 = __bfloat162float(__float2bfloat16_rn(b));
+      float y0 = x0, y1 = x1;
+      const int pos = rope.positions[m];
+      if (head < rope.H + rope.KV) {
+        float sn, cs;
+        sincosf((float)pos * rope.inv_freq[i], &sn, &cs);
+        y0 = x0 * cs - x1 * sn;
+        y1 = x1 * cs + x0 * sn;
+      }
+      if (head < rope.H) {
+        bf16* dst = (bf16*)out + (size_t)m * ldo + (size_t)head * rope.hs + i;
+        dst[0] = __float2bfloat16_rn(y0);
+        dst[half] = __float2bfloat16_rn(y1);
+        continue;
+      }
+      const int seq = rope.row_seq[m];
+      if (!rope.k_cache || seq < 0) continue;                      // a layer that stores nothing, or a padding row
+      if (seq >= rope.num_seqs) { set_status(rope.status, SI_BAD_SEQ); continue; }
+      const int slot = pos / rope.page_size;
+      const int page = (pos >= 0 && slot < rope.table_width) ? rope.block_table[(size_t)seq * rope.table_width + slot] : -1;
+      if (page < 0 || page >= rope.num_pages) { set_status(rope.status, SI_BAD_PAGE); continue; }
+      const bool is_k = head < rope.H + rope.KV;
+      const int kvh = head - rope.H - (is_k ? 0 : rope.KV);
+      bf16* dst = (is_k ? rope.k_cache : rope.v_cache) +
+                  (((size_t)page * rope.KV + kvh) * rope.page_size + pos % rope.page_size) * rope.hs + i;
+      dst[0] = __float2bfloat16_rn(y0);
+      dst[half] = __float2bfloat16_rn(y1);
+    }
+  } else if constexpr (SWIGLU) {
     // threads (mt, lane, e) add the partial sums of gate (element e) and up (element e + 2) of one output
     for (int idx = threadIdx.x; idx < MT * 32 * 2; idx += WARPS * 32) {
       const int mt = idx / 64, ln = (idx >> 1) & 31, e = idx & 1;
@@ -178,11 +239,11 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
   if (out_dtype == SI_BF16) {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
   } else {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
+    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
+    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
   }
   return si_last_error();
 }
@@ -198,7 +259,36 @@ SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W,
   const unsigned blocks = (unsigned)(F / 8);
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
-  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()));
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
+  return si_last_error();
+}
+
+// The stacked q/k/v projection of at most 16 rows with the rotation of q and k and the store of k and v into
+// the cache pages in its epilogue (see the head of this file): x [M, K], W [(H + 2 KV) * hs, K] with q heads
+// first, then k, then v; `out` [M, >= H * hs] bf16 takes the rotated q heads. hs a multiple of 16 with the whole
+// head rotated (rot_dim == hs). k_cache / v_cache null: nothing is stored. Returns -2 for what it does not take.
+SI_EXPORT int si_gemm_skinny_qkv_rope(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
+                                      int M, int K, const int* positions, const int* row_seq, const float* inv_freq,
+                                      const int* block_table, int table_width, void* k_cache, void* v_cache,
+                                      int num_pages, int page_size, int num_seqs, int H, int KV, int hs, int* status,
+                                      cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || H <= 0 || KV <= 0 || hs <= 0 || (hs % 16)) return -2;
+  if (((uintptr_t)x % 16) || ((uintptr_t)W % 16) || !positions || !row_seq || !inv_freq || page_size <= 0) return -2;
+  if (k_cache && (!v_cache || !block_table)) return -2;
+  constexpr int WARPS = 8, UNROLL = 8;
+  const int N = (H + 2 * KV) * hs;
+  const unsigned blocks = (unsigned)((H + 2 * KV) * (hs / 16));
+  SkinnyRope r;
+  r.positions = positions; r.row_seq = row_seq; r.inv_freq = inv_freq; r.block_table = block_table;
+  r.k_cache = (bf16*)k_cache; r.v_cache = (bf16*)v_cache;
+  r.table_width = table_width; r.num_pages = num_pages; r.page_size = page_size; r.num_seqs = num_seqs;
+  r.H = H; r.KV = KV; r.hs = hs; r.status = status;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  const int trig = si_pdl_trigger_mode(blocks, 2 * si_sm_count());
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, false, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, trig, r);
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, false, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, trig, r);
   return si_last_error();
 }

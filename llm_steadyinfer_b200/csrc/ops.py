@@ -593,6 +593,37 @@ def gemm_skinny_swiglu(a, w, out, checked: bool = False) -> None:
            f"gemm_skinny_swiglu(M={M}, F={F}, K={K})")
 
 
+def gemm_skinny_qkv_rope(a, w, out, positions, row_seq, inv_freq, block_table, k_cache, v_cache, page_size: int,
+                         num_seqs: int, H: int, KV: int, hs: int, status=None) -> None:
+    """The stacked q/k/v projection of at most 16 rows with what ``rope_kv_write`` would do next in its epilogue:
+    q and k heads rotated by their row's position (the whole head, rotate-half pairs), q written to
+    ``out[:, :H*hs]``, k and v stored into the rows' cache pages (``k_cache`` None: nothing stored). The k and v
+    columns of ``out`` are left as they are."""
+    _cuda(a, w, out, positions, row_seq, inv_freq, block_table, k_cache, v_cache, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    M, K = a.shape
+    _need(w.shape == ((H + 2 * KV) * hs, K) and out.shape[0] == M and out.shape[1] >= H * hs and out.dtype == torch.bfloat16,
+          "gemm_skinny_qkv_rope: w must be [(H + 2 KV) * hs, K], out [M, >= H * hs] bf16")
+    _need(gemm_skinny_ok(a, w, out) and hs % 16 == 0, "gemm_skinny_qkv_rope: bf16 inputs, at most 16 rows, K a multiple of 8, "
+          "16-byte aligned rows, head_dim a multiple of 16")
+    _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == hs,
+          "gemm_skinny_qkv_rope: inv_freq must be fp32 [head_dim / 2] (the whole head is rotated)")
+    _need(positions.numel() == M and row_seq.numel() == M, "gemm_skinny_qkv_rope: one position and sequence per row")
+    num_pages = 0
+    if k_cache is not None:
+        _need(k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16 and k_cache.is_contiguous()
+              and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (KV, page_size, hs)
+              and k_cache.shape == v_cache.shape, "gemm_skinny_qkv_rope: cache must be bf16 [pages, KV, page_size, hs]")
+        num_pages = k_cache.shape[0]
+    f = _fn("gemm_skinny", "si_gemm_skinny_qkv_rope",
+            [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p,
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, K, _ptr(positions), _ptr(row_seq),
+             _ptr(inv_freq), _ptr(block_table), block_table.shape[1] if block_table is not None else 0, _ptr(k_cache),
+             _ptr(v_cache), num_pages, page_size, num_seqs, H, KV, hs, _ptr(status), _stream()),
+           f"gemm_skinny_qkv_rope(M={M}, heads={H}, kv_heads={KV}, head_dim={hs})")
+
+
 # ---- tcgen05 matrix product (many rows) -------------------------------------------------------
 
 _weight_maps = {}

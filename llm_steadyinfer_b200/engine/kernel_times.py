@@ -26,7 +26,7 @@ KINDS = {
     "paged_attention_ref": "attention_ref", "swiglu": "swiglu", "gemm_f32": "gemm_f32",
     "sample": "sampling", "argmax": "sampling", "attn_portion": "attn_portion_mma", "attn_decode": "attn_decode_mma",
     "attn_decode_tma": "attn_decode_tma", "attn_portion_tc05": "attn_portion_tc05", "gemm_skinny": "gemm_skinny",
-    "gemm_skinny_swiglu": "gemm_skinny_swiglu", "gemm_tc05": "gemm_tc05", "gemm_tc05_swiglu": "gemm_tc05_swiglu",
+    "gemm_skinny_swiglu": "gemm_skinny_swiglu", "gemm_skinny_qkv_rope": "gemm_skinny_qkv_rope", "gemm_tc05": "gemm_tc05", "gemm_tc05_swiglu": "gemm_tc05_swiglu",
     "gemm_rows": "gemm_rows", "gemm_rows_swiglu": "gemm_rows_swiglu",
 }
 

@@ -43,7 +43,8 @@ class LLM:
     def __init__(self, model, dtype="bfloat16", max_batch: int = 32, max_seq_len: Optional[int] = None,
                  max_gen_len: int = 256, block_size: int = 16, num_blocks: Optional[int] = None,
                  max_num_batched_tokens: Union[int, str] = "adaptive", enable_prefix_cache: bool = True,
-                 use_cuda_graph: bool = True, async_decode: bool = True, device: str = "cuda:0"):
+                 use_cuda_graph: bool = True, async_decode: bool = True, device: str = "cuda:0",
+                 reserve: str = "prompt"):
         """``model``: a model folder or a built ``Model``. ``max_batch``: most requests running at
         once. ``max_seq_len``: most tokens (prompt + generated) of one request, by default the
         model's ``max_position``. ``num_blocks``: pages of the cache pool, by default
@@ -51,7 +52,9 @@ class LLM:
         (src/source/scheduler/kv_manager.cpp:23-25). ``max_num_batched_tokens``: prompt tokens per
         step, or "adaptive" for the reference's 512/1024/4096 rule. ``async_decode``: while a
         step runs, the next one is already decided and launched (the tokens it draws pass to the
-        next step on the device), so the host's work per step hides behind the GPU's."""
+        next step on the device), so the host's work per step hides behind the GPU's. ``reserve``: pages
+        a request must get to be admitted, its whole prompt's ("prompt", as the reference) or its first
+        portion's ("portion": more requests run than the pool holds prompts of, and later portions preempt)."""
         self.dtype = _dtype_of(dtype)
         self.model = load_model(model, self.dtype, device) if isinstance(model, (str, bytes)) else model
         spec = self.model.spec
@@ -67,7 +70,7 @@ class LLM:
                                   prefix_reuse=enable_prefix_cache, max_seq_len=self.max_seq_len)
         eos = self.model.config.eos_token_ids() if hasattr(self.model.config, "eos_token_ids") else []
         self.scheduler = Scheduler(self.runner.manager, self.max_batch, self.max_seq_len, max_gen_len,
-                                   token_budget=max_num_batched_tokens, eos_token_ids=eos)
+                                   token_budget=max_num_batched_tokens, eos_token_ids=eos, reserve=reserve)
         self.sampler = Sampler(self.model.device, self.max_batch)
         self.use_cuda_graph = bool(use_cuda_graph)
         self.async_decode = bool(async_decode)

@@ -21,7 +21,12 @@ Where this scheduler decides differently:
   ``max_batch`` caps both, so its budget never binds).
 
 When pages run out:
-* at admission the request waits; a running request is never preempted to admit another;
+* at admission the request waits; a running request is never preempted to admit another. What is
+  reserved at admission is the prompt's pages (``reserve="prompt"``, the default, as the reference
+  does) or, with ``reserve="portion"``, only those of its first portion: then more requests are
+  admitted than the pool can hold prompts of, the pages of later portions are taken when the portion
+  is scheduled, and a portion that finds none has newer requests preempted for it like a decode row
+  (if none can give, it waits for a later step);
 * when a running request needs one more page to decode, running requests newer than it give
   tail pages, newest first and just as many as needed, and are preempted (they return to the
   front of the queue and recompute what they gave; while they wait they may be asked for the
@@ -116,7 +121,7 @@ def default_seed(request_id: Hashable) -> int:
 class Scheduler:
     def __init__(self, cache: CacheManager, max_num_seqs: int, max_model_len: int, max_gen_len: int,
                  token_budget: Union[int, str] = "adaptive", eos_token_ids: Sequence[int] = (),
-                 clock=time.monotonic):
+                 clock=time.monotonic, reserve: str = "prompt"):
         self.cache = cache
         self.max_num_seqs = int(max_num_seqs)
         self.max_model_len = int(max_model_len)
@@ -125,6 +130,9 @@ class Scheduler:
         self.token_budget = 1024 if self.adaptive else int(token_budget)   # scheduler.h:105 starts at 1024
         if self.token_budget < 1:
             raise ValueError("the token budget must be at least 1")
+        if reserve not in ("prompt", "portion"):
+            raise ValueError(f"reserve must be 'prompt' or 'portion', got {reserve!r}")
+        self.reserve = reserve
         self.eos_token_ids = set(int(t) for t in eos_token_ids)
         self.clock = clock
         self.waiting: Deque[Sequence_] = deque()
@@ -186,8 +194,9 @@ class Scheduler:
         decoding = {id(it.seq) for it in items}
         pending = [s for s in self.running if s.state is SeqState.RUNNING and id(s) not in decoding
                    and not s.prefill_done]
-        self._portions(items, pending, {})
-        return items
+        self._portions(items, pending, {}, may_preempt=True)
+        # a portion may have had a newer request preempted whose decode row stood in this step already
+        return [it for it in items if it.seq.state is SeqState.RUNNING]
 
     def schedule_ahead(self, inflight: Sequence[ScheduledItem]) -> Optional[List[ScheduledItem]]:
         """The step that follows ``inflight`` (launched, its tokens not read yet), decided before those
@@ -227,9 +236,13 @@ class Scheduler:
         self.num_steps += 1
         return items
 
-    def _portions(self, items: List[ScheduledItem], pending: List[Sequence_], computed: Dict[int, int]) -> None:
+    def _portions(self, items: List[ScheduledItem], pending: List[Sequence_], computed: Dict[int, int],
+                  may_preempt: bool = False) -> None:
         """Prompt portions in admission order under the token budget, behind the decode rows in ``items``.
-        ``computed``: where a request's cache will stand when the step runs, if not at ``num_computed``."""
+        ``computed``: where a request's cache will stand when the step runs, if not at ``num_computed``.
+        With ``reserve="portion"`` a portion's pages are taken here; one that lacks pages has newer requests
+        preempted for it (``may_preempt``: not while a step is in flight, whose requests must keep their
+        pages), is cut down to the pages it has, or waits for a later step."""
         if not pending:
             return
         self._move_budget(len(items))
@@ -237,11 +250,44 @@ class Scheduler:
         for seq in pending:
             if taken >= self.token_budget:
                 break
+            if seq.state is not SeqState.RUNNING:      # preempted for an older request's portion a moment ago
+                continue
             start = computed.get(id(seq), seq.num_computed)
             remaining = seq.num_tokens - start
             take = min(remaining, self.token_budget - taken)
+            if self.reserve == "portion":
+                take = self._pages_for_portion(seq, start, take, may_preempt)
+                if take <= 0:
+                    continue
             items.append(ScheduledItem(seq, start, take, take == remaining))
             taken += take
+
+    def _pages_for_portion(self, seq: Sequence_, start: int, take: int, may_preempt: bool) -> int:
+        """Take the pages for tokens [start, start + take) of ``seq``; returns how many of the tokens have a
+        place (0: none, the portion waits)."""
+        if self.cache.can_grow(seq.id, start + take):
+            self.cache.grow(seq.id, start + take)
+            return take
+        if may_preempt:
+            ok = True
+            for g, m in enumerate(self.cache.pages_missing(seq.id, start + take)):
+                short = m - self.cache.free_pages(g)
+                if short > 0 and not self._preempt_for(g, short, seq):
+                    ok = False
+                    break
+            if ok and self.cache.can_grow(seq.id, start + take):
+                self.cache.grow(seq.id, start + take)
+                return take
+        # what the free pages and the pages it holds cover
+        ps = self.cache.page_size
+        held = min(len(self.cache.table(g, seq.id)) + self.cache.free_pages(g) for g in range(len(self.cache.groups)))
+        fit = min(take, held * ps - start)
+        if fit <= 0:
+            if may_preempt and not any(s is not seq and s.state is SeqState.RUNNING for s in self.running):
+                self._finish(seq, "aborted")             # alone, every other request's pages taken, and still no room
+            return 0
+        self.cache.grow(seq.id, start + fit)
+        return fit
 
     def _move_budget(self, decode_backlog: int) -> None:
         if not self.adaptive:
@@ -265,21 +311,27 @@ class Scheduler:
                 if seq.prefix_chain is None:               # a request that waits at the head is hashed once
                     seq.prefix_chain = self.cache.chain_hashes(seq.prompt)
                 pages = self.cache.match_prefix(seq.prompt, seq.prefix_chain)
-                need = self.cache.blocks_for(seq.num_tokens) - len(pages)
+                need = self.cache.blocks_for(self._reserved_length(seq, len(pages) * self.cache.page_size)) - len(pages)
                 if any(need > self.cache.free_pages(g) - self._parked_among(pages, g)
                        for g in range(len(self.cache.groups))):
                     break
                 seq.num_computed = self.cache.admit(seq.id, seq.prompt, seq.prefix_chain)
                 seq.prefix_hit_tokens = seq.num_computed
-            elif not self.cache.can_grow(seq.id, seq.num_tokens):
+            elif not self.cache.can_grow(seq.id, self._reserved_length(seq, seq.num_computed)):
                 break
-            self.cache.grow(seq.id, seq.num_tokens)
+            self.cache.grow(seq.id, self._reserved_length(seq, seq.num_computed))
             self.waiting.popleft()
             seq.state = SeqState.RUNNING
             if seq.admit_order < 0:
                 seq.admit_order = next(self._admissions)
             self.running.append(seq)
             self.running.sort(key=lambda s: s.admit_order)
+
+    def _reserved_length(self, seq: Sequence_, computed: int) -> int:
+        """Tokens whose pages a request must get to be admitted: all it has, or its first portion's."""
+        if self.reserve == "portion":
+            return min(seq.num_tokens, computed + self.token_budget)
+        return seq.num_tokens
 
     def _parked_among(self, pages: List[int], g: int) -> int:
         """Matched prefix pages that are counted as free (parked) but will be taken back."""

@@ -13,12 +13,14 @@ import torch
 
 from ..csrc import ops
 from .base import CacheNeed, Mixer, register_mixer
+from . import linear as linear_mod
 from .linear import linear
 
 
 USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
 USE_TMA = True               # decode tiles by TMA where the layout allows
 USE_TC05 = True              # prompt portions on tcgen05 where the layout allows
+FUSE_ROPE = True             # few rows (decode): rotation and cache store in the epilogue of the q/k/v product
 DECODE_BLOCKS_PER_SM = 2     # decode attention blocks that one multiprocessor holds at once
 MAX_SPLITS = 32
 MIN_TILES_PER_SPLIT = 2      # a split covers at least this many 64-key tiles
@@ -77,8 +79,19 @@ class Attention(Mixer):
         T = x.shape[0]
         H, KV, hs = self.H, self.KV, self.hs
         qkv = ctx.buf("attn_qkv", (T, (H + 2 * KV) * hs), self.dtype)
-        linear(x, self.qkv, qkv, ctx.status)
         rot = self.position.rotary() if self.position is not None else None
+        if (FUSE_ROPE and linear_mod.USE_SKINNY and rot is not None and rot[1] == hs and hs % 16 == 0
+                and self.dtype == torch.bfloat16 and ops.gemm_skinny_ok(x, self.qkv, qkv)):
+            # a decode step: one kernel for the projection, the rotation and the store into the pages
+            ops.gemm_skinny_qkv_rope(x, self.qkv, qkv, ctx.positions, ctx.row_seq, rot[0], cache.block_table,
+                                     cache.k if cache.writes else None, cache.v if cache.writes else None,
+                                     cache.page_size, ctx.seq_slots, H, KV, hs, status=ctx.status)
+            attn = ctx.buf("attn_out", (T, H * hs), self.dtype)
+            self.attend(qkv[:, :H * hs], cache, ctx, attn)
+            out = ctx.buf("delta", (T, self.hidden), self.dtype)
+            linear(attn, self.o, out, ctx.status)
+            return out
+        linear(x, self.qkv, qkv, ctx.status)
         if self.position is not None and rot is None:
             q3 = qkv[:, :H * hs].view(T, H, hs)
             k3 = qkv[:, H * hs:(H + KV) * hs].view(T, KV, hs)

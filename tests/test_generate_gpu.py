@@ -271,18 +271,20 @@ def test_shared_prefix_under_load_matches_plain(folders):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_prompt_workload_in_small_preempts_and_completes(folders, dtype):
-    """The long-context workload at a tiny size: prompts that fill whole pages, cut into portions under a token
-    budget beside the decode rows of the requests that are through theirs, in a pool that holds the prompts of
-    six of the eight requests and three pages more. At its first decoded token every request needs a page: the
-    newest ones are preempted, give their last page, wait, recompute it and finish. All eight complete; in
-    float32 with the tokens of the plain implementation, in bfloat16 with them up to the first near-tie."""
+    """The long-context workload at a tiny size: eight prompts that fill whole pages, cut into portions under a
+    token budget beside the decode rows of the requests that are through theirs, admitted on the pages of their
+    first portion into a pool that holds the prompts of five of them. The portions and decode rows of the older
+    requests have the newest ones preempted (three requests, four times or more in all); they wait, come back,
+    recompute what they gave and finish. All eight complete; in float32 with the tokens of the plain
+    implementation, in bfloat16 with them up to the first near-tie."""
     from llm_steadyinfer_b200 import LLM, SamplingParams
     prompts = prompts_of("B", [64] * 8)
     llm = LLM(folders["B"], dtype=dtype, max_batch=8, max_seq_len=96, max_gen_len=16, block_size=8,
-              num_blocks=6 * 8 + 3, max_num_batched_tokens=32, enable_prefix_cache=False)
+              num_blocks=44, max_num_batched_tokens=32, enable_prefix_cache=False, reserve="portion")
     got = llm.generate(prompts, SamplingParams(ignore_eos=True))
     assert all(g.finish_reason == "length" and len(g.token_ids) == 16 for g in got)
-    assert llm.scheduler.num_preemptions >= 3 and llm.scheduler.num_recomputed_tokens >= 3 * 8
+    assert llm.scheduler.num_preemptions >= 4 and llm.scheduler.num_recomputed_tokens >= 16
+    assert sum(1 for g in got if g.num_preemptions) >= 3
     assert sum(g.num_preemptions for g in got) == llm.scheduler.num_preemptions
     want = plain_generate(folders["B"], prompts, 16)
     if dtype == "float32":

@@ -684,6 +684,60 @@ def test_gemm_skinny(M, N, K, out_dtype):
     assert torch.equal(one[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M,H,KV,hs,K,page_size", [(1, 4, 2, 64, 256, 16), (8, 32, 8, 128, 4096, 16), (16, 3, 1, 32, 96, 8),
+                                                   (11, 6, 3, 16, 136, 4), (5, 2, 2, 96, 320, 32)])
+def test_gemm_skinny_qkv_rope(M, H, KV, hs, K, page_size):
+    """The q/k/v product with the rotation and the cache store in its epilogue against the three kernels it
+    stands for (product, then rotation and store): rotated q, and the pages of k and v, a padding row included."""
+    g = torch.Generator(device=DEV).manual_seed(31)
+    o = ops()
+    x = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn((H + 2 * KV) * hs, K, generator=g, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, hs, 2, dtype=torch.float64) / hs))).float().to(DEV)
+    num_seqs, width = M, 6
+    num_pages = num_seqs * width + 3
+    table = torch.randperm(num_pages, generator=g, device=DEV)[:num_seqs * width].to(torch.int32).view(num_seqs, width)
+    positions = torch.randint(0, width * page_size, (M,), generator=g, device=DEV).to(torch.int32)
+    row_seq = torch.arange(M, dtype=torch.int32, device=DEV)
+    if M > 2:
+        row_seq[M - 2] = -1                       # a padding row of a fixed-shape step: nothing stored for it
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    caches = []
+    outs = []
+    for fused in (False, True):
+        kc = torch.zeros(num_pages, KV, page_size, hs, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        qkv = torch.zeros(M, (H + 2 * KV) * hs, dtype=torch.bfloat16, device=DEV)
+        if fused:
+            o.gemm_skinny_qkv_rope(x, w, qkv, positions, row_seq, inv_freq, table, kc, vc, page_size, num_seqs, H, KV, hs, status)
+        else:
+            o.gemm_skinny(x, w, qkv)
+            o.rope_kv_write(qkv, positions, row_seq, inv_freq, hs, table, kc, vc, page_size, num_seqs, H, KV, hs, status)
+        assert status.item() == 0
+        outs.append(qkv[:, :H * hs].float())
+        caches.append((kc.float(), vc.float()))
+    # the same roundings in the same places; a product and a sum may be contracted differently: one bf16 step
+    step = 2 ** -7
+    assert (outs[0] - outs[1]).abs().max().item() <= step * max(1.0, outs[0].abs().max().item())
+    assert (caches[0][0] - caches[1][0]).abs().max().item() <= step * max(1.0, caches[0][0].abs().max().item())
+    assert torch.equal(caches[0][1], caches[1][1]), "v is stored as the product gave it"
+    assert caches[1][0].abs().sum().item() > 0 and caches[1][1].abs().sum().item() > 0
+    # against torch alone: one row's rotated first q head
+    m = 0
+    q0 = (x[m].double() @ w[:hs].double().T).to(torch.bfloat16).double()
+    ang = positions[m].item() * inv_freq.double().cpu()
+    c, sn = torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)
+    want = torch.cat([q0[:hs // 2] * c - q0[hs // 2:] * sn, q0[hs // 2:] * c + q0[:hs // 2] * sn])
+    assert (outs[1][m, :hs].double() - want).abs().max().item() <= 2 ** -7 * max(1.0, want.abs().max().item())
+    # a table entry outside the pool is reported, nothing is written for that row
+    bad = table.clone()
+    bad[0] = num_pages + 5
+    kc = torch.zeros(num_pages, KV, page_size, hs, dtype=torch.bfloat16, device=DEV)
+    o.gemm_skinny_qkv_rope(x[:1], w, torch.zeros(1, (H + 2 * KV) * hs, dtype=torch.bfloat16, device=DEV), positions[:1],
+                           row_seq[:1], inv_freq, bad, kc, torch.zeros_like(kc), page_size, num_seqs, H, KV, hs, status)
+    assert status.item() == 2 and kc.abs().sum().item() == 0
+
+
 def test_gemm_skinny_at_serving_size():
     """The four projections of the Llama-3.1-8B block at 8 rows: achieved weight bandwidth (printed)
     beside the library product."""

@@ -64,7 +64,9 @@ def test_norm_and_mlp_parts(folders, dtype):
     assert (x.double().cpu() - want).abs().max().item() <= tol
     assert (r.double().cpu() - h).abs().max().item() <= 1e-6
 
-    class Ctx:                                   # the feed-forward needs scratch only
+    class Ctx:                                   # the feed-forward needs scratch and the status word only
+        status = None
+
         def buf(self, key, shape, dt):
             return torch.empty(shape, dtype=dt, device=DEV)
     y = blk.feed_forward.forward(x, Ctx())

@@ -286,9 +286,10 @@ def test_step_ahead_counts_pages_row_by_row():
     cache.check_invariant()
 
 
+@pytest.mark.parametrize("reserve", ["prompt", "portion"])
 @pytest.mark.parametrize("windowed", [False, True], ids=["one_group", "window_and_state"])
 @pytest.mark.parametrize("seed", range(12))
-def test_random_serving_with_and_without_steps_ahead(seed, windowed):
+def test_random_serving_with_and_without_steps_ahead(seed, windowed, reserve):
     """A stand-in model (the token of request r at output index i is a fixed function of both) under random
     arrivals, small pools, stop tokens and shared prefixes: with steps decided ahead where the scheduler allows
     it and without, every request ends with the same tokens and reason, and the cache keeps its books."""
@@ -305,6 +306,7 @@ def test_random_serving_with_and_without_steps_ahead(seed, windowed):
                              [None, None, StateNeed((3,))]) if windowed else None
         s, cache = make(num_pages=rng.choice([12, 20, 40]), page_size=4, max_seqs=4, budget=rng.choice([8, 32]),
                         max_len=64, max_gen=12, prefix=True, eos=(5, 6, 7), layout=layout)
+        s.reserve = reserve
         shared = [11, 12, 13, 14, 15, 16, 17, 18]
         todo = []
         for i in range(16):
@@ -343,7 +345,7 @@ def test_random_serving_with_and_without_steps_ahead(seed, windowed):
     assert plain == piped
     assert aheads > 0
     for outs, reason in plain.values():
-        assert reason in ("eos", "length") and len(outs) >= 1
+        assert reason in ("eos", "length") and len(outs) >= 1, (outs, reason)
 
 
 def test_an_id_cannot_be_live_twice():
@@ -395,3 +397,37 @@ def test_a_waiting_prompt_is_hashed_once():
         n += 1
     assert n >= 3 and calls.count(12) == 1 and calls.count(20) == 1
     cache.check_invariant()
+
+
+def test_admission_on_the_first_portion_preempts_for_later_portions():
+    """``reserve="portion"``: requests are admitted when their first portion's pages are free, so more run than
+    the pool holds prompts of; an older request's later portion has the newest ones preempted, they wait, come
+    back and recompute, and every request finishes."""
+    s, cache = make(num_pages=14, page_size=4, max_seqs=4, budget=8, max_gen=3)
+    s.reserve = "portion"
+    ids = [s.add_request(list(range(100 * i, 100 * i + 24))) for i in range(4)]     # 6 pages each, 24 in all: 14 there
+    first = run_step(s, cache)
+    assert len(s.running) == 4, "all four were admitted on two pages each"
+    assert [(it.seq.id, it.start, it.count) for it in first] == [(ids[0], 0, 8)]
+    n = 0
+    while s.has_unfinished():
+        items = run_step(s, cache)
+        assert all(it.seq.state is SeqState.RUNNING or it.seq.state is SeqState.FINISHED for it in items)
+        n += 1
+        assert n < 400, "the schedule must end"
+    assert s.num_preemptions >= 1 and s.num_recomputed_tokens >= 0
+    assert sorted(q.id for q in s.finished) == sorted(ids)
+    assert all(q.finish_reason == "length" and len(q.outputs) == 3 for q in s.finished)
+    assert cache.free_pages(0) == 14
+    cache.check_invariant()
+
+
+def test_portion_admission_aborts_what_can_never_fit():
+    s, cache = make(num_pages=4, page_size=4, max_seqs=2, budget=8, max_gen=2)
+    s.reserve = "portion"
+    a = s.add_request(list(range(15)))            # 15 + 1 tokens fit 4 pages: accepted; its portions fill the pool
+    while s.has_unfinished():
+        run_step(s, cache)
+    assert s.finished[0].id == a and s.finished[0].finish_reason in ("length", "aborted")
+    cache.check_invariant()
+    assert cache.free_pages(0) == 4
