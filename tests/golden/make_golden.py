@@ -16,7 +16,8 @@ The reference fixes theta = 5e5 (src/source/model/model.cpp:368), eps = 1e-6
 to hidden/heads, so the two models use those values.
 
 Outputs: golden_g1.npz, golden_g2.npz (weights, prompt, logits of every prompt position, and
-greedy tokens of two requests), a few hundred KB together.
+greedy tokens of two requests), a few hundred KB together; golden_rope.npz (the reference's sine and
+cosine tables at three values of theta, from its table function, which takes theta as an argument).
 """
 import argparse
 import glob
@@ -123,6 +124,24 @@ def make_case(name: str, c: dict, exe: str, work: str) -> None:
     print(name, "logits", logits.shape, "greedy", gens)
 
 
+ROPE_CASES = [(16, 10000.0), (32, 500000.0), (64, 1000000.0)]      # (head size, theta); 96 positions each
+
+
+def make_rope_tables(exe: str, work: str) -> None:
+    """The reference's sine and cosine tables (src/source/op/kernels/cpu/rope_kernel.cpp:3-16) at three values of
+    theta: its table function takes theta as an argument, so values other than the 5e5 of its model code are
+    anchored on its code as well."""
+    out = {}
+    for hs, theta in ROPE_CASES:
+        path = os.path.join(work, f"rope_{hs}.bin")
+        subprocess.run([exe, "rope", str(hs), "96", repr(theta), path], check=True,
+                       env=dict(os.environ, LD_LIBRARY_PATH="/usr/local/cuda/lib64"))
+        t = np.fromfile(path, np.float32).reshape(2, 96, hs)
+        out[f"sin_{hs}"], out[f"cos_{hs}"], out[f"theta_{hs}"] = t[0], t[1], np.float64(theta)
+    np.savez_compressed(os.path.join(HERE, "golden_rope.npz"), **out)
+    print("rope tables", sorted(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
@@ -131,6 +150,7 @@ def main():
         exe = build(args.reference, work)
         for name, c in CASES.items():
             make_case(name, c, exe, work)
+        make_rope_tables(exe, work)
 
 
 if __name__ == "__main__":

@@ -2,7 +2,14 @@
 #include "model/llama3.h"
 #include "scheduler/scheduler.h"
 #include <cstdio>
+#include "cpu/rope_kernel.h"
+// "rope <head_size> <positions> <theta> <out>": the reference's sine/cosine tables for a theta of the caller's choice
+// (its table function takes theta as an argument; only its model code fixes the value)
+static int rope_tables(char**argv){ int hs=atoi(argv[2]), n=atoi(argv[3]); float theta=atof(argv[4]);
+  std::vector<float> sn((size_t)hs*n), cs((size_t)hs*n); kernel::sin_cos_cache_calc_cpu(hs,n,sn.data(),cs.data(),theta);
+  FILE* o=fopen(argv[5],"wb"); fwrite(sn.data(),4,sn.size(),o); fwrite(cs.data(),4,cs.size(),o); fclose(o); return 0; }
 int main(int argc,char**argv){
+  if(argc>5 && std::string(argv[1])=="rope") return rope_tables(argv);
   const char* bin=argv[1]; int max_seq=atoi(argv[2]);
   auto m=std::make_shared<model::LLamaModel>(base::TokenizerType::kEncodeSpe,"tok",bin,false);
   auto st=m->init(base::DeviceType::kDeviceCPU); if(!st){printf("init failed %d %s\n",int(st),st.get_err_msg().c_str());return 1;}

@@ -3,9 +3,11 @@ arithmetic by default. It shares no code with the package; every function is wri
 formulas of the reference (paths are relative to the reference project's root).
 
 It was compared once with the reference's own CPU model code on a tiny random model; the
-script and its small outputs are under tests/golden/ (see tests/golden/README.md). Options the
-reference's code fixes (theta 5e5, eps 1e-6, no frequency scaling, head size = hidden/heads,
-greedy only) are covered there at those values only; the other values rest on the formulas.
+script and its small outputs are under tests/golden/ (see tests/golden/README.md). Of the options that
+the reference's model code fixes, theta is covered at three values through its table function, which
+takes theta as an argument; eps (1e-6), frequency scaling (none), head size (hidden/heads) and sampling
+(greedy) are covered at the reference's values only, and their other values rest on the formulas cited
+at each function.
 """
 from __future__ import annotations
 

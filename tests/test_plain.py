@@ -31,6 +31,29 @@ def test_plain_equals_reference_cpu_code(name):
     assert pl.generate(cfg, w, prompt[:3], 8) == z["gen_short"].tolist()
 
 
+@pytest.mark.parametrize("hs", [16, 32, 64])
+def test_rope_angles_equal_the_reference_tables_at_other_thetas(hs):
+    """The reference's own sine / cosine table function takes theta as an argument
+    (src/source/op/kernels/cpu/rope_kernel.cpp:3-16; entry 2i of a row is the pair's angle, :76-77): its tables
+    at theta 1e4, 5e5 and 1e6 against the frequencies and the rotation of the plain implementation."""
+    z = np.load(os.path.join(GOLDEN, "golden_rope.npz"))
+    theta = float(z[f"theta_{hs}"])
+    sin_t, cos_t = torch.from_numpy(z[f"sin_{hs}"]), torch.from_numpy(z[f"cos_{hs}"])        # [positions, hs]
+    n = sin_t.shape[0]
+    freqs = pl.rope_frequencies(hs, theta, None)
+    ang = torch.arange(n, dtype=torch.float32)[:, None] * freqs[None, :]
+    # the reference forms theta^(-j/hs) with a float pow: a frequency may differ by an ulp, an angle by 95 ulps of it
+    assert (torch.sin(ang) - sin_t[:, 0::2]).abs().max().item() < 2e-5
+    assert (torch.cos(ang) - cos_t[:, 0::2]).abs().max().item() < 2e-5
+    g = torch.Generator().manual_seed(hs)
+    x = torch.randn(n, 3, hs, generator=g, dtype=pl.DT)
+    got = pl.rope(x, torch.arange(n), freqs)
+    c, s = cos_t[:, 0::2].double()[:, None, :], sin_t[:, 0::2].double()[:, None, :]
+    x0, x1 = x[..., :hs // 2], x[..., hs // 2:]
+    want = torch.cat([c * x0 - s * x1, c * x1 + s * x0], dim=-1)      # the reference's rotation with its own tables
+    assert (got - want).abs().max().item() < 1e-4
+
+
 def test_rmsnorm_definition():
     x = torch.tensor([[3.0, 4.0]], dtype=pl.DT)
     y = pl.rmsnorm(x, torch.tensor([2.0, 0.5], dtype=pl.DT), 0.0)
