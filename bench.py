@@ -333,13 +333,13 @@ def main() -> int:
             runner.finish(r)
         return out
 
+    pre_clocks = ClockSampler()
     if args.section == "decode":
         pre_ms = own_ms = float("nan")
     else:
         for i in range(3):
             prefill_once(i)
         runner.check_status()
-        pre_clocks = ClockSampler()
         pre_clocks.start()
         pre_ms = statistics.median(timed(prefill_once, 1) for _ in range(5))
         # for comparison: the same step with the library product (cuBLAS) in place of this package's tcgen05 kernel

@@ -225,6 +225,30 @@ gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __rest
   }
 }
 
+// Eight warps a block (two blocks an SM) unless the blocks would then make more than one round but no more than
+// two: with four warps a block, four blocks fit an SM and all of them run at once, sharing the memory bandwidth,
+// instead of a full round followed by a part of one.
+static inline bool skinny_four_warps(unsigned blocks) {
+  const unsigned sms = (unsigned)si_sm_count();
+  return blocks > 2 * sms && blocks <= 4 * sms;
+}
+
+template <int WARPS, typename TO, bool SWIGLU, bool ROPE>
+static void skinny_launch(unsigned blocks, cudaStream_t stream, const bf16* xp, long long ldx, const bf16* wp, long long ldw,
+                          TO* out, long long ldo, int M, int N, int K, const SkinnyRope& r) {
+  constexpr int UNROLL = 8;
+  const int trig = si_pdl_trigger_mode(blocks, (512 / (WARPS * 32)) * si_sm_count());
+  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, TO, SWIGLU, ROPE>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, trig, r);
+  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, TO, SWIGLU, ROPE>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, trig, r);
+}
+
+template <typename TO, bool SWIGLU, bool ROPE>
+static void skinny_dispatch(unsigned blocks, cudaStream_t stream, const bf16* xp, long long ldx, const bf16* wp, long long ldw,
+                            TO* out, long long ldo, int M, int N, int K, const SkinnyRope& r) {
+  if (skinny_four_warps(blocks)) skinny_launch<4, TO, SWIGLU, ROPE>(blocks, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, r);
+  else skinny_launch<8, TO, SWIGLU, ROPE>(blocks, stream, xp, ldx, wp, ldw, out, ldo, M, N, K, r);
+}
+
 // Largest M this kernel takes.
 SI_EXPORT int si_gemm_skinny_max_rows() { return 16; }
 
@@ -234,17 +258,11 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -2;
   if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
-  constexpr int WARPS = 8, UNROLL = 8;
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-  if (out_dtype == SI_BF16) {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
-  } else {
-    if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
-    else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, float>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
-  }
+  if (out_dtype == SI_BF16) skinny_dispatch<bf16, false, false>(blocks, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, SkinnyRope());
+  else skinny_dispatch<float, false, false>(blocks, stream, xp, ldx, wp, ldw, (float*)out, ldo, M, N, K, SkinnyRope());
   return si_last_error();
 }
 
@@ -255,12 +273,8 @@ SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W,
   if (M <= 0 || F <= 0) return 0;
   if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (F % 8)) return -2;
   if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
-  constexpr int WARPS = 8, UNROLL = 8;
   const unsigned blocks = (unsigned)(F / 8);
-  const bf16* xp = (const bf16*)x;
-  const bf16* wp = (const bf16*)W;
-  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
-  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, 2 * F, K, si_pdl_trigger_mode(blocks, 2 * si_sm_count()), SkinnyRope());
+  skinny_dispatch<bf16, true, false>(blocks, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, 2 * F, K, SkinnyRope());
   return si_last_error();
 }
 
@@ -277,7 +291,6 @@ SI_EXPORT int si_gemm_skinny_qkv_rope(const void* x, long long ldx, const void* 
   if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || H <= 0 || KV <= 0 || hs <= 0 || (hs % 16)) return -2;
   if (((uintptr_t)x % 16) || ((uintptr_t)W % 16) || !positions || !row_seq || !inv_freq || page_size <= 0) return -2;
   if (k_cache && (!v_cache || !block_table)) return -2;
-  constexpr int WARPS = 8, UNROLL = 8;
   const int N = (H + 2 * KV) * hs;
   const unsigned blocks = (unsigned)((H + 2 * KV) * (hs / 16));
   SkinnyRope r;
@@ -285,10 +298,6 @@ SI_EXPORT int si_gemm_skinny_qkv_rope(const void* x, long long ldx, const void* 
   r.k_cache = (bf16*)k_cache; r.v_cache = (bf16*)v_cache;
   r.table_width = table_width; r.num_pages = num_pages; r.page_size = page_size; r.num_seqs = num_seqs;
   r.H = H; r.KV = KV; r.hs = hs; r.status = status;
-  const bf16* xp = (const bf16*)x;
-  const bf16* wp = (const bf16*)W;
-  const int trig = si_pdl_trigger_mode(blocks, 2 * si_sm_count());
-  if (M <= 8) si_launch(gemm_skinny_kernel<1, WARPS, UNROLL, bf16, false, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, trig, r);
-  else si_launch(gemm_skinny_kernel<2, WARPS, UNROLL, bf16, false, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, xp, ldx, wp, ldw, (bf16*)out, ldo, M, N, K, trig, r);
+  skinny_dispatch<bf16, false, true>(blocks, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K, r);
   return si_last_error();
 }
