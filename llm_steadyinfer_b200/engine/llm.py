@@ -17,6 +17,7 @@ import torch
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_model
 from .scheduler import ScheduledItem, Scheduler, Sequence_
+from . import tracing
 from .step import ModelRunner, StepEntry
 
 
@@ -107,10 +108,12 @@ class LLM:
             pending = self._inflight
             self._inflight = None
             if pending is None:
-                items = self.scheduler.schedule()
+                with tracing.span("schedule"):
+                    items = self.scheduler.schedule()
                 if not items:
                     return []
-                pending = self._launch(items)
+                with tracing.span("launch"):
+                    pending = self._launch(items)
             items, wanted, handle = pending
             if self._run_ahead:
                 ahead = self.scheduler.schedule_ahead(items)
@@ -118,7 +121,8 @@ class LLM:
                     rows = {id(it.seq): r for r, it in enumerate(wanted)}
                     self._inflight = self._launch(ahead, src_rows=rows)
                     self.stats["ahead_steps"] += 1
-            sampled = self._resolve(wanted, handle)
+            with tracing.span("resolve"):
+                sampled = self._resolve(wanted, handle)
         except Exception:
             self._inflight = None
             self.scheduler.abort_all()

@@ -27,6 +27,7 @@ import torch
 from ..cache import CacheLayout, CacheManager, CacheStorage, OutOfPages
 from ..csrc import build, ops
 from ..csrc.ops import KernelError
+from . import tracing
 
 STATUS_TEXT = {
     1: "a token id is outside the vocabulary",
@@ -209,14 +210,16 @@ class ModelRunner:
         next step overwrites) or None when nothing is wanted. ``feed = (ids, dst, src)``: token row
         ``dst[i]`` of the batch is not known on the host yet (its entry holds a placeholder) and is
         taken on the device from ``ids[src[i]]`` (int32 tensor, lists)."""
-        ctx = self._prepare(entries)
-        if feed is not None:
-            self._feed_tokens(ctx, feed)
-        self.storage.zero_new_slots()
-        caches = self.storage.layer_views(self._tables)
-        before = ops.launch_count()
-        self.model.prepare(ctx, caches)
-        logits = self.model.forward(ctx, caches)
+        with tracing.span("prepare"):
+            ctx = self._prepare(entries)
+            if feed is not None:
+                self._feed_tokens(ctx, feed)
+            self.storage.zero_new_slots()
+            caches = self.storage.layer_views(self._tables)
+            before = ops.launch_count()
+            self.model.prepare(ctx, caches)
+        with tracing.span("forward"):
+            logits = self.model.forward(ctx, caches)
         self.launches_last_step = ops.launch_count() - before
         self._commit(entries)
         return logits
@@ -268,7 +271,8 @@ class ModelRunner:
             launches = ops.launch_count() - before
             self.launches_last_step = launches
             if key not in self.capture_failed:
-                self._record(key, ctx, caches, launches)
+                with tracing.span("record"):
+                    self._record(key, ctx, caches, launches)
         else:
             g["graph"].replay()
             ops.add_launches(g["launches"])

@@ -16,6 +16,7 @@ from ..config.base import ModelConfig, ModelSpec
 from ..csrc import ops
 from ..parts import Block, feed_forward_class, mixer_class, norm_class, position_class
 from ..parts.linear import configure_library_gemm, linear
+from ..engine import tracing
 
 
 class Model:
@@ -109,7 +110,11 @@ class Model:
         ops.embedding_gather(ctx.tokens, self.embed, resid, status=ctx.status)
         delta = None
         for o, i in enumerate(self.spec.order):
-            delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
+            if tracing.ENABLED:
+                with tracing.span(f"layer {i}"):
+                    delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
+            else:
+                delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
         R = ctx.num_logit_rows
         if R == 0:
             return None
