@@ -45,6 +45,30 @@ template <> __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const f
   }
 }
 
+// The residual stream's add in the epilogue: dst (fp32) += the 32 sums, each rounded to bf16 first, as when the
+// product is stored in bf16 and the norm kernel after it adds it into the stream.
+__device__ __forceinline__ void add_row32(float* dst, const float (&v)[32], int valid, bool vec) {
+  if (vec && valid == 32) {
+    float4 r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = reinterpret_cast<const float4*>(dst)[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      r[i].x += __bfloat162float(__float2bfloat16_rn(v[4 * i]));
+      r[i].y += __bfloat162float(__float2bfloat16_rn(v[4 * i + 1]));
+      r[i].z += __bfloat162float(__float2bfloat16_rn(v[4 * i + 2]));
+      r[i].w += __bfloat162float(__float2bfloat16_rn(v[4 * i + 3]));
+      reinterpret_cast<float4*>(dst)[i] = r[i];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < valid) dst[i] += __bfloat162float(__float2bfloat16_rn(v[i]));
+  }
+}
+
+// What the epilogue does with a tile: store it, store silu(gate) * up of it, or add it into an fp32 tensor.
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2 };
+
 // 16 outputs of the gated activation from 32 accumulator columns (two groups of 8 gates + 8 ups); gate and
 // up are rounded to bf16 first, as when the projection is stored and a second kernel applies the activation.
 __device__ __forceinline__ void store_swiglu16(bf16* dst, const float (&v)[32], int valid, bool vec) {
@@ -69,7 +93,7 @@ __device__ __forceinline__ void store_swiglu16(bf16* dst, const float (&v)[32], 
   }
 }
 
-template <int STAGES, typename TO, bool SWIGLU>
+template <int STAGES, typename TO, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
                  TO* __restrict__ out, long long ldo, int M, int N, int K, int* status) {
@@ -153,6 +177,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   } else {
     const int q = warp & 3;                   // the 32 tensor-memory lanes this warp may read
     const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
+    const bool vec4 = (ldo % 4 == 0) && ((uintptr_t)out % 16 == 0);          // rows of fp32 in 16-byte pieces
     int local = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
@@ -179,7 +204,8 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
         for (int c = 0; c < 4; ++c) {
           const int n = n0 + h * 128 + c * 32;
           if (row < M && n < N) {
-            if (SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            if (EPI == EPI_SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            else if (EPI == EPI_ADD) add_row32((float*)out + (size_t)row * ldo + n, v[c], min(32, N - n), vec4);
             else store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
           }
         }
@@ -202,7 +228,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
 // Barriers: full[s] (leader: one arrival with the bytes of all four boxes), empty[s] (each CTA: the commit
 // after the stage's instructions), acc_full[b] (each CTA: the commit after a tile's last instruction),
 // acc_empty[b] (leader: the eight epilogue warps of both CTAs).
-template <int STAGES, typename TO, bool SWIGLU>
+template <int STAGES, typename TO, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192)
 gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
                       TO* __restrict__ out, long long ldo, int M, int N, int K, int* status) {
@@ -290,6 +316,7 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
   } else {
     const int q = warp & 3;
     const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
+    const bool vec4 = (ldo % 4 == 0) && ((uintptr_t)out % 16 == 0);          // rows of fp32 in 16-byte pieces
     int local = 0;
     for (int tile = pair; tile < tiles; tile += pairs, ++local) {
       const int buf = local & 1;
@@ -316,7 +343,8 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
         for (int c = 0; c < 4; ++c) {
           const int n = n0 + h * 128 + c * 32;
           if (row < M && n < N) {
-            if (SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            if (EPI == EPI_SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            else if (EPI == EPI_ADD) add_row32((float*)out + (size_t)row * ldo + n, v[c], min(32, N - n), vec4);
             else store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
           }
         }
@@ -338,12 +366,12 @@ static bool pair_enabled() {
   return on == 1;
 }
 
-template <typename TO, bool SWIGLU>
+template <typename TO, int EPI>
 static int launch_pair(const CUtensorMap& am, const CUtensorMap& bm_half, void* out, long long ldo, int M, int N, int K,
                        int* status, cudaStream_t stream) {
   constexpr int STAGES = 6;
   const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 128 * 64 * 2) + 1024;
-  auto k = gemm_tc05_pair_kernel<STAGES, TO, SWIGLU>;
+  auto k = gemm_tc05_pair_kernel<STAGES, TO, EPI>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
@@ -353,11 +381,11 @@ static int launch_pair(const CUtensorMap& am, const CUtensorMap& bm_half, void* 
   return si_last_error();
 }
 
-template <int STAGES, typename TO, bool SWIGLU>
+template <int STAGES, typename TO, int EPI>
 static int launch(const CUtensorMap& am, const CUtensorMap& bm, void* out, long long ldo, int M, int N, int K,
                   int* status, cudaStream_t stream) {
   const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 256 * 64 * 2) + 1024;
-  auto k = gemm_tc05_kernel<STAGES, TO, SWIGLU>;
+  auto k = gemm_tc05_kernel<STAGES, TO, EPI>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + 127) / 128) * ((N + 255) / 256);
@@ -395,12 +423,12 @@ SI_EXPORT int si_gemm_tc05(const void* x, long long ldx, const void* wmap, const
   if (rc) return rc;
   if (use_pair(M, wmap_half)) {
     const CUtensorMap& bh = *(const CUtensorMap*)wmap_half;
-    if (out_dtype == SI_BF16) return launch_pair<bf16, false>(am, bh, out, ldo, M, N, K, status, stream);
-    return launch_pair<float, false>(am, bh, out, ldo, M, N, K, status, stream);
+    if (out_dtype == SI_BF16) return launch_pair<bf16, EPI_STORE>(am, bh, out, ldo, M, N, K, status, stream);
+    return launch_pair<float, EPI_STORE>(am, bh, out, ldo, M, N, K, status, stream);
   }
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
-  if (out_dtype == SI_BF16) return launch<4, bf16, false>(am, bm, out, ldo, M, N, K, status, stream);
-  return launch<4, float, false>(am, bm, out, ldo, M, N, K, status, stream);
+  if (out_dtype == SI_BF16) return launch<4, bf16, EPI_STORE>(am, bm, out, ldo, M, N, K, status, stream);
+  return launch<4, float, EPI_STORE>(am, bm, out, ldo, M, N, K, status, stream);
 }
 
 // out[M, F] = silu(gate) * up (bf16) of the stacked projection x[M, K] W[2F, K]^T whose rows are interleaved in
@@ -412,7 +440,19 @@ SI_EXPORT int si_gemm_tc05_swiglu(const void* x, long long ldx, const void* wmap
   CUtensorMap am;
   const int rc = gemm_tc05_common(x, ldx, wmap, &am, M, K);
   if (rc) return rc;
-  if (use_pair(M, wmap_half)) return launch_pair<bf16, true>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, 2 * F, K, status, stream);
+  if (use_pair(M, wmap_half)) return launch_pair<bf16, EPI_SWIGLU>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, 2 * F, K, status, stream);
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
-  return launch<4, bf16, true>(am, bm, out, ldo, M, 2 * F, K, status, stream);
+  return launch<4, bf16, EPI_SWIGLU>(am, bm, out, ldo, M, 2 * F, K, status, stream);
+}
+
+// resid[M, N] (fp32, rows `ldr` apart) += x[M, K] W[N, K]^T, each sum rounded to bf16 before it is added: the
+// output projection of a mixer or a feed-forward added into the residual stream by the product itself.
+SI_EXPORT int si_gemm_tc05_add(const void* x, long long ldx, const void* wmap, const void* wmap_half, float* resid,
+                               long long ldr, int M, int N, int K, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  CUtensorMap am;
+  const int rc = gemm_tc05_common(x, ldx, wmap, &am, M, K);
+  if (rc) return rc;
+  if (use_pair(M, wmap_half)) return launch_pair<float, EPI_ADD>(am, *(const CUtensorMap*)wmap_half, resid, ldr, M, N, K, status, stream);
+  return launch<4, float, EPI_ADD>(am, *(const CUtensorMap*)wmap, resid, ldr, M, N, K, status, stream);
 }

@@ -679,6 +679,21 @@ def gemm_tc05(a, w, out, status=None) -> None:
              _stream()), f"gemm_tc05(M={M}, N={N}, K={K})")
 
 
+def gemm_tc05_add(a, w, resid, status=None) -> None:
+    """resid[M,N] (fp32) += a[M,K] @ w[N,K]^T on the tcgen05 tensor cores, each sum rounded to bf16 before the add
+    (what storing the product in bf16 and adding it in the norm kernel gives)."""
+    _cuda(a, w, resid, status)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and resid.shape == (M, N) and resid.dtype == torch.float32 and resid.stride(1) == 1,
+          "gemm_tc05_add: resid must be fp32 [M, N] rows")
+    _need(gemm_tc05_ok(a, w, resid), "gemm_tc05_add: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_tc05", "si_gemm_tc05_add", [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p])
+    half = _weight_map(w, 128) if M > 128 else None
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(resid), resid.stride(0), M, N, K, _ptr(status), _stream()),
+           f"gemm_tc05_add(M={M}, N={N}, K={K})")
+
+
 def gemm_tc05_swiglu(a, w, out, status=None) -> None:
     """out[M,F] = silu(gate) * up of a[M,K] @ w[2F,K]^T on the tcgen05 tensor cores, the rows of w interleaved
     in groups of 8 (8 gates, their 8 ups, ...): the activation runs in the product's epilogue."""

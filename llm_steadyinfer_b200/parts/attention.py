@@ -27,6 +27,8 @@ MIN_TILES_PER_SPLIT = 2      # a split covers at least this many 64-key tiles
 
 
 class Attention(Mixer):
+    adds_into_residual = True
+
     def __init__(self, params, dtype, device, position=None):
         super().__init__(params, dtype, device, position)
         self.hidden = int(params["hidden_size"])
@@ -75,7 +77,7 @@ class Attention(Mixer):
             names += ["attention_tma"] * bool(USE_TMA) + ["attention_tc05"] * bool(USE_TC05)
         return tuple(names)
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, resid=None):
         T = x.shape[0]
         H, KV, hs = self.H, self.KV, self.hs
         qkv = ctx.buf("attn_qkv", (T, (H + 2 * KV) * hs), self.dtype)
@@ -102,6 +104,8 @@ class Attention(Mixer):
                           cache.page_size, ctx.seq_slots, H, KV, hs, status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * hs), self.dtype)
         self.attend(qkv[:, :H * hs], cache, ctx, attn)
+        if resid is not None and linear_mod.linear_into_residual(attn, self.o, resid, ctx.status):
+            return None                                   # the output projection added itself into the stream
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(attn, self.o, out, ctx.status)
         return out

@@ -8,7 +8,10 @@ know which model or layer it sits in. Four kinds exist:
 ``PositionEncoding``  gives a mixer what it needs to encode positions: ``rotary()`` returns
                       ``(inv_freq, rot_dim)`` for mixers that fuse the rotation, or None, in
                       which case the mixer calls ``apply(q, k, ctx)`` on unfused views.
-``Mixer``             ``forward(x, ctx, cache) -> delta`` mixes token rows of a sequence
+``Mixer``             ``forward(x, ctx, cache) -> delta`` mixes token rows of a sequence. A mixer or
+                      feed-forward that says ``adds_into_residual = True`` is also given ``resid=`` (the fp32
+                      stream) and may add its result there itself and return None (its last product then does
+                      the add in its epilogue). It
                       (``prepare(ctx, cache)`` may plan the step on the host first); it
                       declares the cache it needs (``cache_need()``: paged keys/values, with or
                       without a window) and per-request state of fixed size (``state_need()``).
@@ -58,6 +61,9 @@ class Part:
     # the device. Only then may a decode step be captured into a CUDA graph and replayed; a model with a
     # part that says False (the default, which is always right) runs every step directly.
     capturable = False
+    # True if ``forward`` takes ``resid=`` (the fp32 residual stream) and may add its result into it itself,
+    # returning None instead of the delta (mixers and feed-forwards; the default keeps the plain contract)
+    adds_into_residual = False
 
     def __init__(self, params: Dict[str, Any], dtype: torch.dtype, device: torch.device):
         self.params = dict(params)

@@ -66,8 +66,14 @@ def pre_norm(block: Block, resid, delta, ctx, cache):
     T, d = resid.shape
     x = ctx.buf("block_x", (T, d), block.mixer.dtype)
     block.norm(block.mixer_norm, resid, delta, x, block.mixer.streams_first(T))
-    a = block.mixer.forward(x, ctx, cache)
+    # a part that can add its result into the stream itself is given the stream and returns None
+    if block.mixer.adds_into_residual:
+        a = block.mixer.forward(x, ctx, cache, resid=resid)
+    else:
+        a = block.mixer.forward(x, ctx, cache)
     block.norm(block.feed_forward_norm, resid, a, x, block.feed_forward.streams_first(T))
+    if block.feed_forward.adds_into_residual:
+        return block.feed_forward.forward(x, ctx, resid=resid)
     return block.feed_forward.forward(x, ctx)
 
 

@@ -60,3 +60,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status=None) -> 
     else:
         raise ops.KernelError(f"linear: unsupported dtypes x={x.dtype} w={w.dtype} out={out.dtype}")
     return out
+
+
+# Many-row products that end a mixer or a feed-forward can add into the residual stream themselves
+# (gemm_tc05_add). Off: measured on the 8B shape the prompt step is 4 to 7 % slower with it, because the epilogue's
+# strided fp32 read-modify-write no longer hides under the next tile's instructions.
+FUSE_RESIDUAL = os.environ.get("SI_FUSE_RESIDUAL", "0") == "1"
+
+
+def linear_into_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, status=None) -> bool:
+    """``resid += x @ w^T`` by the product's own epilogue, where a kernel of the package does that (bf16, at least
+    ``OWN_GEMM_MIN_ROWS`` rows); False, and nothing done, where none does. The sums are rounded to bf16 before the
+    add, as when ``linear`` stores them and the norm after it adds them."""
+    if (FUSE_RESIDUAL and USE_OWN_GEMM and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and resid.dtype == torch.float32 and x.shape[0] >= OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available()
+            and ops.gemm_tc05_ok(x, w, resid)):
+        ops.gemm_tc05_add(x, w, resid, status)
+        return True
+    return False

@@ -23,6 +23,7 @@ USE_TC05_GEMM = True   # gate/up product of more than 16 rows through this packa
 
 class GatedMLP(FeedForward):
     capturable = True
+    adds_into_residual = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -55,7 +56,7 @@ class GatedMLP(FeedForward):
             return ("gemm_f32", "swiglu")
         return ("gemm_skinny", "swiglu", "gemm_tc05", "gemm_rows")
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, resid=None):
         T = x.shape[0]
         act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
         if (self.group == INTERLEAVE and linear_mod.USE_SKINNY and act.dtype == torch.bfloat16
@@ -72,6 +73,8 @@ class GatedMLP(FeedForward):
             gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
             linear(x, self.gate_up, gu, ctx.status)
             ops.swiglu(gu, act, self.group)
+        if resid is not None and linear_mod.linear_into_residual(act, self.down, resid, ctx.status):
+            return None                                   # the down projection added itself into the stream
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(act, self.down, out, ctx.status)
         return out

@@ -893,6 +893,26 @@ def test_gemm_rows_at_serving_size():
             print(f"{M:4d} rows {name:8s}: " + ", ".join(f"{k} {v:.1f} us ({gb / v:.0f} GB/s)" for k, v in res.items()))
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 1000, 320), (300, 4096, 512), (129, 96, 1336), (2048, 520, 256)])
+def test_gemm_tc05_add_into_the_residual_stream(M, N, K):
+    """The product that adds itself into an fp32 tensor: equal, bit for bit, to storing the product in bf16 and
+    adding that (what the norm kernel after it would do), with one CTA a tile and with pairs."""
+    g = torch.Generator(device=DEV).manual_seed(41)
+    a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    resid0 = torch.randn(M, N, generator=g, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stored = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_tc05(a, w, stored, status)
+    want = resid0 + stored.float()
+    got = resid0.clone()
+    ops().gemm_tc05_add(a, w, got, status)
+    assert status.item() == 0
+    assert torch.equal(got, want)
+    ref = resid0.double() + (a.double() @ w.double().T)
+    assert (got.double() - ref).abs().max().item() <= 2 ** -8 * max(1.0, (a.double() @ w.double().T).abs().max().item())
+
+
 def test_gemm_tc05_at_prefill_size():
     """The projections of the Llama-3.1-8B block at 2,048 rows: achieved TFLOP/s (printed) beside the library."""
     g = torch.Generator(device=DEV).manual_seed(15)
