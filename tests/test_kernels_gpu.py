@@ -17,6 +17,29 @@ def ops():
     return o
 
 
+def graph_time_us(fn, n=20):
+    """Device time of one call of ``fn(i)`` in microseconds: calls i = 0 .. n-1 recorded into a CUDA graph and
+    replayed, so that the host's part of a call (tens of microseconds from Python) is not in the figure."""
+    fn(0)
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fn(0)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(n):
+                fn(i)
+    for _ in range(2):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000 / n
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("V,d,T", [(1000, 96, 7), (4099, 1336, 33)])
 def test_embedding(dtype, V, d, T):
@@ -858,31 +881,25 @@ def test_gemm_rows_swiglu(M, F, K):
 
 
 def test_gemm_rows_at_serving_size():
-    """The projections of the Llama-3.1-8B block and the output head at 8 to 128 rows: achieved bandwidth of the
-    weight stream (printed) beside the few-row kernel (up to 16 rows) and the library."""
+    """The projections of the Llama-3.1-8B block and the output head at 8 to 128 rows: time from a CUDA graph and
+    bandwidth of the weight stream (printed) beside the few-row kernel (up to 16 rows) and the library; the calls
+    of a graph go round several copies of the weight, so that none finds its weight in L2."""
     g = torch.Generator(device=DEV).manual_seed(23)
     shapes = (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336), ("head", 128256, 4096))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     for M in (8, 16, 32, 64, 128):
         for name, N, K in shapes:
             a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
-            w = (0.02 * torch.randn(N, K, generator=g, device=DEV)).to(torch.bfloat16)
+            # copies of the weight, 300 MB of them: a call does not find its weight in L2 (126 MB) from the call before
+            ws = [(0.02 * torch.randn(N, K, generator=g, device=DEV)).to(torch.bfloat16)
+                  for _ in range(max(1, -(-300_000_000 // (N * K * 2))))]
+            w = ws[-1]
             out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-            runs = {"rows": lambda: ops().gemm_rows(a, w, out, status), "library": lambda: torch.mm(a, w.t(), out=out)}
+            runs = {"rows": lambda i: ops().gemm_rows(a, ws[i % len(ws)], out, status),
+                    "library": lambda i: torch.mm(a, ws[i % len(ws)].t(), out=out)}
             if M <= 16:
-                runs["few-row"] = lambda: ops().gemm_skinny(a, w, out)
-            res = {}
-            for label, fn in runs.items():
-                for _ in range(3):
-                    fn()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                e0.record()
-                for _ in range(10):
-                    fn()
-                e1.record()
-                torch.cuda.synchronize()
-                res[label] = e0.elapsed_time(e1) * 100
+                runs["few-row"] = lambda i: ops().gemm_skinny(a, ws[i % len(ws)], out)
+            res = {label: graph_time_us(fn) for label, fn in runs.items()}
             assert status.item() == 0
             out.fill_(float("nan"))
             ops().gemm_rows(a, w, out, status)
