@@ -30,6 +30,34 @@
 #include "tma_common.cuh"
 #include <limits.h>
 
+// Packed fp32 arithmetic of sm_100 in the softmax (two scores an instruction) and three-input maxima.
+#ifndef SI_ATTN_PACKED
+#define SI_ATTN_PACKED 1
+#endif
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int NROWS>
 __device__ __forceinline__ bf16* half_ptr(bf16* base, int row, int chunk) {
   return base + (size_t)(chunk >> 3) * (NROWS * 64) + (size_t)row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
@@ -280,11 +308,19 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
         }
       }
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#if SI_ATTN_PACKED
+#pragma unroll
+      for (int i = 0; i < BN; i += 8) {                    // three-input maxima: half the instructions
+        m4[0] = max3(m4[0], s[i], s[i + 1]); m4[1] = max3(m4[1], s[i + 2], s[i + 3]);
+        m4[2] = max3(m4[2], s[i + 4], s[i + 5]); m4[3] = max3(m4[3], s[i + 6], s[i + 7]);
+      }
+#else
 #pragma unroll
       for (int i = 0; i < BN; i += 4) {
         m4[0] = fmaxf(m4[0], s[i]); m4[1] = fmaxf(m4[1], s[i + 1]);
         m4[2] = fmaxf(m4[2], s[i + 2]); m4[3] = fmaxf(m4[3], s[i + 3]);
       }
+#endif
       // the scale is positive, so the maximum may be taken before it
       const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
       // raise the base only when the maximum has outgrown it by 2^8; then O and l are rescaled. S being
@@ -303,6 +339,36 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
         }
       }
       const float base = m == -INFINITY ? 0.f : m;
+#if SI_ATTN_PACKED
+      // scale, subtraction of the base and the row's sum two scores at a time (fma.rn.f32x2, add.rn.f32x2: the
+      // same roundings as the single instructions, half as many of them)
+      const unsigned long long sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nb2 = pack_f32x2(-base, -base);
+      unsigned long long sum2[2] = {0ull, 0ull};
+#pragma unroll
+      for (int b = 0; b < BN / 64; ++b) {
+        unsigned pk[32];
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          float e[4];
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s[64 * b + i + 2 * w], s[64 * b + i + 2 * w + 1]), sc2, nb2), x0, x1);
+            e[2 * w] = fast_exp2(x0);                      // exp2(-inf) = 0 for masked keys
+            e[2 * w + 1] = fast_exp2(x1);
+            sum2[w] = add_f32x2(sum2[w], pack_f32x2(e[2 * w], e[2 * w + 1]));
+          }
+          pk[i / 2] = pack_bf16(e[0], e[1]);
+          pk[i / 2 + 1] = pack_bf16(e[2], e[3]);
+        }
+        // the probabilities of keys 64b .. 64b+63 go over columns 32b .. 32b+31 of S, which is in registers
+        tmem_st_32x32_issue(ts + 32 * b, pk);
+      }
+      float s4[4];
+      unpack_f32x2(sum2[0], s4[0], s4[1]);
+      unpack_f32x2(sum2[1], s4[2], s4[3]);
+      l = l * factor + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+#else
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int b = 0; b < BN / 64; ++b) {
@@ -322,6 +388,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
         tmem_st_32x32_issue(ts + 32 * b, pk);
       }
       l = l * factor + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+#endif
       tmem_st_wait();
       tc05_fence_before_sync();
       __syncwarp();

@@ -73,11 +73,12 @@ __device__ __forceinline__ void rows_store_chunk(TO* __restrict__ out, long long
 // Built with -DSI_ROWS_TIMING, every block leaves the times (ns, %globaltimer) of its milestones in
 // g_rows_times, which si_gemm_rows_times() copies out: where a launch spends its time, block by block.
 #ifdef SI_ROWS_TIMING
-__device__ unsigned long long g_rows_times[256][8];
+__device__ unsigned long long g_rows_times[8][256][8];   // the last eight launches
+__device__ unsigned g_rows_seq, g_rows_done;
 __device__ __forceinline__ void rows_stamp(int i) {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
-  g_rows_times[blockIdx.x][i] = t;
+  g_rows_times[*(volatile unsigned*)&g_rows_seq % 8][blockIdx.x][i] = t;
 }
 #else
 __device__ __forceinline__ void rows_stamp(int) {}
@@ -266,6 +267,13 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant
   __syncthreads();
   if (threadIdx.x == 0) rows_stamp(7);
   if (warp == 1) tmem_dealloc(tmem, 256);
+#ifdef SI_ROWS_TIMING
+  if (threadIdx.x == 0 && atomicAdd(&g_rows_done, 1u) == gridDim.x - 1) {   // the launch's last block
+    g_rows_done = 0;
+    __threadfence();
+    atomicAdd(&g_rows_seq, 1u);
+  }
+#endif
 }
 
 #ifdef SI_ROWS_TIMING

@@ -1003,3 +1003,34 @@ def test_attention_portion_at_prefill_size():
         us = e0.elapsed_time(e1) * 100
         flops = 4.0 * H * hs * T * (T + 1) / 2
         print(f"attn_portion {label}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+
+
+def test_attention_portion_at_the_end_of_a_long_context():
+    """The last 2,048 tokens of a 16,384-token prompt at the Llama-3.1-8B head layout (what a prompt cut into
+    portions asks of the kernel): sampled rows against torch, and the time (printed). Nearly every key tile lies
+    before the diagonal here, so the figure is the kernel's steady rate, without the causal edge."""
+    o = ops()
+    H, KV, hs, page_size, T, C = 32, 8, 128, 16, 2048, 16384
+    if not o.attn_portion_tc05_ok(H, KV, hs, page_size):
+        pytest.skip("the tcgen05 kernel does not take this layout")
+    g = torch.Generator(device=DEV).manual_seed(61)
+    blocks = C // page_size
+    kc = torch.randn(blocks + 7, KV, page_size, hs, generator=g, device=DEV).to(torch.bfloat16)
+    vc = torch.randn(blocks + 7, KV, page_size, hs, generator=g, device=DEV).to(torch.bfloat16)
+    table = torch.randperm(blocks + 7, generator=g, device=DEV)[:blocks].to(torch.int32).view(1, blocks)
+    q = torch.randn(T, H * hs, generator=g, device=DEV).to(torch.bfloat16)
+    q[777] *= 6.0                                           # one row whose softmax is sharp: a far key must be found
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hs)
+    tok = o.attn_portion_tc05_tokens(H, KV)
+    items = torch.tensor([(0, b, min(tok, T - b), C - T + b) for b in range(0, T, tok)], dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    run = lambda: o.attn_portion_tc05(q, kc, vc, table, items, out, page_size, 1, H, KV, hs, scale, 0, status=status)
+    run()
+    assert status.item() == 0 and not torch.isnan(out).any()
+    for r in (0, 1, 63, 64, 777, 1024, 2046, 2047):
+        ref = _torch_attention(q[r], kc, vc, table[0], C - T + r, H, KV, hs, scale)
+        assert (out[r].float() - ref).abs().max().item() <= 2 ** -8 * 4, f"row {r} against torch"
+    us = graph_time_us(lambda i: run(), n=5)
+    flops = 4.0 * H * hs * sum(C - T + r + 1 for r in range(T))
+    print(f"attn_portion tcgen05, 2,048 tokens ending at {C}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
