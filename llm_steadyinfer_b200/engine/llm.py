@@ -79,6 +79,7 @@ class LLM:
         self._run_ahead = self.async_decode and self.runner.graphs_available()
         self._inflight = None             # a launched step whose tokens have not been read: (items, wanted, handle)
         self._returned = 0
+        self._idle_steps = 0
         self.stats = {"steps": 0, "decode_steps": 0, "graph_steps": 0, "ahead_steps": 0, "tokens_in": 0,
                       "tokens_out": 0}
 
@@ -111,7 +112,16 @@ class LLM:
                 with tracing.span("schedule"):
                     items = self.scheduler.schedule()
                 if not items:
+                    # nothing to run although requests are unfinished: a step or two may pass like this (requests
+                    # requeued by a preemption are admitted by the next call), but never many
+                    self._idle_steps += 1
+                    if self._idle_steps > 8 and self.scheduler.has_unfinished():
+                        raise RuntimeError(
+                            f"the scheduler has found nothing to run for {self._idle_steps} steps although "
+                            f"{len(self.scheduler.running)} running and {len(self.scheduler.waiting)} waiting "
+                            f"requests are unfinished; they are aborted")
                     return []
+                self._idle_steps = 0
                 with tracing.span("launch"):
                     pending = self._launch(items)
             items, wanted, handle = pending

@@ -374,7 +374,8 @@ class Scheduler:
     def _preempt_for(self, group: int, need: int, requester: Sequence_) -> bool:
         """Free ``need`` pages of ``group``: first from requests that are preempted already and
         wait (they may give all they hold), then from running requests newer than the requester,
-        newest first, each keeping at least one page. Nothing happens unless enough can be freed
+        newest first, each keeping at least one page unless that frees too little. Nothing happens unless enough
+        can be freed
         (scheduler.cpp:269-313, which also takes from older requests)."""
         pool = self.cache.groups[group].pool
         ps = self.cache.page_size
@@ -388,22 +389,27 @@ class Scheduler:
         waiting.sort(key=lambda s: s.admit_order, reverse=True)
         running = [s for s in reversed(self.running)
                    if s.admit_order > requester.admit_order and s.state is SeqState.RUNNING]
-        plan = []
-        got = 0
-        for s, min_keep in [(s, 0) for s in waiting] + [(s, 1) for s in running]:
+        # running requests keep their first page if that frees enough; if not, they give everything too (a
+        # pool in which every newer request holds one page would otherwise leave the older one waiting for ever)
+        for running_keep in (1, 0):
+            plan = []
+            got = 0
+            for s, min_keep in [(s, 0) for s in waiting] + [(s, running_keep) for s in running]:
+                if got >= need:
+                    break
+                n = len(self.cache.table(group, s.id))
+                if all_or_nothing:
+                    keep = 0
+                else:
+                    keep = max(n - 1, min_keep)
+                    while keep > min_keep and gain_if_cut(s, keep) < need - got:
+                        keep -= 1
+                g = gain_if_cut(s, keep)
+                if g > 0:
+                    plan.append((s, keep))
+                    got += g
             if got >= need:
                 break
-            n = len(self.cache.table(group, s.id))
-            if all_or_nothing:
-                keep = 0
-            else:
-                keep = max(n - 1, min_keep)
-                while keep > min_keep and gain_if_cut(s, keep) < need - got:
-                    keep -= 1
-            g = gain_if_cut(s, keep)
-            if g > 0:
-                plan.append((s, keep))
-                got += g
         if got < need:
             return False
         newly = []

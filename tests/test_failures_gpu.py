@@ -99,3 +99,25 @@ def test_a_store_into_a_shared_page_is_refused_before_anything_runs(folders):
     pool.release(page)
     runner.finish("r")
     mgr.check_invariant()
+
+
+def test_a_schedule_that_stalls_ends_with_an_error_not_a_loop(folders):
+    """If the scheduler ever found nothing to run while requests are unfinished, ``generate`` would loop for
+    ever; the entry point counts such steps and, after a few, aborts the requests and raises. The stall is made
+    on the host: a scheduler whose ``schedule`` returns nothing."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    llm = LLM(folders["A"], dtype="float32", max_batch=2, max_seq_len=64, max_gen_len=4, block_size=16)
+    prompt = ru.random_tokens(CONFIGS["A"][0]["vocab_size"], 5, 77)
+    want = llm.generate([prompt], SamplingParams(ignore_eos=True))[0].token_ids
+    real = llm.scheduler.schedule
+    llm.scheduler.schedule = lambda: []
+    rid = llm.add_request(prompt, SamplingParams(ignore_eos=True))
+    with pytest.raises(RuntimeError) as e:
+        for _ in range(100):
+            llm.step()
+    assert "nothing to run" in str(e.value)
+    assert llm.all_finished()
+    assert [(s.id, s.finish_reason) for s in llm.get_finished()][-1] == (rid, "aborted")
+    llm.runner.manager.check_invariant()
+    llm.scheduler.schedule = real
+    assert llm.generate([prompt], SamplingParams(ignore_eos=True))[0].token_ids == want, "the engine goes on"

@@ -431,3 +431,24 @@ def test_portion_admission_aborts_what_can_never_fit():
     assert s.finished[0].id == a and s.finished[0].finish_reason in ("length", "aborted")
     cache.check_invariant()
     assert cache.free_pages(0) == 4
+
+
+def test_newer_requests_with_one_page_each_give_it_up_for_an_older_portion():
+    """``reserve="portion"`` with a portion of one page: every request is admitted on one page and the pool is
+    full of one-page holders. The oldest request's next portion then needs a page that only a newer request's
+    last page can give: that request gives it, waits and starts again, and every request finishes. (Victims that
+    always kept their first page left the older request waiting for ever.)"""
+    s, cache = make(num_pages=5, page_size=4, max_seqs=5, budget=4, max_gen=2)
+    s.reserve = "portion"
+    ids = [s.add_request(list(range(50 * i, 50 * i + 10))) for i in range(5)]       # 3 pages each, 5 in the pool
+    n = 0
+    while s.has_unfinished():
+        items = run_step(s, cache)
+        n += 1
+        assert items or n < 3, "a step with nothing to run while requests wait: the schedule has stalled"
+        assert n < 400, "the schedule must end"
+    assert s.num_preemptions >= 1
+    assert sorted(q.id for q in s.finished) == sorted(ids)
+    assert all(q.finish_reason == "length" and len(q.outputs) == 2 for q in s.finished)
+    assert cache.free_pages(0) == 5
+    cache.check_invariant()
