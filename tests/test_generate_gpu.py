@@ -293,3 +293,46 @@ def test_long_prompt_workload_in_small_preempts_and_completes(folders, dtype):
         assert_same_until_a_near_tie(folders["B"], prompts, [g.token_ids for g in got], want)
     llm.runner.manager.check_invariant()
     assert not llm.runner.manager.requests
+
+
+@pytest.mark.parametrize("first", [0, 8, 16])
+def test_random_set_ups_match_plain(folders, first):
+    """A random search over serving set-ups in float32 (model, number and lengths of requests, shared prefixes,
+    greedy and seeded sampling, batch size, pool size down to what one request needs, token budget from one page
+    to whole prompts, both admission rules, prefix reuse on and off, steps ahead on and off): every request's
+    tokens equal the plain implementation's, and no page is left behind. (A longer run of this search found the
+    stall that ``test_newer_requests_with_one_page_each_give_it_up_for_an_older_portion`` pins.)"""
+    import random
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    plain = {n: plain_llama.read_model_folder(folders[n]) for n in CONFIGS}
+    for seed in range(first, first + 8):
+        rng = random.Random(seed)
+        name = rng.choice(list(CONFIGS))
+        cfg, _, page = CONFIGS[name]
+        V = cfg["vocab_size"]
+        shared = ru.random_tokens(V, rng.choice([8, 24, 40]), 9000 + seed)
+        prompts, params, sampling = [], [], []
+        for i in range(rng.randint(3, 12)):
+            toks = ru.random_tokens(V, rng.choice([1, 2, 3, 5, 9, 17, 33, 47, 60, 90]), 7000 + 100 * seed + i)
+            prompts.append(shared + toks if rng.random() < 0.35 else toks)
+            kw = {"max_tokens": rng.choice([1, 2, 7, 16, 29, 40])}
+            if rng.random() < 0.4:
+                kw.update(temperature=rng.choice([0.6, 1.0]), top_p=rng.choice([1.0, 0.8]), top_k=rng.choice([0, 10]),
+                          seed=rng.randrange(1000))
+            sampling.append(kw)
+            params.append(SamplingParams(ignore_eos=True, **kw))
+        longest = max(len(p) for p in prompts) + 40
+        one = -(-longest // page) + 1                          # pages of the longest request, and one
+        setup = dict(max_batch=rng.randint(1, 9), max_seq_len=one * page, max_gen_len=40, block_size=page,
+                     num_blocks=rng.choice([one, one + 3, 2 * one, 4 * one]), async_decode=rng.random() < 0.6,
+                     max_num_batched_tokens=rng.choice(["adaptive", 8, 16, 48, 2048]),
+                     reserve=rng.choice(["prompt", "portion"]), enable_prefix_cache=rng.random() < 0.6)
+        llm = LLM(folders[name], dtype="float32", **setup)
+        res = llm.generate(prompts, params)
+        llm.runner.manager.check_invariant()
+        assert not llm.runner.manager.requests
+        mcfg, w = plain[name]
+        for i, (g, kw) in enumerate(zip(res, sampling)):
+            kw = dict(kw)
+            want = plain_llama.generate(mcfg, w, prompts[i], kw.pop("max_tokens"), **kw)
+            assert g.finish_reason == "length" and g.token_ids == want, f"seed {seed}, {name}, {setup}: request {i}"
