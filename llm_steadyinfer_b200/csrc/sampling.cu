@@ -14,8 +14,10 @@
 
 #define SAMPLE_THREADS 1024
 
+// Larger float, larger key; -0.0 and +0.0, equal as numbers, get the same key (they must tie like other equals).
 __device__ __forceinline__ unsigned ordered_key(float x) {
   unsigned u = __float_as_uint(x);
+  if (u == 0x80000000u) u = 0u;
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 

@@ -292,6 +292,29 @@ def test_sampling_kernel_matches_plain():
         assert out.tolist() == want, (temp, k, p)
 
 
+def test_sampling_treats_both_zeros_as_equal():
+    """-0.0 and +0.0 are equal logits: top-k keeps all ties of the k-th, whichever zero they are, and the draw
+    goes over all of them in index order, as the plain sampler's (a random search with rounded logits found the
+    kernel's integer image of the logits telling the two zeros apart)."""
+    V, R = 40, 16
+    logits = torch.full((R, V), -3.0)
+    zeros = [3, 7, 8, 21, 39]
+    for r in range(R):
+        for j, i in enumerate(zeros):
+            logits[r, i] = -0.0 if (r + j) % 2 else 0.0
+    dl = logits.to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    seed = torch.arange(R, dtype=torch.int64, device=DEV) * 31 + 5
+    ctr = torch.arange(R, dtype=torch.int64, device=DEV)
+    for temp, k, p in [(1.0, 1, 1.0), (0.7, 2, 0.5), (1.5, 0, 0.0001)]:
+        ops().sample(dl, out, temperature=torch.full((R,), temp, device=DEV),
+                     top_k=torch.full((R,), k, dtype=torch.int32, device=DEV), top_p=torch.full((R,), p, device=DEV),
+                     seed=seed, counter=ctr)
+        want = [plain_llama.sample(logits[r], temp, k, p, seed=int(seed[r]), counter=int(ctr[r])) for r in range(R)]
+        assert out.tolist() == want, (temp, k, p)
+        assert len(set(want)) > 1 and set(want) <= set(zeros), "the draws spread over all five zeros"
+
+
 def test_sampling_distribution():
     """Draws over many counters follow softmax(x / T) restricted by top-p."""
     V = 37
