@@ -138,6 +138,9 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
     steps0, pre0, rec0 = sched.num_steps, sched.num_preemptions, sched.num_recomputed_tokens
     used_sum = alloc_sum = running_sum = samples = peak_pages = 0
     ps = llm.runner.page_size
+    from .gpu_sampler import GpuUtilSampler
+    gpu = GpuUtilSampler(torch.cuda.current_device())
+    gpu.start()
     start = time.monotonic()
     while pending or not llm.all_finished():
         now = time.monotonic() - start
@@ -161,6 +164,7 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
         llm.step()
     torch.cuda.synchronize()
     wall = time.monotonic() - start
+    gpu.stop()
     fin = [s for s in llm.get_finished() if s.id not in warm and s.outputs]
     ttft = [(s.first_token_time - s.arrival_time) * 1e3 for s in fin]
     e2e = [(s.finish_time - s.arrival_time) * 1e3 for s in fin]
@@ -185,7 +189,28 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
         "recomputed_tokens": sched.num_recomputed_tokens - rec0,
         "prefix_hit_tokens": sum(s.prefix_hit_tokens for s in fin),
         "finish_reasons": dict((r, sum(1 for s in fin if s.finish_reason == r)) for r in {s.finish_reason for s in fin}),
+        **model_flops_utilisation(llm, (prompt_tokens + output_tokens) / wall), **gpu.summary(),
     }
+
+
+def model_flops_utilisation(llm, total_tps: float) -> dict:
+    """MFU as the reference reports it (offline_batch_benchmark.cpp:355-362): tokens a second times the FLOPs of
+    a token's projections over a peak rate, here the peak of the dtype that computes."""
+    import torch
+    from .gpu_sampler import flops_per_token, peak_tflops
+    cfg = llm.model.config
+    dims = [getattr(cfg, k, None) for k in ("hidden_size", "intermediate_size", "num_hidden_layers",
+                                            "num_attention_heads", "num_key_value_heads", "head_dim")]
+    if any(d is None for d in dims):
+        return {"mfu": 0.0, "peak_tflops": 0.0, "peak_source": "no estimate for this architecture", "theoretical_peak_tps": 0.0}
+    per_token = flops_per_token(*dims)
+    prop = torch.cuda.get_device_properties(torch.cuda.current_device())
+    clock_mhz = getattr(prop, "clock_rate", 0) / 1e3 or 1965.0
+    here = os.path.dirname(os.path.abspath(__file__))
+    peak, source = peak_tflops("bfloat16" if llm.dtype == torch.bfloat16 else "float32", prop.multi_processor_count, clock_mhz,
+                               os.path.join(here, "..", "..", "MEASURED_PEAKS.json"))
+    return {"mfu": round(total_tps * per_token / (peak * 1e12), 6), "peak_tflops": round(peak, 1), "peak_source": source,
+            "theoretical_peak_tps": round(peak * 1e12 / per_token, 1)}
 
 
 def main(argv: Optional[List[str]] = None) -> int:
@@ -221,7 +246,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         rows.append(m)
         print(f"[run {it}] requests {m['completed']}/{m['num_requests']}  output_tps {m['output_tps']}  total_tps {m['total_tps']}  "
               f"ttft p50/p99 {m['ttft_p50_ms']}/{m['ttft_p99_ms']} ms  tpot p50/p99 {m['tpot_p50_ms']}/{m['tpot_p99_ms']} ms  "
-              f"avg batch {m['avg_batch_size']}  preemptions {m['preemptions']}  prefix hit tokens {m['prefix_hit_tokens']}")
+              f"avg batch {m['avg_batch_size']}  preemptions {m['preemptions']}  prefix hit tokens {m['prefix_hit_tokens']}  "
+              f"mfu {m['mfu']}  gpu sm/mem util {m['gpu_sm_util_pct']}/{m['gpu_mem_util_pct']} %")
     if args.output_csv:
         os.makedirs(os.path.dirname(os.path.abspath(args.output_csv)), exist_ok=True)
         with open(args.output_csv, "w", newline="") as f:

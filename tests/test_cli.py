@@ -25,6 +25,40 @@ def test_positional_form_and_flags():
         parse_args([])
 
 
+def test_gpu_sampler_against_a_stand_in_for_nvml():
+    """The sampler thread averages what NVML returns and only reads; without NVML its figures stay 0."""
+    import time
+    import types
+    from llm_steadyinfer_b200.cli.gpu_sampler import GpuUtilSampler, flops_per_token, peak_tflops
+    calls = {"init": 0, "shutdown": 0, "reads": 0}
+
+    def rates(dev):
+        calls["reads"] += 1
+        return types.SimpleNamespace(gpu=80 if calls["reads"] % 2 else 60, memory=30)
+
+    fake = types.SimpleNamespace(
+        nvmlInit=lambda: calls.__setitem__("init", calls["init"] + 1),
+        nvmlShutdown=lambda: calls.__setitem__("shutdown", calls["shutdown"] + 1),
+        nvmlDeviceGetHandleByIndex=lambda i: ("dev", i), nvmlDeviceGetUtilizationRates=rates,
+        nvmlDeviceGetMemoryInfo=lambda dev: types.SimpleNamespace(used=3 * 1024 * 1024 * 1024))
+    s = GpuUtilSampler(index=0, period_s=0.005, nvml=fake)
+    assert s.start()
+    time.sleep(0.08)
+    s.stop()
+    out = s.summary()
+    assert out["gpu_samples"] >= 4 and 60 <= out["gpu_sm_util_pct"] <= 80 and out["gpu_mem_util_pct"] == 30
+    assert out["gpu_mem_used_mb"] == 3072.0 and calls["init"] == 1 and calls["shutdown"] == 1
+    broken = types.SimpleNamespace(nvmlInit=lambda: (_ for _ in ()).throw(RuntimeError("no driver")))
+    b = GpuUtilSampler(nvml=broken)
+    assert not b.start() and b.summary()["gpu_samples"] == 0
+    b.stop()
+    # the reference's estimate (benchmark/bench_common.h:215-221) at the Llama-3.1-8B sizes: 2 x the blocks' parameters
+    assert flops_per_token(4096, 14336, 32, 32, 8, 128) == 32 * (4.0 * 4096 * 128 * 40 + 6.0 * 4096 * 14336)
+    assert peak_tflops("bfloat16", 148, 1965.0, None) == (2250.0, "nominal dense bf16")
+    v, src = peak_tflops("float32", 148, 1965.0, None)
+    assert abs(v - 148 * 128 * 2 * 1.965e-3) < 1e-9 and "fp32" in src
+
+
 @pytest.mark.gpu
 def test_cli_runs_the_1b_style_workload_small(tmp_path):
     """Lognormal lengths, Poisson arrivals, a shared prefix, sampling: through the program itself."""
@@ -44,3 +78,5 @@ def test_cli_runs_the_1b_style_workload_small(tmp_path):
     assert m["completed"] == 24 and m["rejected"] == 0 and m["output_tokens"] > 24
     assert m["prefix_hit_tokens"] > 0 and m["output_tps"] > 0 and m["ttft_p99_ms"] >= m["ttft_p50_ms"] > 0
     assert (tmp_path / "m.csv").read_text().startswith("run_id,")
+    assert 0 < m["mfu"] < 1 and m["peak_tflops"] > 0 and m["theoretical_peak_tps"] > m["total_tps"]
+    assert {"gpu_sm_util_pct", "gpu_mem_util_pct", "gpu_mem_used_mb", "gpu_samples"} <= set(m)
