@@ -136,7 +136,9 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
                                   seed=args.seed * 100003 + i, max_tokens=out_lens[i], ignore_eos=args.ignore_eos)
     rejected, pending, ids = 0, list(range(len(prompts))), {}
     steps0, pre0, rec0 = sched.num_steps, sched.num_preemptions, sched.num_recomputed_tokens
-    used_sum = alloc_sum = running_sum = samples = peak_pages = 0
+    used_sum = alloc_sum = running_sum = samples = peak_pages = busy_sum = peak_busy = 0
+    dec0 = llm.stats["steps_with_decode"]
+    llm.decode_host_ms.clear()
     ps = llm.runner.page_size
     from .gpu_sampler import GpuUtilSampler
     gpu = GpuUtilSampler(torch.cuda.current_device())
@@ -160,6 +162,9 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
             alloc_sum += pages * ps
             running_sum += len(running)
             peak_pages = max(peak_pages, pages)
+            busy = len(llm.runner.manager.requests)          # requests that hold cache, preempted ones included
+            busy_sum += busy
+            peak_busy = max(peak_busy, busy)
             samples += 1
         llm.step()
     torch.cuda.synchronize()
@@ -173,6 +178,14 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
     prompt_tokens = sum(len(s.prompt) for s in fin)
     output_tokens = sum(len(s.outputs) for s in fin)
     mean = lambda xs: statistics.fmean(xs) if xs else 0.0
+    # a request's own waste: the unused end of its last page (the reference, with one slot of max_seq_len per
+    # request, counts the unused end of the slot: offline_batch_benchmark.cpp:301-302)
+    per_seq_frag = [1.0 - n / (-(-n // ps) * ps) for n in (len(s.prompt) + len(s.outputs) for s in fin)]
+    decode_steps = llm.stats["steps_with_decode"] - dec0
+    host_ms = list(llm.decode_host_ms)
+    # steps that drew at least one token (the reference counts its pure decode steps, and its first tokens come
+    # from other steps: offline_batch_benchmark.cpp:343-354); as if each had drawn max_batch of them
+    peak_tps = args.max_batch * decode_steps / wall if wall > 0 else 0.0
     return {
         "run_id": run_id, "num_requests": len(prompts), "completed": len(fin), "rejected": rejected,
         "prompt_tokens": prompt_tokens, "output_tokens": output_tokens, "total_tokens": prompt_tokens + output_tokens,
@@ -184,7 +197,13 @@ def run_once(llm, prompts, out_lens, args, run_id: int, rng: random.Random) -> d
         "e2e_avg_ms": round(mean(e2e), 3), "e2e_p99_ms": round(pct(e2e, 99), 3),
         "kv_cache_util_global": round(used_sum / alloc_sum, 4) if alloc_sum else 0.0,
         "kv_cache_frag_global": round(1 - used_sum / alloc_sum, 4) if alloc_sum else 0.0,
+        "kv_cache_frag_per_seq": round(mean(per_seq_frag), 4),
+        "avg_busy_kv_slots": round(busy_sum / samples, 3) if samples else 0.0, "peak_busy_kv_slots": peak_busy,
+        "avg_batch_reconstruct_ms": round(mean(host_ms), 4), "p99_batch_reconstruct_ms": round(pct(host_ms, 99), 4),
         "peak_kv_blocks": peak_pages, "avg_batch_size": round(running_sum / samples, 3) if samples else 0.0,
+        "avg_decode_batch": round(output_tokens / decode_steps, 3) if decode_steps else 0.0,
+        "throughput_efficiency": round(output_tokens / wall / peak_tps, 4) if peak_tps else 0.0,
+        "theoretical_peak_tps": round(peak_tps, 2),
         "steps": sched.num_steps - steps0, "preemptions": sched.num_preemptions - pre0,
         "recomputed_tokens": sched.num_recomputed_tokens - rec0,
         "prefix_hit_tokens": sum(s.prefix_hit_tokens for s in fin),
@@ -202,15 +221,14 @@ def model_flops_utilisation(llm, total_tps: float) -> dict:
     dims = [getattr(cfg, k, None) for k in ("hidden_size", "intermediate_size", "num_hidden_layers",
                                             "num_attention_heads", "num_key_value_heads", "head_dim")]
     if any(d is None for d in dims):
-        return {"mfu": 0.0, "peak_tflops": 0.0, "peak_source": "no estimate for this architecture", "theoretical_peak_tps": 0.0}
+        return {"mfu": 0.0, "peak_tflops": 0.0, "peak_source": "no estimate for this architecture"}
     per_token = flops_per_token(*dims)
     prop = torch.cuda.get_device_properties(torch.cuda.current_device())
     clock_mhz = getattr(prop, "clock_rate", 0) / 1e3 or 1965.0
     here = os.path.dirname(os.path.abspath(__file__))
     peak, source = peak_tflops("bfloat16" if llm.dtype == torch.bfloat16 else "float32", prop.multi_processor_count, clock_mhz,
                                os.path.join(here, "..", "..", "MEASURED_PEAKS.json"))
-    return {"mfu": round(total_tps * per_token / (peak * 1e12), 6), "peak_tflops": round(peak, 1), "peak_source": source,
-            "theoretical_peak_tps": round(peak * 1e12 / per_token, 1)}
+    return {"mfu": round(total_tps * per_token / (peak * 1e12), 6), "peak_tflops": round(peak, 1), "peak_source": source}
 
 
 def main(argv: Optional[List[str]] = None) -> int:

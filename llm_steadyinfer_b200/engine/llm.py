@@ -9,6 +9,8 @@ reference's ``Scheduler(model, max_batch, max_seq_len, max_gen_len, block_size)`
 """
 from __future__ import annotations
 
+import collections
+import time
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Union
 
@@ -80,8 +82,9 @@ class LLM:
         self._inflight = None             # a launched step whose tokens have not been read: (items, wanted, handle)
         self._returned = 0
         self._idle_steps = 0
+        self.decode_host_ms = collections.deque(maxlen=1 << 16)    # host time of the latest steps that drew tokens
         self.stats = {"steps": 0, "decode_steps": 0, "graph_steps": 0, "ahead_steps": 0, "tokens_in": 0,
-                      "tokens_out": 0}
+                      "tokens_out": 0, "steps_with_decode": 0}
 
     # ---- the reference's driver-facing calls ----------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -144,6 +147,7 @@ class LLM:
         """Queue one step on the GPU (model, sampling, copy of the ids to the host) without waiting for it.
         Rows with ``fed`` set take their token from the ids that the step before this one sampled, which
         are still on the device: ``src_rows`` maps ``id(request)`` to its row among that step's wanted rows."""
+        t0 = time.perf_counter()
         entries = [StepEntry(it.seq.id, [0] if it.fed else it.tokens, [it.count - 1] if it.want_logits else [])
                    for it in items]
         feed = None
@@ -165,6 +169,12 @@ class LLM:
             logits = self.runner.step(entries, feed=feed)
         self.stats["tokens_in"] += sum(it.count for it in items)
         wanted = [it for it in items if it.want_logits]
+        if wanted:
+            # a step that draws tokens: the host's part of it (the batch's integers packed and copied, the launch),
+            # which the reference's scheduler records for its decode steps as "batch reconstruct" time
+            # (scheduler.cpp:560-573)
+            self.stats["steps_with_decode"] += 1
+            self.decode_host_ms.append((time.perf_counter() - t0) * 1e3)
         if not wanted:
             return items, wanted, None
         # the index of the output token keys the draw; a fed row draws the one after the unread token

@@ -78,5 +78,10 @@ def test_cli_runs_the_1b_style_workload_small(tmp_path):
     assert m["completed"] == 24 and m["rejected"] == 0 and m["output_tokens"] > 24
     assert m["prefix_hit_tokens"] > 0 and m["output_tps"] > 0 and m["ttft_p99_ms"] >= m["ttft_p50_ms"] > 0
     assert (tmp_path / "m.csv").read_text().startswith("run_id,")
-    assert 0 < m["mfu"] < 1 and m["peak_tflops"] > 0 and m["theoretical_peak_tps"] > m["total_tps"]
+    assert 0 < m["mfu"] < 1 and m["peak_tflops"] > 0
+    # the reference's occupancy figures (offline_batch_benchmark.cpp:343-354)
+    assert 0 < m["avg_decode_batch"] <= 6 and 0 < m["throughput_efficiency"] <= 1
+    assert abs(m["throughput_efficiency"] - m["output_tps"] / m["theoretical_peak_tps"]) < 1e-3
+    assert 0 < m["avg_busy_kv_slots"] <= m["peak_busy_kv_slots"] <= 6 and 0 <= m["kv_cache_frag_per_seq"] < 1
+    assert m["avg_batch_reconstruct_ms"] > 0 and m["p99_batch_reconstruct_ms"] > 0     # (a recording can lift the mean above p99)
     assert {"gpu_sm_util_pct", "gpu_mem_util_pct", "gpu_mem_used_mb", "gpu_samples"} <= set(m)
