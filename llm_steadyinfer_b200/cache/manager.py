@@ -181,6 +181,9 @@ class CacheManager:
 
     def grow(self, req, new_length: int) -> None:
         """Take pages so that tokens [0, new_length) have a place, in every group or in none."""
+        need = -(-new_length // self.page_size)
+        if all(len(g.tables[req]) >= need for g in self.groups):
+            return                                  # the usual decode step: the last page still has room
         missing = self.pages_missing(req, new_length)
         for m, g in zip(missing, self.groups):
             if m > g.pool.num_free:

@@ -384,21 +384,29 @@ class ModelRunner:
         h[b_qs:b_qs + S_cap + 1] = T
         h[b_cl:b_cl + S_cap] = 0
         h[b_sl:b_sl + S_cap] = 0
+        # one assignment a region: the per-entry values are gathered in lists first (a step of 64 decode rows
+        # would otherwise pay for several hundred small array writes)
+        toks, pos, seqs, qs, cl, sl, lr = [], [], [], [], [], [], []
         row = 0
-        r = 0
         for s, e in enumerate(entries):
             n = len(e.tokens)
             start = mgr.length(e.req)
-            h[b_tok + row:b_tok + row + n] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-            h[b_pos + row:b_pos + row + n] = np.arange(start, start + n, dtype=np.int32)
-            h[b_seq + row:b_seq + row + n] = s
-            h[b_qs + s] = row
-            h[b_cl + s] = start + n
-            h[b_sl + s] = mgr.slot(e.req)
+            if n == 1:
+                toks.append(e.tokens[0]); pos.append(start); seqs.append(s)
+            else:
+                toks.extend(e.tokens); pos.extend(range(start, start + n)); seqs.extend([s] * n)
+            qs.append(row); cl.append(start + n); sl.append(mgr.slot(e.req))
             for w in e.want:
-                h[b_lr + r] = row + w
-                r += 1
+                lr.append(row + w)
             row += n
+        h[b_tok:b_tok + T] = np.asarray(toks, dtype=np.int64).astype(np.int32)   # an id beyond 32 bits wraps and is flagged by the kernel
+        h[b_pos:b_pos + T] = pos
+        h[b_seq:b_seq + T] = seqs
+        h[b_qs:b_qs + S] = qs
+        h[b_cl:b_cl + S] = cl
+        h[b_sl:b_sl + S] = sl
+        if lr:
+            h[b_lr:b_lr + len(lr)] = lr
         tabs = h[table_off:table_off + G * S_cap * W_cap].reshape(G, S_cap, W_cap)
         tabs[:] = -1
         for g in range(G):
