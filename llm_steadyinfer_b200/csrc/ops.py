@@ -712,7 +712,6 @@ def gemm_tc05_swiglu(a, w, out, status=None) -> None:
 # ---- tcgen05 matrix product for up to 128 rows ------------------------------------------------------
 
 ROWS_MAX = 128
-_rows_scratch: dict = {}
 
 
 def gemm_rows_ok(a, w, out) -> bool:
@@ -720,34 +719,17 @@ def gemm_rows_ok(a, w, out) -> bool:
     return a.shape[0] <= ROWS_MAX and gemm_tc05_ok(a, w, out)
 
 
-def _rows_scratch_for(device) -> torch.Tensor:
-    """The kernel's scratch on ``device`` (partial sums of the blocks that share a tile, and their flags):
-    one buffer for all calls, which run one after the other on the engine's stream. Allocated at the first call
-    (before any graph is recorded: a shape's first step runs directly); calls on several streams at once would
-    have to bring their own."""
-    t = _rows_scratch.get(device.index)
-    if t is None:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("gemm_rows: the scratch would have to be allocated while a graph is recorded")
-        lib = build.load("gemm_rows")
-        lib.si_gemm_rows_scratch_words.restype = _c_ll
-        with torch.cuda.device(device):
-            words = int(lib.si_gemm_rows_scratch_words())
-        t = _rows_scratch[device.index] = torch.zeros(words, dtype=torch.float32, device=device)
-    return t
-
-
 def gemm_rows(a, w, out, status=None) -> None:
-    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 128 on the tcgen05 tensor cores, W streamed once through all SMs
-    in equal shares (see gemm_rows.cu)."""
+    """out[M,N] = a[M,K] @ w[N,K]^T for M <= 128 on the tcgen05 tensor cores: a tile of 128 output columns a
+    block, the k range of a tile cut over a cluster where the tiles alone do not fill the GPU (see gemm_rows.cu)."""
     _cuda(a, w, out, status)
     M, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (M, N), "gemm_rows: shapes")
     _need(gemm_rows_ok(a, w, out), "gemm_rows: bf16 inputs, at most 128 rows, K a multiple of 8, 16-byte aligned rows")
-    f = _fn("gemm_rows", "si_gemm_rows", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    f = _fn("gemm_rows", "si_gemm_rows", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(a), a.stride(0), _weight_map(w, 128), _ptr(out), out.stride(0), _dt(out), M, N, K,
-             _ptr(_rows_scratch_for(a.device)), _ptr(status), _stream()), f"gemm_rows(M={M}, N={N}, K={K})")
+             _ptr(status), _stream()), f"gemm_rows(M={M}, N={N}, K={K})")
 
 
 def gemm_rows_swiglu(a, w, out, status=None) -> None:
@@ -759,9 +741,9 @@ def gemm_rows_swiglu(a, w, out, status=None) -> None:
     _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
           "gemm_rows_swiglu: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
     _need(gemm_rows_ok(a, w, out), "gemm_rows_swiglu: bf16 inputs, at most 128 rows, K a multiple of 8, 16-byte aligned rows")
-    f = _fn("gemm_rows", "si_gemm_rows_swiglu", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p])
+    f = _fn("gemm_rows", "si_gemm_rows_swiglu", [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(a), a.stride(0), _weight_map(w, 128), _ptr(out), out.stride(0), M, F, K,
-             _ptr(_rows_scratch_for(a.device)), _ptr(status), _stream()), f"gemm_rows_swiglu(M={M}, F={F}, K={K})")
+             _ptr(status), _stream()), f"gemm_rows_swiglu(M={M}, F={F}, K={K})")
 
 
 # ---- prompt-portion attention on tcgen05 ---------------------------------------------------------

@@ -8,7 +8,7 @@ batches, short portions) to the library product behind ``torch.mm`` (cuBLAS, fp3
 the reference sends every projection and the LM head to ``cublasGemmEx``
 (src/source/op/kernels/cuda/matmul_kernel.cu:128-150). The package has a tcgen05 kernel for those
 row counts too (``gemm_rows.cu``, SI_OWN_ROWS=1 turns it on), but at the shapes measured the library
-is still 1.2 to 3 times faster there. The library also takes what the kernels refuse (rows that are
+is still 1.1 to 1.6 times faster there. The library also takes what the kernels refuse (rows that are
 not 16-byte aligned), and every many-row product with SI_OWN_GEMM=0.
 """
 from __future__ import annotations
