@@ -1057,3 +1057,146 @@ def test_attention_portion_at_the_end_of_a_long_context():
     us = graph_time_us(lambda i: run(), n=5)
     flops = 4.0 * H * hs * sum(C - T + r + 1 for r in range(T))
     print(f"attn_portion tcgen05, 2,048 tokens ending at {C}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+
+
+# ---- random searches over sizes ---------------------------------------------------------------------------------
+
+def _swiglu_of_interleaved(y, F):
+    """silu(gate) * up of a product whose columns hold 8 gates, their 8 ups, 8 gates, ... (both rounded to bf16)."""
+    y = y.to(torch.bfloat16).double().view(y.shape[0], F // 8, 2, 8)
+    gate, up = y[:, :, 0], y[:, :, 1]
+    return (gate / (1 + torch.exp(-gate)) * up).reshape(y.shape[0], F)
+
+
+def test_matrix_products_at_random_sizes():
+    """Every matrix-product kernel of the package (few rows, up to 128 rows, many rows; plain, with the gated
+    activation, into the residual stream) at 400 random sizes and row strides against a float64 product."""
+    import random
+    o = ops()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for seed in range(400):
+        rng = random.Random(seed)
+        g = torch.Generator(device=DEV).manual_seed(seed)
+        kind = rng.choice(["skinny", "skinny_swiglu", "tc05", "tc05", "tc05_swiglu", "tc05_add", "rows", "rows_swiglu"])
+        K = 8 * rng.choice([1, 2, 5, 8, 12, 33, 64, 100, 167, 512, 1792])
+        M = (rng.randint(1, 16) if kind.startswith("skinny") else rng.randint(1, 128) if kind.startswith("rows")
+             else rng.choice([1, 17, 100, 127, 128, 129, 200, 255, 256, 257, 300, 511, 513, 700, 1025]))
+        N = rng.choice([8, 16, 40, 96, 128, 136, 256, 264, 520, 1000, 1024, 2056, 4096 + 8 * rng.randint(0, 40)])
+        if "swiglu" in kind:
+            N = 2 * (N // 2 // 8 * 8 or 8)
+        ldx, ldw = K + 8 * rng.choice([0, 0, 1, 3]), K + 8 * rng.choice([0, 0, 2])
+        x = torch.randn(M, ldx, generator=g, device=DEV).to(torch.bfloat16)[:, :K]
+        w = (torch.randn(N, ldw, generator=g, device=DEV) / K ** 0.5).to(torch.bfloat16)[:, :K]
+        want = x.double() @ w.double().T
+        what = f"seed {seed}: {kind}, {M} x {N} x {K}, row strides {ldx} and {ldw}"
+        if kind in ("skinny", "tc05", "rows"):
+            odt = rng.choice([torch.bfloat16, torch.float32])
+            out = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+            {"skinny": lambda: o.gemm_skinny(x, w, out), "tc05": lambda: o.gemm_tc05(x, w, out, status),
+             "rows": lambda: o.gemm_rows(x, w, out, status)}[kind]()
+            tol = 2 ** -8 * max(1.0, want.abs().max().item()) if odt == torch.bfloat16 else 1e-3
+            err = (out.double() - want).abs().max().item()
+        elif kind == "tc05_add":
+            resid = torch.randn(M, N, generator=g, device=DEV)
+            before = resid.clone()
+            o.gemm_tc05_add(x, w, resid, status)
+            err = (resid.double() - (before.double() + want.to(torch.bfloat16).double())).abs().max().item()
+            tol = 2 ** -7 * max(1.0, want.abs().max().item())
+        else:
+            F = N // 2
+            out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+            {"skinny_swiglu": lambda: o.gemm_skinny_swiglu(x, w, out), "tc05_swiglu": lambda: o.gemm_tc05_swiglu(x, w, out, status),
+             "rows_swiglu": lambda: o.gemm_rows_swiglu(x, w, out, status)}[kind]()
+            ref = _swiglu_of_interleaved(want, F)
+            err = (out.double() - ref).abs().max().item()
+            tol = 2 ** -6 * max(1.0, ref.abs().max().item())
+        assert err <= tol and status.item() == 0, f"{what}: off by {err:.3e} (allowed {tol:.3e}), status {status.item()}"
+
+
+def test_attention_kernels_at_random_layouts():
+    """The tensor-core attention kernels at 250 random layouts (head sizes, heads, groups, page sizes, windows),
+    lengths around the edges of pages and tiles, tails from one decode row to whole prompts, and numbers of
+    splits, against the plain attention. Layouts that a kernel declines by contract are passed over."""
+    import random
+    ran = 0
+    for seed in range(250):
+        rng = random.Random(seed)
+        hs = rng.choice([16, 32, 48, 64, 64, 64, 80, 96, 128, 128, 128, 256])
+        KV, G = rng.choice([1, 2, 3, 8]), rng.choice([1, 2, 3, 4, 5, 8, 16, 32])
+        if KV * G > 40:
+            G = rng.choice([1, 2, 4])
+        H, page = KV * G, rng.choice([4, 8, 16, 32, 64])
+        window = rng.choice([None, None, 5, 64, 65, 130])
+        S = rng.randint(1, 6)
+        lengths = [rng.choice([1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 200, 333, 512, 640]) for _ in range(S)]
+        tails = [rng.choice([1, 1, 1, 2, 3, 8, 40, 64, 128, 10 ** 6]) for _ in range(S)]
+        mode = rng.choice(["cp_async", "tma", "tcgen05"])
+        nsplit = 1 if mode == "tcgen05" else rng.choice([1, 1, 2, 3, 5, 8])
+        what = (f"seed {seed}: {mode}, {H} heads, {KV} groups, head size {hs}, page {page}, window {window}, "
+                f"lengths {lengths}, tails {tails}, {nsplit} splits")
+        seqs, table, kc, vc = build_cache(torch.bfloat16, lengths, H, KV, hs, page, seed=seed)
+        try:
+            out, rows, _, _ = _run_tc_attention(seqs, table, kc, vc, lengths, tails, H, KV, hs, page, window, nsplit,
+                                                mode != "cp_async", mode == "tcgen05")
+        except pytest.skip.Exception:
+            continue
+        except ops().KernelError as e:
+            assert "do not fit" in str(e) or "outside what the kernel supports" in str(e), f"{what}: {e}"
+            continue
+        ran += 1
+        scale = 1.0 / math.sqrt(hs)
+        full = [plain_llama.attention(q.double(), k.double(), v.double(), scale, window) for q, k, v in seqs]
+        want = torch.stack([full[s][p].reshape(-1) for s, p in rows])
+        vmax = max(v.abs().max().item() for _, _, v in seqs)
+        assert not torch.isnan(out).any(), f"{what}: a row was not written"
+        err = (out - want).abs().max().item()
+        assert err <= 2 ** -8 * vmax, f"{what}: off by {err:.3e}"
+    assert ran >= 100
+
+
+def test_sampling_at_random_rows():
+    """The sampling kernel against the plain sampler over 300 random batches: vocabularies from 2 to 4,099,
+    temperatures, top-k from 1 to beyond the vocabulary, top-p down to 0.0001, ties, many equal logits (both
+    zeros among them), rows half masked with -inf, flat rows."""
+    import random
+    for seed in range(300):
+        rng = random.Random(seed)
+        g = torch.Generator().manual_seed(seed)
+        V, R = rng.choice([2, 3, 31, 32, 33, 130, 1000, 1024, 4099]), rng.randint(1, 9)
+        scale = rng.choice([0.01, 1.0, 2.5, 30.0])
+        logits = (scale * torch.randn(R, V, generator=g)).float()
+        kind = rng.choice(["plain", "ties", "rounded", "masked", "flat"])
+        if kind == "ties":
+            for r in range(R):
+                logits[r, torch.randint(0, V, (min(V, 5),), generator=g)] = logits[r].max() + rng.choice([0.0, 1.0])
+        elif kind == "rounded":
+            logits = (logits * 2).round() / 2
+        elif kind == "masked":
+            mask = torch.rand(R, V, generator=g) < 0.5
+            mask[:, 0] = False
+            logits[mask] = float("-inf")
+        elif kind == "flat":
+            logits[:] = 1.25
+        temps = [rng.choice([0.0, 0.3, 0.7, 1.0, 1.5]) for _ in range(R)]
+        ks = [rng.choice([0, 1, 2, 5, 50, V, V + 5]) for _ in range(R)]
+        ps = [rng.choice([1.0, 0.99, 0.9, 0.5, 0.1, 0.0001]) for _ in range(R)]
+        seeds, ctrs = [rng.randrange(2 ** 31) for _ in range(R)], [rng.randrange(1000) for _ in range(R)]
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops().sample(logits.to(DEV), out, temperature=torch.tensor(temps, device=DEV),
+                     top_k=torch.tensor(ks, dtype=torch.int32, device=DEV), top_p=torch.tensor(ps, device=DEV),
+                     seed=torch.tensor(seeds, dtype=torch.int64, device=DEV), counter=torch.tensor(ctrs, dtype=torch.int64, device=DEV))
+        want = [plain_llama.sample(logits[r], temps[r], ks[r], ps[r], seed=seeds[r], counter=ctrs[r]) for r in range(R)]
+        got = out.tolist()
+        for r in range(R):
+            if got[r] == want[r]:
+                continue
+            # a draw that lands within rounding of a boundary between two kept tokens may fall either way (the
+            # kernel sums in float32, the plain sampler in float64): both must then be kept tokens of equal
+            # or neighbouring cumulative mass; anything else is a fault
+            assert temps[r] > 0 and logits[r, got[r]] > float("-inf"), (
+                f"seed {seed}, {kind}, row {r}: kernel {got[r]}, plain {want[r]} (T {temps[r]}, k {ks[r]}, p {ps[r]})")
+            p = torch.softmax(logits[r].double() / temps[r], 0)
+            lo, hi = sorted((got[r], want[r]))
+            between = p[lo:hi + 1].sum().item() - max(p[lo].item(), p[hi].item())
+            assert between <= 1e-5, (
+                f"seed {seed}, {kind}, row {r}: kernel {got[r]}, plain {want[r]} with mass {between:.2e} between them")
