@@ -101,6 +101,7 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   const int page_rows = 1 << log2_page;
   const int pages_per_tile = BN >> log2_page;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
@@ -128,6 +129,9 @@ attn_portion_tc05_kernel(const AttnParams p, const __grid_constant__ CUtensorMap
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   tc05_fence_before_sync();
   __syncthreads();                                   // barriers, tensor memory and the zeroed rows stand
+  // launched as a programmatic dependent, all of the above ran while the kernel before this one (which wrote the
+  // queries and the newest keys and values) was ending; the items and the block table were copied in earlier
+  pdl_wait();
   tc05_fence_after_sync();
   const unsigned tmem = tmem_slot;
   if (warp != 8) {
@@ -448,7 +452,7 @@ static int launch(const AttnParams& p, const CUtensorMap& km, const CUtensorMap&
   auto k = attn_portion_tc05_kernel<NH>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  k<<<dim3(p.KV, num_items), 320, smem, stream>>>(p, km, vm, log2_page);
+  si_launch(k, dim3(p.KV, num_items), dim3(320), smem, stream, p, km, vm, log2_page);
   return si_last_error();
 }
 

@@ -111,6 +111,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int nk = (K + BK - 1) / BK;
+  pdl_trigger();
 
   if (threadIdx.x == 0) {
 #pragma unroll
@@ -124,6 +125,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   __syncthreads();
   tc05_fence_after_sync();
   const unsigned tmem = tmem_slot;
+  pdl_wait();                                           // see the pair kernel
 
   if (warp == 0) {
     if (lane == 0) {
@@ -248,6 +250,7 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
   const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int nk = (K + BK - 1) / BK;
+  pdl_trigger();                                          // one block an SM: the next kernel's blocks take no block's place
 
   if (threadIdx.x == 0) {
 #pragma unroll
@@ -261,9 +264,20 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
   cluster_sync_all();                                     // both CTAs' barriers and tensor memory are ready
   tc05_fence_after_sync();
   const unsigned tmem = tmem_slot;
-
+  // Launched as a programmatic dependent: everything above ran while the kernel before this one was ending. W does
+  // not depend on that kernel, so the producer also fetches the W boxes of its first stages before it waits;
+  // nothing else touches global memory before that kernel's results are there.
   if (warp == 0) {
     if (lane == 0) {
+      const long long total = (long long)((tiles - pair + pairs - 1) / pairs) * nk;     // k steps of this pair
+      const int ahead = total < STAGES ? (int)total : STAGES;
+      for (int i = 0; i < ahead; ++i) {
+        const int tile = pair + (i / nk) * pairs, kb = i % nk;
+        const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+        if (rank == 0) mbar_expect_tx(&full_bar[i], 2 * (A_BYTES + B_BYTES));
+        tma_load_2d_pair(Bs + i * B_BYTES, &bmap, cluster_map_u32(&full_bar[i], 0), kb * BK, n0);
+      }
+      pdl_wait();
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < tiles && ok; tile += pairs) {
@@ -271,15 +285,17 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
         const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < nk; ++kb, ++it) {
           const int s = it % STAGES;
-          if (it >= STAGES && !mbar_wait(&empty_bar[s], (unsigned)(((it / STAGES) - 1) & 1))) {
-            set_status(status, SI_WAIT_LIMIT);
-            ok = false;
-            break;
-          }
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * (A_BYTES + B_BYTES));
           const unsigned bar = cluster_map_u32(&full_bar[s], 0);
+          if (it >= ahead) {
+            if (it >= STAGES && !mbar_wait(&empty_bar[s], (unsigned)(((it / STAGES) - 1) & 1))) {
+              set_status(status, SI_WAIT_LIMIT);
+              ok = false;
+              break;
+            }
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * (A_BYTES + B_BYTES));
+            tma_load_2d_pair(Bs + s * B_BYTES, &bmap, bar, kb * BK, n0);
+          }
           tma_load_2d_pair(As + s * A_BYTES, &amap, bar, kb * BK, m0);
-          tma_load_2d_pair(Bs + s * B_BYTES, &bmap, bar, kb * BK, n0);
         }
       }
     }
@@ -314,6 +330,7 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
       if (!ok && lane == 0) set_status(status, SI_WAIT_LIMIT);
     }
   } else {
+    pdl_wait();                                           // `out` may still be read by the kernel before this one
     const int q = warp & 3;
     const bool vec = (ldo % 8 == 0) && ((uintptr_t)out % 16 == 0);
     const bool vec4 = (ldo % 4 == 0) && ((uintptr_t)out % 16 == 0);          // rows of fp32 in 16-byte pieces
@@ -377,7 +394,7 @@ static int launch_pair(const CUtensorMap& am, const CUtensorMap& bm_half, void* 
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
   const int pairs = tiles < si_sm_count() / 2 ? tiles : si_sm_count() / 2;
   if (pairs < 1) return -2;
-  k<<<dim3(2 * pairs), 192, smem, stream>>>(am, bm_half, (TO*)out, ldo, M, N, K, status);
+  si_launch(k, dim3(2 * pairs), dim3(192), smem, stream, am, bm_half, (TO*)out, ldo, M, N, K, status);
   return si_last_error();
 }
 
@@ -390,7 +407,7 @@ static int launch(const CUtensorMap& am, const CUtensorMap& bm, void* out, long 
   if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + 127) / 128) * ((N + 255) / 256);
   const int blocks = tiles < si_sm_count() ? tiles : si_sm_count();
-  k<<<dim3(blocks), 192, smem, stream>>>(am, bm, (TO*)out, ldo, M, N, K, status);
+  si_launch(k, dim3(blocks), dim3(192), smem, stream, am, bm, (TO*)out, ldo, M, N, K, status);
   return si_last_error();
 }
 
