@@ -178,3 +178,56 @@ SI_EXPORT int si_add_rmsnorm(float* resid, const void* delta, const int* rows, c
     return launch2<float, __nv_bfloat16>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
   return launch2<float, float>(resid, delta, rows, weight, out, num_rows, hidden, eps, ahead, ahead_bytes, stream);
 }
+
+// ---- a norm that is not on the residual stream ------------------------------------------------------------------
+// out[r, :] = weight * x[r, :] * rsqrt(mean(x[r, :]^2) + eps) for rows of `n` elements that lie in a two-level
+// layout: row r = (a, b) with b < inner starts at x + a * outer_stride + b * inner_stride (the heads of a token
+// inside a stacked projection, for a norm over each head; inner = 1 for plain rows). One warp a row, statistics in
+// fp32, in place if out == x. Nothing is added and no stream is written: what a mixer calls for a norm of its own.
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const TX* __restrict__ x, TX* __restrict__ out,
+                                                           const TW* __restrict__ weight, long long num_rows, int n, int inner,
+                                                           long long x_outer, long long x_inner, long long o_outer,
+                                                           long long o_inner, float eps) {
+  pdl_prologue();
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= num_rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long a = r / inner, b = r - a * inner;
+  const TX* xr = x + a * x_outer + b * x_inner;
+  TX* orow = out + a * o_outer + b * o_inner;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) {
+    const float v = to_f32<TX>(xr[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)n + eps);
+  for (int i = lane; i < n; i += 32) orow[i] = from_f32<TX>(to_f32<TW>(weight[i]) * (to_f32<TX>(xr[i]) * inv));
+}
+
+template <typename TX, typename TW>
+static int rows_launch(const void* x, void* out, const void* weight, long long num_rows, int n, int inner, long long x_outer,
+                       long long x_inner, long long o_outer, long long o_inner, float eps, cudaStream_t stream) {
+  const long long blocks = (num_rows + 7) / 8;
+  if (blocks > 0x7fffffffLL) return -2;
+  si_launch(rmsnorm_rows_kernel<TX, TW>, dim3((unsigned)blocks), dim3(256), 0, stream, (const TX*)x, (TX*)out, (const TW*)weight,
+            num_rows, n, inner, x_outer, x_inner, o_outer, o_inner, eps);
+  return si_last_error();
+}
+
+// x_dtype: dtype of x and out; strides in elements. Returns 0, a CUDA error code, or -2 (size refused).
+SI_EXPORT int si_rmsnorm_rows(const void* x, void* out, int x_dtype, const void* weight, int weight_dtype, long long num_rows,
+                              int n, int inner, long long x_outer, long long x_inner, long long o_outer, long long o_inner,
+                              float eps, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (n <= 0 || inner <= 0) return -2;
+  if (x_dtype == SI_BF16) {
+    if (weight_dtype == SI_BF16)
+      return rows_launch<__nv_bfloat16, __nv_bfloat16>(x, out, weight, num_rows, n, inner, x_outer, x_inner, o_outer, o_inner, eps, stream);
+    return rows_launch<__nv_bfloat16, float>(x, out, weight, num_rows, n, inner, x_outer, x_inner, o_outer, o_inner, eps, stream);
+  }
+  if (weight_dtype == SI_BF16) return -2;
+  return rows_launch<float, float>(x, out, weight, num_rows, n, inner, x_outer, x_inner, o_outer, o_inner, eps, stream);
+}
+

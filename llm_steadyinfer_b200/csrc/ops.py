@@ -174,6 +174,26 @@ def add_rmsnorm(resid, delta, weight, eps: float, out, rows=None, ahead=None) ->
              R, d, float(eps), _ptr(ahead) if ahead_bytes else None, ahead_bytes, _stream()), f"add_rmsnorm(hidden={d})")
 
 
+def rmsnorm_rows(x, weight, eps: float, out=None) -> None:
+    """out[..., :] = weight * x[..., :] * rsqrt(mean(x[..., :]^2) + eps) over the last dimension of a 2-D or 3-D
+    tensor (or view: only the last dimension must be contiguous), in place by default. No residual stream is
+    involved: for norms inside a part (a norm over each head of a stacked projection, say)."""
+    out = x if out is None else out
+    _cuda(x, weight, out)
+    _need(x.dim() in (2, 3) and out.shape == x.shape and out.dtype == x.dtype, "rmsnorm_rows: x and out must be 2-D or 3-D and alike")
+    _need(x.stride(-1) == 1 and out.stride(-1) == 1 and weight.is_contiguous() and weight.numel() == x.shape[-1],
+          "rmsnorm_rows: the last dimension must be contiguous and as long as the weight")
+    if x.dim() == 2:
+        rows, inner = x.shape[0], 1
+        xs, os_ = (x.stride(0), 0), (out.stride(0), 0)
+    else:
+        rows, inner = x.shape[0] * x.shape[1], x.shape[1]
+        xs, os_ = (x.stride(0), x.stride(1)), (out.stride(0), out.stride(1))
+    f = _fn("norm", "si_rmsnorm_rows", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_f, _c_p])
+    _check(f(_ptr(x), _ptr(out), _dt(x), _ptr(weight), _dt(weight), rows, x.shape[-1], inner, xs[0], xs[1], os_[0], os_[1],
+             float(eps), _stream()), f"rmsnorm_rows(n={x.shape[-1]})")
+
+
 def rope_kv_write(qkv, positions, row_seq, inv_freq, rot_dim: int, block_table, k_cache, v_cache,
                   page_size: int, num_seqs: int, H: int, KV: int, hs: int, status=None) -> None:
     """Rotate q (in place) and k, store k and v of every row into its page.

@@ -102,6 +102,12 @@ class Norm(Part):
                 rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 
+    def normalize(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> None:
+        """The norm alone, over the last dimension of ``x`` (2-D or 3-D, last dimension contiguous), in place by
+        default: for a norm that is not on the residual stream (one that a mixer applies to its queries and keys,
+        head by head, say). Kinds that have no such form leave this unimplemented."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     def rotary(self) -> Optional[Tuple[torch.Tensor, int]]:

@@ -38,5 +38,8 @@ class RMSNorm(Norm):
     def forward(self, resid, delta, out, rows=None, ahead=None):
         ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, ahead=ahead)
 
+    def normalize(self, x, out=None):
+        ops.rmsnorm_rows(x, self.weight, self.eps, out)
+
 
 register_norm("rmsnorm", RMSNorm)

@@ -270,6 +270,31 @@ def test_argmax_split(R, V):
         assert torch.equal(one, out)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_rows_off_the_residual_stream(dtype):
+    """The norm alone over rows, and over the heads of a token inside a stacked projection (a 3-D view with two
+    strides), in place and into another buffer, against torch; what lies beside the rows is not touched."""
+    g = torch.Generator().manual_seed(29)
+    T, H, KV, hs, eps = 37, 5, 2, 48, 3e-6
+    w = (1 + 0.1 * torch.randn(hs, generator=g)).to(dtype).to(DEV)
+    qkv = torch.randn(T, (H + 2 * KV) * hs, generator=g).to(dtype).to(DEV)
+    before = qkv.clone()
+    q = qkv[:, :H * hs].view(T, H, hs)
+    want = plain_llama.rmsnorm(before[:, :H * hs].double().cpu().view(T, H, hs), w.double().cpu(), eps)
+    ops().rmsnorm_rows(q, w, eps)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7 * want.abs().max().item()
+    assert (qkv[:, :H * hs].double().cpu().view(T, H, hs) - want).abs().max().item() <= tol
+    assert torch.equal(qkv[:, H * hs:], before[:, H * hs:]), "keys and values beside the queries are as they were"
+    x = torch.randn(9, 1336, generator=g).to(dtype).to(DEV)
+    w2 = (1 + 0.1 * torch.randn(1336, generator=g)).to(DEV)                      # a weight kept in 32-bit
+    out = torch.full_like(x, float("nan"))
+    ops().rmsnorm_rows(x, w2, 1e-5, out)
+    want = plain_llama.rmsnorm(x.double().cpu(), w2.double().cpu(), 1e-5)
+    assert (out.double().cpu() - want).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2 ** -7 * want.abs().max().item())
+    with pytest.raises(ops().KernelError):
+        ops().rmsnorm_rows(x.t(), w2, 1e-5)
+
+
 def test_sampling_kernel_matches_plain():
     g = torch.Generator().manual_seed(6)
     V, R = 1000, 24

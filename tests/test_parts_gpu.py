@@ -63,6 +63,11 @@ def test_norm_and_mlp_parts(folders, dtype):
     tol = 1e-5 if dtype == torch.float32 else 2 ** -8 * want.abs().max().item()
     assert (x.double().cpu() - want).abs().max().item() <= tol
     assert (r.double().cpu() - h).abs().max().item() <= 1e-6
+    # the norm alone, off the residual stream (what a mixer with a norm of its own would call)
+    y3 = (0.5 * torch.randn(T, 3, d, generator=g)).to(dtype).to(DEV)
+    want3 = pl.rmsnorm(y3.double().cpu(), w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+    blk.feed_forward_norm.normalize(y3)
+    assert (y3.double().cpu() - want3).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2 ** -7 * want3.abs().max().item())
 
     class Ctx:                                   # the feed-forward needs scratch and the status word only
         status = None
