@@ -107,13 +107,13 @@ __device__ __forceinline__ void l2_prefetch_share(const void* base, long long by
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
-// SI_PDL_TRIGGER: 0 no kernel triggers; 1 (default) the small kernels; 2 also every kernel of one wave of
+// SI_PDL_TRIGGER: 0 no kernel triggers; 1 the small kernels; 2 (default) also every kernel of one wave of
 // blocks, at its start; 3 also kernels of several waves, once their main loop is done.
 static inline int si_pdl_trigger_level() {
   static int level = -1;
   if (level < 0) {
     const char* e = getenv("SI_PDL_TRIGGER");
-    level = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 1;
+    level = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 2;
   }
   return level;
 }
